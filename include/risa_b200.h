@@ -1,0 +1,110 @@
+/*
+ * C-ABI of the B200-native RISA quantised-attention library (librisa_b200.so).
+ *
+ * Every entry point takes plain pointers to DEVICE memory, sizes, element strides and the
+ * caller's CUDA stream (as void*), enqueues work on that stream without synchronising the host,
+ * allocates nothing unless stated, and returns 0 on success or a non-zero status whose text is
+ * available from risa_b200_last_error() (thread-local).  The reference project's own launchers
+ * throw C++ exceptions through their extern "C" signatures; a status code is what a cgo / JNI /
+ * ctypes / nanobind caller can actually consume.
+ *
+ * Each declaration names the reference interface it replaces (path inside the reference project).
+ * Data layouts are the reference's public packed formats:
+ *   q/k codes  int8 [B,H,L,D] contiguous, D in {64,128,256}
+ *   q scales   f32  [B,Hq,ceil(Lq/128)*(D==256?64:32)],  k scales f32 [B,Hkv,ceil(Lk/cta_k)*4]
+ *   v codes    int8 [B*Hkv*D, padded_Lk] with the 16-token storage order
+ *              {0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15}, v scale / centre f32 [B*Hkv*D]
+ * dtype codes: 0 = float32, 1 = float16, 2 = bfloat16, 3 = bool (masks only).
+ */
+#ifndef RISA_B200_H
+#define RISA_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RISA_B200_OK 0
+#define RISA_B200_INVALID 1 /* contract violation: shapes, strides, alignment, null pointers */
+#define RISA_B200_CUDA 2    /* CUDA runtime / launch error                                     */
+#define RISA_B200_DEVICE 3  /* kernel reported a device-side failure (bounded wait ran out)    */
+
+/* Text of the last failure on the calling thread ("" if none). */
+const char* risa_b200_last_error(void);
+/* Library ABI version; bumped when a signature changes. */
+int risa_b200_abi_version(void);
+
+/* K anchor detection + rotation + INT8 quantisation of Q and K.
+ * Replaces launch_quantize_qk / launch_quantize_qk_gather (csrc/launchers.h:14-31; kernels
+ * csrc/kernels/quantize_qk_impl.cuh:442-826).  q_perm / k_perm: optional int32 [B,H,L] gather
+ * tables (NULL = identity), the reference's risa::QuantInput.  anchors: int32 [B,Hkv] scratch that
+ * receives the chosen anchor row (or -1). */
+int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scale, const void* k,
+                          void* k_codes, float* k_scale, int batch, int q_heads, int q_len,
+                          int kv_heads, int k_len, int head_dim, int cta_k, int64_t q_stride_b,
+                          int64_t q_stride_h, int64_t q_stride_n, int64_t k_stride_b,
+                          int64_t k_stride_h, int64_t k_stride_n, int dtype_code, int32_t* anchors,
+                          const int32_t* q_perm, const int32_t* k_perm, void* stream);
+
+/* Per-channel INT8 quantisation of V (absmax or residual-corrected midpoint-affine) into the
+ * transposed, token-permuted packed layout.  Replaces launch_quantize_v / launch_quantize_v_gather
+ * (csrc/launchers.h:33-43; kernel csrc/kernels/quantize_v_impl.cuh:83-409).  workspace: device
+ * scratch of at least risa_b200_quantize_v_workspace_size() bytes (the reference kernel needs
+ * none because it uses one CTA per 8 channels; this one spreads a channel over many CTAs). */
+size_t risa_b200_quantize_v_workspace_size(int batch, int kv_heads, int k_len, int head_dim);
+int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_center, int batch,
+                         int kv_heads, int k_len, int head_dim, int padded_len, int64_t stride_b,
+                         int64_t stride_h, int64_t stride_n, int dtype_code, int midpoint_affine,
+                         const int32_t* perm, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/* Fused INT8 attention over packed operands: dense, masked, causal, CSR sparse reuse, block-mass
+ * capture, optional LSE.  Replaces launch_attention (csrc/launchers.h:49-60; kernels
+ * csrc/kernels/attention_int8.cuh:145-1088, attention_dispatch.cu:113-296).  Same argument
+ * meaning; block_mass is the reference's capture workspace (masses, per-tile statistics, final
+ * softmax state) in the same layout. */
+int risa_b200_attention(const void* q, const void* k, const void* v, void* o, const float* q_scale,
+                        const float* k_scale, const float* v_scale, const float* v_center,
+                        const void* mask, int64_t mask_stride_b, int64_t mask_stride_h,
+                        int64_t mask_stride_q, int64_t mask_stride_k, int mask_dtype_code,
+                        int cta_k, int batch, int q_len, int k_len, int q_heads, int kv_heads,
+                        int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h,
+                        float sm_scale, int out_dtype_code, const int32_t* sparse_row_offsets,
+                        const int32_t* sparse_block_indices, float* block_mass, int is_causal,
+                        float* lse, const int32_t* key_mask_tiles, void* stream);
+
+/* Selects which attention kernel family the library may use: 0 = automatic (tensor-core kernel
+ * where it applies), 1 = force the row-per-thread integer kernel (used by parity tests to compare
+ * the two).  Process-wide; returns the previous value. */
+int risa_b200_set_attention_path(int path);
+
+/* Retained-mass prefix selection over descending-sorted block masses and CSR packing.  Replaces
+ * launch_select_retained_mass + retained_mass_selector_workspace_size (csrc/launchers.h:61-67;
+ * csrc/kernels/sparse_selection.cu:9-159).  summary receives {selected mass, total mass, number of
+ * selected blocks} as doubles. */
+size_t risa_b200_selector_workspace_size(int row_count);
+int risa_b200_select_retained_mass(const float* sorted_mass, const int64_t* descending_indices,
+                                   int32_t* counts, uint8_t* support, double* row_totals,
+                                   int32_t* row_offsets, int32_t* block_indices, double* summary,
+                                   void* scan_workspace, size_t scan_workspace_bytes,
+                                   int row_count, int key_blocks, double theta, void* stream);
+
+/* Visible-tile list of a mask broadcast over queries.  Replaces launch_prepare_key_mask_tiles
+ * (csrc/launchers.h:45-48; csrc/kernels/key_mask_tiles.cu:10-61). */
+int risa_b200_prepare_key_mask_tiles(const void* mask, int32_t* tiles, int batch, int q_heads,
+                                     int k_len, int tile_size, int64_t stride_b, int64_t stride_h,
+                                     int64_t stride_k, int dtype_code, void* stream);
+
+/* Row-wise logit shift scale * <q_i, k_anchor> removed by the K anchor translation.  Replaces
+ * launch_correct_lse (csrc/launchers.h:9-13; csrc/kernels/lse_correction.cu:4-44). */
+int risa_b200_correct_lse(const void* q, const void* k, const int32_t* anchors, float* out,
+                          int batch, int q_heads, int kv_heads, int q_len, int head_dim,
+                          int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n, float scale,
+                          int dtype_code, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RISA_B200_H */

@@ -1,0 +1,191 @@
+"""Loads the C-ABI library and exposes it as the native module the runtime calls.
+
+The reference binds its kernels through a nanobind module ``_C`` that receives DLPack capsules
+(src/risa_attention/_backend.py:6-54, csrc/bindings.cpp:642-673).  Here ``_C`` is a thin object
+over ``librisa_b200.so`` (see include/risa_b200.h): tensors are passed as device pointers plus
+element strides, the stream as the raw ``cudaStream_t``.  There is no CPU fallback: when the
+library or a capable GPU is missing every entry point raises ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+MINIMUM_COMPUTE_CAPABILITY = (10, 0)
+_LIB_PATH = Path(__file__).resolve().parent / "librisa_b200.so"
+_EXTENSION_ERROR: Exception | None = None
+
+c_i32, c_i64, c_f32, c_f64, c_vp, c_sz = (
+    ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t,
+)
+
+_SIGNATURES = {
+    "risa_b200_last_error": (ctypes.c_char_p, []),
+    "risa_b200_abi_version": (c_i32, []),
+    "risa_b200_quantize_qk": (c_i32, [c_vp] * 6 + [c_i32] * 7 + [c_i64] * 6 + [c_i32] + [c_vp] * 4),
+    "risa_b200_quantize_v_workspace_size": (c_sz, [c_i32] * 4),
+    "risa_b200_quantize_v": (
+        c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 3 + [c_i32] * 2 + [c_vp, c_vp, c_sz, c_vp]),
+    "risa_b200_attention": (
+        c_i32,
+        [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
+                                                                   c_i32, c_vp, c_vp, c_vp]),
+    "risa_b200_set_attention_path": (c_i32, [c_i32]),
+    "risa_b200_selector_workspace_size": (c_sz, [c_i32]),
+    "risa_b200_select_retained_mass": (
+        c_i32, [c_vp] * 9 + [c_sz, c_i32, c_i32, c_f64, c_vp]),
+    "risa_b200_prepare_key_mask_tiles": (c_i32, [c_vp, c_vp] + [c_i32] * 4 + [c_i64] * 3 + [c_i32, c_vp]),
+    "risa_b200_correct_lse": (
+        c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 6 + [c_f32, c_i32, c_vp]),
+}
+
+DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.bool: 3}
+
+
+def _ptr(tensor):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def _stride(tensor, dim):
+    # An extent of one never contributes to an address; report 0 so alignment checks ignore it.
+    return tensor.stride(dim)
+
+
+class _Native:
+    """ctypes view of librisa_b200.so with the reference's native entry-point names."""
+
+    fused_gather_version = 1
+
+    def __init__(self, path: Path):
+        self.lib = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(self.lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+
+    def _check(self, status: int):
+        if status != 0:
+            raise RuntimeError(self.lib.risa_b200_last_error().decode())
+
+    # -- risa_sdpa_quantize (csrc/bindings.cpp:195-272) ---------------------------------------
+    def risa_sdpa_quantize(self, q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale,
+                           v_center, cta_k, input_dtype_code, use_midpoint_affine, stream_ptr,
+                           anchors, q_perm=None, k_perm=None, v_perm=None, workspace=None):
+        b, hq, lq, d = q.shape
+        hkv, lk = k.shape[1], k.shape[2]
+        self._check(self.lib.risa_b200_quantize_qk(
+            _ptr(q), _ptr(q_int8), _ptr(q_scale), _ptr(k), _ptr(k_int8), _ptr(k_scale), b, hq, lq,
+            hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
+            k.stride(2), input_dtype_code, _ptr(anchors), _ptr(q_perm), _ptr(k_perm), stream_ptr))
+        self._check(self.lib.risa_b200_quantize_v(
+            _ptr(v), _ptr(v_int8), _ptr(v_scale), _ptr(v_center), b, hkv, lk, d, v_int8.shape[1],
+            v.stride(0), v.stride(1), v.stride(2), input_dtype_code, int(use_midpoint_affine),
+            _ptr(v_perm), _ptr(workspace), workspace.numel() * workspace.element_size(),
+            stream_ptr))
+
+    def quantize_v_workspace_size(self, batch, kv_heads, k_len, head_dim) -> int:
+        return int(self.lib.risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim))
+
+    # -- risa_sdpa_prequantized (csrc/bindings.cpp:277-461) -------------------------------------
+    def risa_sdpa_prequantized(self, q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale,
+                               v_center, cta_k, sm_scale, output_dtype_code, stream_ptr,
+                               attn_mask=None, sparse_row_offsets=None, sparse_block_indices=None,
+                               block_mass=None, is_causal=False, lse=None, key_mask_tiles=None):
+        b, hq, lq, d = q_int8.shape
+        hkv, lk = k_int8.shape[1], k_int8.shape[2]
+        padded = (lk + cta_k - 1) // cta_k * cta_k
+        if v_int8.ndim != 2 or tuple(v_int8.shape) != (b * hkv * d, padded) or \
+                tuple(o.shape) != (b, hq, lq, d) or k_int8.shape[0] != b or k_int8.shape[3] != d:
+            raise RuntimeError("risa_sdpa_prequantized: incompatible quantized tensor shapes")
+        hnd = (lq <= 1 or o.stride(2) == d) and (hq <= 1 or o.stride(1) == lq * d)
+        nhd = (hq <= 1 or o.stride(1) == d) and (lq <= 1 or o.stride(2) == hq * d)
+        if not (q_int8.is_contiguous() and k_int8.is_contiguous() and v_int8.is_contiguous()) or \
+                o.stride(3) != 1 or not (hnd or nhd):
+            raise RuntimeError("risa_sdpa_prequantized: quantized tensors must be contiguous and "
+                               "output must use HND- or NHD-contiguous storage")
+        if lse is not None and (tuple(lse.shape) != (b, hq, lq) or lse.dtype != torch.float32
+                                or not lse.is_contiguous()):
+            raise RuntimeError(
+                "risa_sdpa_prequantized: LSE must be contiguous float32 [batch_size,Hq,query_length]")
+        ms = (0, 0, 0, 0)
+        mask_code = -1
+        if attn_mask is not None:
+            if tuple(attn_mask.shape) != (b, hq, lq, lk):
+                raise RuntimeError("risa_sdpa_prequantized: attention mask must be expanded to "
+                                   "[batch_size,query_heads,query_length,key_length]")
+            if attn_mask.dtype not in DTYPE_CODES:
+                raise RuntimeError("risa_sdpa_prequantized: attention mask must be bool, float16, "
+                                   "bfloat16, or float32")
+            mask_code = DTYPE_CODES[attn_mask.dtype]
+            ms = attn_mask.stride()
+        o_b = hq * lq * d if b <= 1 else o.stride(0)
+        o_n = d if lq <= 1 else o.stride(2)
+        o_h = lq * d if hq <= 1 else o.stride(1)
+        self._check(self.lib.risa_b200_attention(
+            _ptr(q_int8), _ptr(k_int8), _ptr(v_int8), _ptr(o), _ptr(q_scale), _ptr(k_scale),
+            _ptr(v_scale), _ptr(v_center), _ptr(attn_mask), ms[0], ms[1], ms[2], ms[3], mask_code,
+            cta_k, b, lq, lk, hq, hkv, d, o_b, o_n, o_h, sm_scale, output_dtype_code,
+            _ptr(sparse_row_offsets), _ptr(sparse_block_indices), _ptr(block_mass),
+            int(is_causal), _ptr(lse), _ptr(key_mask_tiles), stream_ptr))
+
+    # -- select_retained_mass_csr (csrc/bindings.cpp, sparse_selection.cu) ----------------------
+    def retained_mass_selector_workspace_size(self, row_count: int) -> int:
+        return int(self.lib.risa_b200_selector_workspace_size(row_count))
+
+    def select_retained_mass_csr(self, sorted_mass, descending_indices, counts, support,
+                                 row_totals, row_offsets, block_indices, summary, scan_workspace,
+                                 theta, stream_ptr):
+        rows, blocks = sorted_mass.shape
+        self._check(self.lib.risa_b200_select_retained_mass(
+            _ptr(sorted_mass), _ptr(descending_indices), _ptr(counts), _ptr(support),
+            _ptr(row_totals), _ptr(row_offsets), _ptr(block_indices), _ptr(summary),
+            _ptr(scan_workspace), scan_workspace.numel(), rows, blocks, float(theta), stream_ptr))
+
+    def prepare_key_mask_tiles(self, mask, tiles, tile_size, stream_ptr):
+        if mask.ndim != 4 or mask.stride(2) != 0 or tile_size not in (64, 128):
+            raise RuntimeError("prepare_key_mask_tiles requires an expanded broadcast key mask")
+        b, h, _, lk = mask.shape
+        self._check(self.lib.risa_b200_prepare_key_mask_tiles(
+            _ptr(mask), _ptr(tiles), b, h, lk, tile_size, mask.stride(0), mask.stride(1),
+            mask.stride(3), DTYPE_CODES[mask.dtype], stream_ptr))
+
+    def risa_lse_shift(self, q, k, anchors, out, scale, stream_ptr):
+        b, hq, lq, d = q.shape
+        self._check(self.lib.risa_b200_correct_lse(
+            _ptr(q), _ptr(k), _ptr(anchors), _ptr(out), b, hq, k.shape[1], lq, d, q.stride(0),
+            q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), scale,
+            DTYPE_CODES[q.dtype], stream_ptr))
+
+    def set_attention_path(self, path: int) -> int:
+        return int(self.lib.risa_b200_set_attention_path(path))
+
+
+try:
+    if getattr(torch.version, "hip", None) or not getattr(torch.version, "cuda", None):
+        raise ImportError("RISA Attention requires an NVIDIA CUDA build of PyTorch")
+    _C = _Native(_LIB_PATH)
+except (ImportError, OSError, AttributeError) as error:
+    _C = None
+    _EXTENSION_ERROR = error
+
+
+def is_available(device: torch.device | int | str | None = None) -> bool:
+    """True when the library is loaded and ``device`` is a Blackwell datacenter GPU (sm_100)."""
+    if _C is None or not torch.cuda.is_available():
+        return False
+    try:
+        resolved = None
+        if device is not None:
+            resolved = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+            if resolved.type != "cuda":
+                return False
+        return torch.cuda.get_device_capability(resolved) >= MINIMUM_COMPUTE_CAPABILITY
+    except (AssertionError, RuntimeError, ValueError):
+        return False
+
+
+def require_extension() -> None:
+    if _C is None:
+        detail = f": {_EXTENSION_ERROR}" if _EXTENSION_ERROR is not None else ""
+        raise RuntimeError(f"RISA Attention CUDA library is not available{detail}")

@@ -1,0 +1,62 @@
+"""Builds librisa_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
+
+Usage: ``python -m risaattention_b200.build [--force]``.  Objects are cached under
+``risaattention_b200/csrc/_obj`` and rebuilt when a source or header is newer.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OBJ = CSRC / "_obj"
+LIB = PKG / "librisa_b200.so"
+UNITS = ["prep_qk", "prep_v", "misc", "attention_api", "attention_rows", "attention_tc"]
+# --use_fast_math is part of the numeric contract shared with the reference's kernels
+# (approximate division / reciprocal, flush-to-zero, contracted multiply-adds).
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "--use_fast_math", "--expt-relaxed-constexpr",
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
+]
+
+
+def _newest_header() -> float:
+    headers = list(CSRC.glob("*.cuh")) + list((PKG.parent / "include").glob("*.h"))
+    return max(p.stat().st_mtime for p in headers)
+
+
+def _compile(unit: str, force: bool, verbose: bool) -> str | None:
+    src, obj = CSRC / f"{unit}.cu", OBJ / f"{unit}.o"
+    if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, _newest_header()):
+        return None
+    cmd = ["nvcc", *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {unit}.cu:\n{proc.stdout}\n{proc.stderr}")
+    return proc.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        logs = list(pool.map(lambda u: _compile(u, force, verbose), UNITS))
+    rebuilt = any(log is not None for log in logs)
+    if verbose:
+        for unit, log in zip(UNITS, logs):
+            if log:
+                (OBJ / f"{unit}.ptxas.log").write_text(log)
+    if rebuilt or not LIB.exists():
+        objs = [str(OBJ / f"{u}.o") for u in UNITS]
+        subprocess.run(["nvcc", "-shared", "-o", str(LIB), *objs, "-lcudart", "-lcuda"], check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

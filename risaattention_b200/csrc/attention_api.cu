@@ -1,0 +1,146 @@
+// C-ABI entry of the fused INT8 attention call: validation, kernel-family selection and the
+// block-mass reduction that follows a capture pass.
+#include "attention_common.cuh"
+#include <atomic>
+
+namespace risa_b200 {
+namespace {
+
+std::atomic<int> g_attention_path{0};
+
+// Block mass of (query block, key tile): sum over the block's queries of
+// numerator * 2^(tile_max - m_final) / d_final.  One CTA per (query block, head, batch), thread =
+// query; the sum uses the reference's tree (shfl_down inside each warp, then across the four warp
+// sums; attention_int8.cuh:1067-1086) because the masses feed an exact selection.
+__global__ __launch_bounds__(128) void block_mass_kernel(const AttentionArgs a, int n_q, int n_k) {
+  __shared__ float warp_sums[4];
+  const CaptureLayout cap = capture_layout(a, n_q, n_k);
+  const int q_block = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int row = q_block * 128 + threadIdx.x;
+  const bool ok = row < a.q_len;
+  const int64_t bh = int64_t(batch) * a.q_heads + head;
+  const int64_t grow = bh * a.q_len + row;
+  float m_final = 0.f, d_final = 0.f;
+  if (ok) {
+    m_final = cap.state[grow * 2];
+    d_final = cap.state[grow * 2 + 1];
+  }
+  float* out = a.block_mass + (bh * n_q + q_block) * n_k;
+  for (int t = 0; t < n_k; ++t) {
+    float mass = 0.0f;
+    if (ok) {
+      float numer, tmax;
+      if (t + 1 < n_k) {
+        const uint32_t* slot = cap.full + (grow * (n_k - 1) + t) * 2;
+        numer = __uint2float_rn(slot[0]);
+        tmax = __uint_as_float(slot[1]);
+      } else {
+        numer = cap.last[grow * 2];
+        tmax = cap.last[grow * 2 + 1];
+      }
+      mass = d_final > 0.0f ? numer * ex2_approx(tmax - m_final) / d_final : 0.0f;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mass += __shfl_down_sync(0xffffffffu, mass, off);
+    __syncthreads();  // warp_sums of the previous tile consumed
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = mass;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float total = threadIdx.x < 4 ? warp_sums[threadIdx.x] : 0.0f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) total += __shfl_down_sync(0xffffffffu, total, off);
+      if (threadIdx.x == 0) out[t] = total;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace risa_b200
+
+using namespace risa_b200;
+
+extern "C" int risa_b200_set_attention_path(int path) {
+  return g_attention_path.exchange(path == 1 ? 1 : 0);
+}
+
+extern "C" int risa_b200_attention(
+    const void* q, const void* k, const void* v, void* o, const float* q_scale,
+    const float* k_scale, const float* v_scale, const float* v_center, const void* mask,
+    int64_t mask_stride_b, int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+    int mask_dtype_code, int cta_k, int batch, int q_len, int k_len, int q_heads, int kv_heads,
+    int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+    int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
+    float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles,
+    void* stream_ptr) {
+  RISA_REQUIRE(cta_k == 64 || cta_k == 128, "risa_attention: cta_k must be 64 or 128");
+  RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
+               "risa_attention: unsupported head_dim");
+  RISA_REQUIRE(!(cta_k == 128 && head_dim == 64),
+               "risa_attention: cta_k 128 requires head_dim 128 or 256");
+  RISA_REQUIRE((sparse_row_offsets == nullptr) == (sparse_block_indices == nullptr),
+               "risa_attention: sparse row offsets and block indices must be provided together");
+  RISA_REQUIRE(!(block_mass && sparse_row_offsets),
+               "risa_attention: block mass requires dense attention");
+  RISA_REQUIRE(q && k && v && o && q_scale && k_scale && v_scale && v_center,
+               "risa_attention: null tensor");
+  RISA_REQUIRE(batch > 0 && q_len > 0 && k_len > 0 && q_heads > 0 && kv_heads > 0 &&
+                   q_heads % kv_heads == 0,
+               "risa_attention: sizes must be positive and q heads divisible by kv heads");
+  RISA_REQUIRE(out_dtype_code == 1 || out_dtype_code == 2,
+               "risa_attention: output_dtype_code must be 1 (fp16) or 2 (bf16)");
+  RISA_REQUIRE(mask == nullptr || (mask_dtype_code >= 0 && mask_dtype_code <= 3),
+               "risa_attention: attention mask must be bool, float16, bfloat16, or float32");
+  RISA_REQUIRE(reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(k) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(v) % 16 == 0 && reinterpret_cast<uintptr_t>(o) % 4 == 0 &&
+                   o_stride_b % 2 == 0 && o_stride_n % 2 == 0 && o_stride_h % 2 == 0,
+               "risa_attention: packed operands must be 16-byte aligned and output strides even");
+  AttentionArgs a;
+  a.q = static_cast<const int8_t*>(q);
+  a.k = static_cast<const int8_t*>(k);
+  a.v = static_cast<const int8_t*>(v);
+  a.o = o;
+  a.q_scale = q_scale;
+  a.k_scale = k_scale;
+  a.v_scale = v_scale;
+  a.v_center = v_center;
+  a.mask = mask;
+  a.mask_stride_b = mask_stride_b;
+  a.mask_stride_h = mask_stride_h;
+  a.mask_stride_q = mask_stride_q;
+  a.mask_stride_k = mask_stride_k;
+  a.mask_dtype_code = mask_dtype_code;
+  a.cta_k = cta_k;
+  a.batch = batch;
+  a.q_len = q_len;
+  a.k_len = k_len;
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.o_stride_b = o_stride_b;
+  a.o_stride_n = o_stride_n;
+  a.o_stride_h = o_stride_h;
+  a.sm_scale = sm_scale;
+  a.out_dtype_code = out_dtype_code;
+  a.row_offsets = sparse_row_offsets;
+  a.block_indices = sparse_block_indices;
+  a.block_mass = block_mass;
+  a.is_causal = is_causal != 0;
+  a.lse = lse;
+  a.key_mask_tiles = (mask != nullptr && mask_stride_q == 0 && !sparse_row_offsets &&
+                      !block_mass && !is_causal)
+                         ? key_mask_tiles
+                         : nullptr;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  int status;
+  if (g_attention_path.load() == 0 && attention_tc_supported(a))
+    status = attention_tc(a, stream);
+  else
+    status = attention_rows(a, stream);
+  if (status != RISA_B200_OK) return status;
+  if (block_mass) {
+    const int n_q = (q_len + 127) / 128, n_k = (k_len + cta_k - 1) / cta_k;
+    block_mass_kernel<<<dim3(n_q, q_heads, batch), 128, 0, stream>>>(a, n_q, n_k);
+    return check_launch("attention (block mass)");
+  }
+  return RISA_B200_OK;
+}

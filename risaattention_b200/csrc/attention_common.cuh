@@ -1,0 +1,91 @@
+// Argument block, capture-workspace layout and per-element helpers shared by the attention kernels.
+#pragma once
+#include "softmax_row.cuh"
+
+namespace risa_b200 {
+
+struct AttentionArgs {
+  const int8_t* q;
+  const int8_t* k;
+  const int8_t* v;
+  void* o;
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const float* v_center;
+  const void* mask;
+  int64_t mask_stride_b, mask_stride_h, mask_stride_q, mask_stride_k;
+  int mask_dtype_code;
+  int cta_k, batch, q_len, k_len, q_heads, kv_heads, head_dim;
+  int64_t o_stride_b, o_stride_n, o_stride_h;  // in elements
+  float sm_scale;
+  int out_dtype_code;  // 1 = fp16, 2 = bf16
+  const int32_t* row_offsets;
+  const int32_t* block_indices;
+  float* block_mass;
+  int is_causal;
+  float* lse;
+  const int32_t* key_mask_tiles;
+};
+
+// Capture workspace (FP32 words), identical to the reference's (attention_int8.cuh:58-60,
+// 770-797, 871-895): block masses [B*Hq*n_q, n_k]; then for every query row and every visited tile
+// but the last a pair (u32 probability sum, f32 tile maximum); then per row the last tile's pair
+// (f32 sum, f32 maximum); then per row (final maximum, final denominator).
+struct CaptureLayout {
+  uint32_t* full;
+  float* last;
+  float* state;
+};
+
+__host__ __device__ inline CaptureLayout capture_layout(const AttentionArgs& a, int n_q, int n_k) {
+  const int64_t rows = int64_t(a.batch) * a.q_heads * a.q_len;
+  const int64_t masses = int64_t(a.batch) * a.q_heads * n_q * n_k;
+  CaptureLayout c;
+  c.full = reinterpret_cast<uint32_t*>(a.block_mass + masses);
+  c.last = a.block_mass + masses + rows * (n_k - 1) * 2;
+  c.state = c.last + rows * 2;
+  return c;
+}
+
+#ifdef __CUDACC__
+// Score of (row, key) after the attention mask: kept -> s + bias * log2(e); masked -> -inf.
+// Boolean masks keep where true; additive masks keep where the bias is finite
+// (reference attention_masks.cuh:45-89).
+__device__ __forceinline__ float apply_mask(const AttentionArgs& a, int batch, int head, int row,
+                                            int key, bool row_ok, float s) {
+  bool keep = row_ok && key < a.k_len;
+  float bias = 0.0f;
+  if (keep) {
+    const int64_t off = int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
+                        int64_t(row) * a.mask_stride_q + int64_t(key) * a.mask_stride_k;
+    if (a.mask_dtype_code == 3) {
+      keep = static_cast<const uint8_t*>(a.mask)[off] != 0;
+    } else {
+      if (a.mask_dtype_code == 0)
+        bias = static_cast<const float*>(a.mask)[off];
+      else if (a.mask_dtype_code == 1)
+        bias = __half2float(static_cast<const __half*>(a.mask)[off]);
+      else
+        bias = __bfloat162float(static_cast<const __nv_bfloat16*>(a.mask)[off]);
+      keep = isfinite(bias);
+    }
+  }
+  return keep ? fmaf(s, 1.0f, bias * kLog2e) : -INFINITY;
+}
+
+__device__ __forceinline__ void store_pair(void* p, float a, float b, int out_dtype_code) {
+  if (out_dtype_code == 1) {
+    *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b);
+  } else {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+}
+#endif
+
+// Kernel families (defined in attention_rows.cu / attention_tc.cu).
+int attention_rows(const AttentionArgs& a, cudaStream_t stream);
+bool attention_tc_supported(const AttentionArgs& a);
+int attention_tc(const AttentionArgs& a, cudaStream_t stream);
+
+}  // namespace risa_b200

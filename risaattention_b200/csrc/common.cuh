@@ -1,0 +1,99 @@
+// Shared host/device helpers for the B200 RISA kernels.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/risa_b200.h"
+
+namespace risa_b200 {
+
+// ---- host-side status plumbing -----------------------------------------------------------
+char* error_buffer();  // thread-local, 512 bytes (defined in cabi.cu)
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(error_buffer(), 512, fmt, args);
+  va_end(args);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(RISA_B200_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return RISA_B200_OK;
+}
+
+#define RISA_REQUIRE(cond, ...)                                   \
+  do {                                                            \
+    if (!(cond)) return ::risa_b200::fail(RISA_B200_INVALID, __VA_ARGS__); \
+  } while (0)
+
+// ---- device helpers ----------------------------------------------------------------------
+#ifdef __CUDACC__
+template <typename T> struct Load4;
+template <> struct Load4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* out) {
+    const float4 raw = __ldg(reinterpret_cast<const float4*>(p));
+    out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+  }
+};
+template <> struct Load4<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float* out) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+    out[0] = __low2float(a); out[1] = __high2float(a);
+    out[2] = __low2float(b); out[3] = __high2float(b);
+  }
+};
+template <> struct Load4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+    out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+  }
+};
+
+template <typename T> __device__ __forceinline__ float load_scalar(const T* p) {
+  return static_cast<float>(__ldg(p));
+}
+
+// cvt.rni.sat.s8.f32: round to nearest even, saturate to [-128, 127].
+__device__ __forceinline__ uint32_t to_s8(float x) {
+  int32_t q;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
+  return static_cast<uint32_t>(q) & 0xffu;
+}
+__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
+  return to_s8(a) | (to_s8(b) << 8) | (to_s8(c) << 16) | (to_s8(d) << 24);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+#endif
+
+#define RISA_DISPATCH_FLOAT(code, T, ...)                 \
+  do {                                                    \
+    if ((code) == 0) { using T = float; __VA_ARGS__; }    \
+    else if ((code) == 1) { using T = __half; __VA_ARGS__; } \
+    else { using T = __nv_bfloat16; __VA_ARGS__; }        \
+  } while (0)
+
+}  // namespace risa_b200

@@ -1,0 +1,436 @@
+// Q/K preparation for INT8 attention on B200: K anchor detection, block Hadamard rotation and
+// symmetric INT8 quantisation with FP32 group scales.
+//
+// Behaviour follows the reference project's csrc/kernels/quantize_qk_impl.cuh (anchor :442-577,
+// rotations :69-147, Q groups :153-269, K groups :278-426) so that codes and scales are
+// bit-identical; the kernel organisation is different:
+//   * a lane owns 16 contiguous channels of a row (four vector loads, one 16-byte code store),
+//     so only the three highest Hadamard stages need warp shuffles;
+//   * one CTA quantises a whole 128-row query block or a whole key tile, with the four key scale
+//     groups of the tile spread over its warps, so no lane holds more than 64 values.
+// This file is compiled with --use_fast_math on purpose: the reference's scale arithmetic
+// (x / 127.f, 1.f / x) is defined by that mode's approximate division and reciprocal.
+#include "common.cuh"
+
+namespace risa_b200 {
+namespace {
+
+constexpr int kRotH4 = 4, kRotH64 = 64, kRotSigned128 = 128, kRotPlain128 = 129;
+
+// In-lane H4 on 4 adjacent channels (channel bits 1 and 2), with the 0.5 normalisation.
+__device__ __forceinline__ void h4(float* v) {
+  const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+  v[0] = (a0 + a2) * 0.5f;
+  v[1] = (a1 + a3) * 0.5f;
+  v[2] = (a0 - a2) * 0.5f;
+  v[3] = (a1 - a3) * 0.5f;
+}
+
+// Rotates the 16 channels [16*chunk, 16*chunk+16) held by this lane.  Lanes holding one row's
+// (or one 128-channel tile's) chunks are consecutive, so span 16/32/64 pair lane ^ 1/2/4.
+template <int ROT>
+__device__ __forceinline__ void rotate16(float* v, int chunk) {
+  if constexpr (ROT == kRotSigned128) {
+    constexpr uint32_t kSigns[4] = {0x1035997bu, 0x8087f5eeu, 0xee2e4e1au, 0x71132418u};
+    const uint32_t word = chunk < 2 ? kSigns[0] : chunk < 4 ? kSigns[1] : chunk < 6 ? kSigns[2]
+                                                                                   : kSigns[3];
+    const uint32_t bits = word >> ((chunk & 1) * 16);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t flip = ((bits >> i) & 1u) ^ 1u;
+      v[i] = __uint_as_float(__float_as_uint(v[i]) ^ (flip << 31));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) h4(v + i);
+  if constexpr (ROT == kRotH4) return;
+  // spans 4 and 8 stay inside the lane
+#pragma unroll
+  for (int span = 4; span <= 8; span <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & span) == 0) {
+        const float lo = v[i], hi = v[i + span];
+        v[i] = lo + hi;
+        v[i + span] = lo - hi;
+      }
+    }
+  }
+  constexpr int kLaneStages = ROT == kRotH64 ? 2 : 3;  // spans 16,32 (,64)
+#pragma unroll
+  for (int s = 0; s < kLaneStages; ++s) {
+    const int bit = 1 << s;
+    const bool upper = (chunk & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], bit);
+      v[i] = upper ? other - v[i] : v[i] + other;
+    }
+  }
+  constexpr float kNorm = ROT == kRotH64 ? 0.25f : 0.1767766952966369f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] *= kNorm;
+}
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) Load4<T>::load(p + 4 * i, v + 4 * i);
+}
+
+__device__ __forceinline__ float absmax16(const float* v) {
+  float mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(v[i]));
+  return mx;
+}
+
+__device__ __forceinline__ void store16_codes(int8_t* p, const float* v, float inv) {
+  uint4 w;
+  w.x = pack4_s8(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+  w.y = pack4_s8(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+  w.z = pack4_s8(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
+  w.w = pack4_s8(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
+  *reinterpret_cast<uint4*>(p) = w;
+}
+
+// ------------------------------------------------------------------------------------------
+// Q: one CTA per (128-row block, head, batch).  A scale group is 4 rows {r, r+8, r+16, r+24} of a
+// 32-row tile (D <= 128) or 2 rows {r, r+8} of a 16-row tile (D = 256), times all channels.
+// ------------------------------------------------------------------------------------------
+template <typename T, int D, int ROT>
+__global__ __launch_bounds__(256) void quantize_q_kernel(
+    const T* __restrict__ q, int8_t* __restrict__ codes, float* __restrict__ scales, int q_len,
+    int q_heads, int scales_per_head, int64_t stride_b, int64_t stride_h, int64_t stride_n,
+    const int32_t* __restrict__ perm) {
+  constexpr int LPR = D / 16;                       // lanes per row
+  constexpr int GROUP_ROWS = D == 256 ? 2 : 4;      // rows per scale group
+  constexpr int GLANES = GROUP_ROWS * LPR;          // lanes per group (16 or 32)
+  constexpr int GPP = 32 / GLANES;                  // groups per warp pass
+  constexpr int TILE_ROWS = D == 256 ? 16 : 32;     // rows sharing one set of 8 groups
+  constexpr int GROUPS = 128 / GROUP_ROWS;          // groups per 128-row block
+  constexpr int PASSES = GROUPS / GPP / 8;          // passes per warp (8 warps)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const T* in = q + b * stride_b + h * stride_h;
+  const int64_t bh = static_cast<int64_t>(b) * q_heads + h;
+  int8_t* out = codes + bh * q_len * D;
+  float* sc_out = scales + bh * scales_per_head + blk * (GROUPS);
+  const int32_t* row_map = perm ? perm + bh * q_len : nullptr;
+
+  const int slot = lane / GLANES;           // which group of the pass
+  const int j = (lane % GLANES) / LPR;      // row inside the group
+  const int chunk = lane % LPR;             // 16-channel chunk inside the row
+
+  float v[PASSES][16];
+  int rows[PASSES];
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int group = (warp * PASSES + p) * GPP + slot;  // 0..GROUPS-1 == tile*8 + o
+    const int row = blk * 128 + (group >> 3) * TILE_ROWS + (group & 7) + 8 * j;
+    rows[p] = row;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[p][i] = 0.f;
+    if (row < q_len) {
+      const int64_t src = row_map ? __ldg(row_map + row) : row;
+      load16(in + src * stride_n + chunk * 16, v[p]);
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    rotate16<ROT>(v[p], D == 256 ? (chunk & 7) : chunk);
+    float mx = absmax16(v[p]);
+#pragma unroll
+    for (int off = GLANES / 2; off > 0; off >>= 1)
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const float sc = mx / 127.f + 1e-7f;
+    const float inv = 1.f / sc;
+    const int group = (warp * PASSES + p) * GPP + slot;
+    if ((lane % GLANES) == 0) sc_out[group] = sc;
+    if (rows[p] < q_len) store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// K: one CTA per (key tile, kv head, batch).  Scale group w of a tile = rows with (n % 8) / 2 == w.
+// Warp (w, s) takes a contiguous share of group w's rows; groups spanning several warps combine
+// their maxima through shared memory.
+// ------------------------------------------------------------------------------------------
+constexpr int k_threads(int d, int cta_k) { return d * cta_k / 64 < 128 ? 128 : d * cta_k / 64; }
+
+template <typename T, int D, int CTA_K, int ROT>
+__global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
+    const T* __restrict__ k, int8_t* __restrict__ codes, float* __restrict__ scales,
+    const int32_t* __restrict__ anchors, int k_len, int kv_heads, int scales_per_head,
+    int64_t stride_b, int64_t stride_h, int64_t stride_n, const int32_t* __restrict__ perm) {
+  constexpr int LPR = D / 16;
+  constexpr int RPP = 32 / LPR;                 // rows per warp pass
+  constexpr int THREADS = k_threads(D, CTA_K);  // at most 64 values per lane
+  constexpr int NW = THREADS / 128;             // warps per scale group (>= 1 except D64)
+  constexpr int WPG = NW < 1 ? 1 : NW;
+  constexpr int GROUP_ROWS = CTA_K / 4;
+  constexpr int RW = GROUP_ROWS / WPG;          // rows per warp
+  constexpr int PASSES = RW / RPP;
+  static_assert(PASSES >= 1 && PASSES * RPP == RW, "tile geometry");
+  __shared__ float warp_max[4][WPG];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w = warp % 4, s = warp / 4;
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const T* in = k + b * stride_b + h * stride_h;
+  const int64_t bh = static_cast<int64_t>(b) * kv_heads + h;
+  int8_t* out = codes + bh * k_len * D;
+  const int32_t* row_map = perm ? perm + bh * k_len : nullptr;
+  const int jr = lane / LPR, chunk = lane % LPR;
+
+  float bias[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bias[i] = 0.f;
+  const int anchor = __ldg(anchors + bh);
+  if (anchor >= 0) {
+    const int64_t src = row_map ? __ldg(row_map + anchor) : anchor;
+    load16(in + src * stride_n + chunk * 16, bias);
+  }
+
+  float v[PASSES][16];
+  int rows[PASSES];
+  float mx = 0.f;
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int i = s * RW + p * RPP + jr;  // index inside the group's row list
+    const int row = tile * CTA_K + 8 * (i >> 1) + 2 * w + (i & 1);
+    rows[p] = row;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) v[p][c] = 0.f;
+    if (row < k_len) {
+      const int64_t src = row_map ? __ldg(row_map + row) : row;
+      load16(in + src * stride_n + chunk * 16, v[p]);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) v[p][c] -= bias[c];
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    rotate16<ROT>(v[p], D == 256 ? (chunk & 7) : chunk);
+    mx = fmaxf(mx, absmax16(v[p]));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if constexpr (WPG > 1) {
+    if (lane == 0) warp_max[w][s] = mx;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < WPG; ++i) mx = fmaxf(mx, warp_max[w][i]);
+  }
+  const float sc = mx / 127.f + 1e-7f;
+  const float inv = 1.f / sc;
+  if (s == 0 && lane == 0) scales[bh * scales_per_head + tile * 4 + w] = sc;
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p)
+    if (rows[p] < k_len)
+      store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
+}
+
+// ------------------------------------------------------------------------------------------
+// K anchor detector: nine evenly spaced keys per (batch, kv head); the candidate minimising the
+// summed squared distance to the others becomes the anchor if it lowers the sampled energy without
+// raising the sampled absmax by more than 12.5 %.  The FP32 reduction shape (thread t owns
+// channels t and t+128, shfl_down tree, warps added 0..3) decides borderline cases and is kept.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ __launch_bounds__(128) void detect_anchor_kernel(const T* __restrict__ k,
+                                                            int32_t* __restrict__ anchors,
+                                                            int k_len, int head_dim, int kv_heads,
+                                                            int64_t stride_b, int64_t stride_h,
+                                                            int64_t stride_n,
+                                                            const int32_t* __restrict__ perm) {
+  constexpr int S = 9;
+  __shared__ float smp[S * 256];
+  __shared__ float w_energy[4], w_max[4], w_dist[S][4], w_benergy[4], w_bmax[4];
+  __shared__ int chosen;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int64_t bh = static_cast<int64_t>(b) * kv_heads + h;
+  const T* in = k + b * stride_b + h * stride_h;
+  const int32_t* row_map = perm ? perm + bh * k_len : nullptr;
+  for (int idx = tid; idx < S * head_dim; idx += 128) {
+    const int sample = idx / head_dim, channel = idx - sample * head_dim;
+    const int row = sample * (k_len - 1) / (S - 1);
+    const int64_t src = row_map ? __ldg(row_map + row) : row;
+    smp[idx] = load_scalar(in + src * stride_n + channel);
+  }
+  __syncthreads();
+  float energy = 0.f, vmax = 0.f, dist[S];
+#pragma unroll
+  for (int c = 0; c < S; ++c) dist[c] = 0.f;
+  for (int channel = tid; channel < head_dim; channel += 128) {
+    float sum = 0.f;
+#pragma unroll
+    for (int sidx = 0; sidx < S; ++sidx) {
+      const float x = smp[sidx * head_dim + channel];
+      energy = fmaf(x, x, energy);
+      vmax = fmaxf(vmax, fabsf(x));
+      sum += x;
+    }
+#pragma unroll
+    for (int c = 0; c < S; ++c) {
+      const float dd = S * smp[c * head_dim + channel] - sum;
+      dist[c] = fmaf(dd, dd, dist[c]);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    energy += __shfl_down_sync(0xffffffffu, energy, off);
+    vmax = fmaxf(vmax, __shfl_down_sync(0xffffffffu, vmax, off));
+#pragma unroll
+    for (int c = 0; c < S; ++c) dist[c] += __shfl_down_sync(0xffffffffu, dist[c], off);
+  }
+  if (lane == 0) {
+    w_energy[warp] = energy;
+    w_max[warp] = vmax;
+#pragma unroll
+    for (int c = 0; c < S; ++c) w_dist[c][warp] = dist[c];
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int best = 0;
+    float best_d = 3.402823466e+38F;
+#pragma unroll
+    for (int c = 0; c < S; ++c) {
+      float dsum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dsum += w_dist[c][i];
+      if (dsum < best_d) {
+        best = c;
+        best_d = dsum;
+      }
+    }
+    chosen = best;
+  }
+  __syncthreads();
+  float benergy = 0.f, bmax = 0.f;
+  for (int channel = tid; channel < head_dim; channel += 128) {
+    const float a = smp[chosen * head_dim + channel];
+#pragma unroll
+    for (int sidx = 0; sidx < S; ++sidx) {
+      const float r = smp[sidx * head_dim + channel] - a;
+      benergy = fmaf(r, r, benergy);
+      bmax = fmaxf(bmax, fabsf(r));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    benergy += __shfl_down_sync(0xffffffffu, benergy, off);
+    bmax = fmaxf(bmax, __shfl_down_sync(0xffffffffu, bmax, off));
+  }
+  if (lane == 0) {
+    w_benergy[warp] = benergy;
+    w_bmax[warp] = bmax;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float te = 0.f, tm = 0.f, be = 0.f, bm = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      te += w_energy[i];
+      tm = fmaxf(tm, w_max[i]);
+      be += w_benergy[i];
+      bm = fmaxf(bm, w_bmax[i]);
+    }
+    const bool improves = be < te && bm <= tm * 1.125f;
+    anchors[bh] = improves ? chosen * (k_len - 1) / (S - 1) : -1;
+  }
+}
+
+template <typename T, int D, int ROT>
+void launch_q(const void* q, void* codes, float* scales, int batch, int heads, int q_len,
+              int64_t sb, int64_t sh, int64_t sn, const int32_t* perm, cudaStream_t stream) {
+  const int blocks = (q_len + 127) / 128;
+  const int per_head = blocks * (D == 256 ? 64 : 32);
+  quantize_q_kernel<T, D, ROT><<<dim3(blocks, heads, batch), 256, 0, stream>>>(
+      static_cast<const T*>(q), static_cast<int8_t*>(codes), scales, q_len, heads, per_head, sb,
+      sh, sn, perm);
+}
+
+template <typename T, int D, int CTA_K, int ROT>
+void launch_k(const void* k, void* codes, float* scales, const int32_t* anchors, int batch,
+              int heads, int k_len, int64_t sb, int64_t sh, int64_t sn, const int32_t* perm,
+              cudaStream_t stream) {
+  const int tiles = (k_len + CTA_K - 1) / CTA_K;
+  quantize_k_kernel<T, D, CTA_K, ROT><<<dim3(tiles, heads, batch), k_threads(D, CTA_K), 0, stream>>>(
+      static_cast<const T*>(k), static_cast<int8_t*>(codes), scales, anchors, k_len, heads,
+      tiles * 4, sb, sh, sn, perm);
+}
+
+template <typename T, int D, int ROT>
+void launch_qk(const void* q, void* qc, float* qs, const void* k, void* kc, float* ks,
+               const int32_t* anchors, int batch, int hq, int lq, int hkv, int lk, int cta_k,
+               const int64_t* st, const int32_t* qperm, const int32_t* kperm,
+               cudaStream_t stream) {
+  launch_q<T, D, ROT>(q, qc, qs, batch, hq, lq, st[0], st[1], st[2], qperm, stream);
+  if constexpr (D == 64) {
+    launch_k<T, D, 64, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm, stream);
+  } else {
+    if (cta_k == 128)
+      launch_k<T, D, 128, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm,
+                               stream);
+    else
+      launch_k<T, D, 64, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm,
+                              stream);
+  }
+}
+
+}  // namespace
+}  // namespace risa_b200
+
+using namespace risa_b200;
+
+extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scale, const void* k,
+                                     void* k_codes, float* k_scale, int batch, int q_heads,
+                                     int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
+                                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                     int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                     int dtype_code, int32_t* anchors, const int32_t* q_perm,
+                                     const int32_t* k_perm, void* stream_ptr) {
+  RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
+               "quantize_qk: padded head_dim must be 64, 128, or 256");
+  RISA_REQUIRE((cta_k == 64 || cta_k == 128) && !(head_dim == 64 && cta_k != 64),
+               "quantize_qk: unsupported key tile %d for head_dim %d", cta_k, head_dim);
+  RISA_REQUIRE(q && q_codes && q_scale && k && k_codes && k_scale, "quantize_qk: null tensor");
+  RISA_REQUIRE(anchors != nullptr, "quantize_qk: anchor_indices scratch is required");
+  RISA_REQUIRE(dtype_code >= 0 && dtype_code <= 2, "quantize_qk: dtype code must be 0, 1 or 2");
+  RISA_REQUIRE(batch > 0 && q_heads > 0 && kv_heads > 0 && q_len > 0 && k_len > 0,
+               "quantize_qk: sizes must be positive");
+  const size_t vec = 4 * (dtype_code == 0 ? 4 : 2);
+  auto stride_ok = [](int64_t stride, int extent) {
+    return extent < 2 || (stride > 0 && stride % 4 == 0);
+  };
+  RISA_REQUIRE(reinterpret_cast<uintptr_t>(q) % vec == 0 && stride_ok(q_stride_b, batch) &&
+                   stride_ok(q_stride_h, q_heads) && stride_ok(q_stride_n, q_len) &&
+                   reinterpret_cast<uintptr_t>(k) % vec == 0 && stride_ok(k_stride_b, batch) &&
+                   stride_ok(k_stride_h, kv_heads) && stride_ok(k_stride_n, k_len),
+               "quantize_qk: Q/K base pointers and batch/head/sequence strides must preserve "
+               "4-element alignment");
+  RISA_REQUIRE(reinterpret_cast<uintptr_t>(q_codes) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(k_codes) % 16 == 0,
+               "quantize_qk: code buffers must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int64_t st[6] = {q_stride_b, q_stride_h, q_stride_n, k_stride_b, k_stride_h, k_stride_n};
+#define RISA_QK(D, ROT)                                                                       \
+  launch_qk<T, D, ROT>(q, q_codes, q_scale, k, k_codes, k_scale, anchors, batch, q_heads, q_len, \
+                       kv_heads, k_len, cta_k, st, q_perm, k_perm, stream)
+  const bool h4_only = k_len <= 256;
+  RISA_DISPATCH_FLOAT(dtype_code, T, {
+    detect_anchor_kernel<T><<<dim3(kv_heads, batch), 128, 0, stream>>>(
+        static_cast<const T*>(k), anchors, k_len, head_dim, kv_heads, k_stride_b, k_stride_h,
+        k_stride_n, k_perm);
+    if (head_dim == 64) {
+      if (h4_only) RISA_QK(64, kRotH4); else RISA_QK(64, kRotH64);
+    } else if (head_dim == 128) {
+      if (h4_only) RISA_QK(128, kRotH4); else RISA_QK(128, kRotSigned128);
+    } else {
+      if (h4_only) RISA_QK(256, kRotH4); else RISA_QK(256, kRotPlain128);
+    }
+  });
+#undef RISA_QK
+  return check_launch("quantize_qk");
+}

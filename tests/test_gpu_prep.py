@@ -1,0 +1,131 @@
+"""Q/K/V preparation kernels against the reference's own kernels: every code, scale, anchor and
+centre must be bit-identical."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests.util import qkv  # noqa: E402
+
+
+def _ours(q, k, v, cta_k, affine):
+    from risaattention_b200 import _backend
+    from risaattention_b200._quantization import PackedBuffers, quantize_into
+
+    buf = PackedBuffers(q, k, cta_k)
+    quantize_into(buf, q, k, v, cta_k, affine)
+    return buf
+
+
+CASES = [
+    # d, lq, lk, cta_k, hq, hkv
+    (64, 137, 200, 64, 4, 2),      # H4 rotation (Lk <= 256), partial blocks
+    (64, 300, 1025, 64, 4, 4),     # H64
+    (128, 137, 263, 64, 2, 1),     # signed H128, 64-key tiles
+    (128, 257, 1153, 128, 4, 2),   # 128-key tiles, ragged tail
+    (128, 1024, 2048, 128, 8, 2),
+    (256, 137, 263, 64, 2, 1),     # plain H128 per half
+    (256, 200, 1153, 128, 4, 2),
+    (128, 100, 100, 64, 2, 2),     # H4 with D128
+    (256, 33, 64, 64, 2, 1),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("anchor", [False, True])
+def test_prep_bit_exact(ref, dtype, case, anchor):
+    d, lq, lk, cta_k, hq, hkv = case
+    for affine in (False, True):
+        q, k, v = qkv(2, hq, hkv, lq, lk, d, dtype, seed=lq + lk, anchor=anchor)
+        v = v + 1.5
+        got = _ours(q, k, v, cta_k, affine)
+        want = ref.prequantize(q, k, v, cta_k=cta_k, midpoint_affine=affine)
+        torch.cuda.synchronize()
+        assert torch.equal(got.anchors, want["anchors"])
+        if anchor:
+            assert (want["anchors"] >= 0).any(), "test data was meant to trigger the anchor"
+        assert torch.equal(got.q_codes, want["q"])
+        assert torch.equal(got.k_codes, want["k"])
+        assert torch.equal(got.q_scales, want["q_scale"])
+        assert torch.equal(got.k_scales, want["k_scale"])
+        assert torch.equal(got.v_codes, want["v"])
+        assert torch.equal(got.v_scales, want["v_scale"])
+        assert torch.equal(got.v_centers, want["v_center"]), "v_center must match bit for bit"
+
+
+@pytest.mark.parametrize("layout", ["nhd"])
+def test_prep_strided_inputs(ref, layout):
+    q, k, v = qkv(2, 4, 2, 300, 1500, 128, torch.bfloat16, seed=5, layout=layout)
+    got = _ours(q, k, v, 128, True)
+    want = ref.prequantize(q, k, v, cta_k=128, midpoint_affine=True)
+    for a, b in ((got.q_codes, want["q"]), (got.k_codes, want["k"]), (got.v_codes, want["v"]),
+                 (got.v_centers, want["v_center"]), (got.q_scales, want["q_scale"])):
+        assert torch.equal(a, b)
+
+
+def test_prep_against_cpu_oracle():
+    """Second opinion: the CPU restatement agrees up to its documented budget (approximate
+    division / reciprocal cannot be reproduced on a CPU): codes differ by at most 1, rarely."""
+    from oracle import risa_oracle as O
+
+    q, k, v = qkv(1, 4, 2, 300, 1153, 128, torch.bfloat16, seed=3)
+    got = _ours(q, k, v, 128, True)
+    anchors = O.detect_k_anchor(k.float().cpu())
+    assert torch.equal(anchors, got.anchors.cpu())
+    qc, qs = O.quantize_q(q.float().cpu(), 1153)
+    kc, ks = O.quantize_k(k.float().cpu(), 128, anchors)
+    vc, vs, vcen = O.quantize_v(v.float().cpu(), 128, True)
+    for mine, oracle in ((got.q_codes, qc), (got.k_codes, kc), (got.v_codes, vc)):
+        diff = (mine.cpu().int() - oracle.int()).abs()
+        assert diff.max() <= 1 and (diff > 0).float().mean() < 2e-3
+    torch.testing.assert_close(got.q_scales.cpu(), qs, rtol=1e-6, atol=0)
+    torch.testing.assert_close(got.k_scales.cpu(), ks, rtol=1e-6, atol=0)
+    torch.testing.assert_close(got.v_scales.cpu(), vs, rtol=1e-6, atol=0)
+    torch.testing.assert_close(got.v_centers.cpu(), vcen, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("length", [1025, 2048, 2049, 4097])
+def test_absmax_values_known_answer(dtype, length):
+    """Power-of-two data make codes and scales independent of rounding (the reference's own
+    known-answer test, tests/cuda/test_value_quantization.py:18-52)."""
+    import risaattention_b200 as risa
+
+    batch, heads, channels = 2, 3, 128
+    tokens = torch.arange(length, device="cuda")[None, None, :, None]
+    offs = torch.arange(batch * heads, device="cuda").reshape(batch, heads, 1, 1)
+    codes = ((tokens + offs) % 255 - 127).expand(batch, heads, length, channels)
+    scales = 2.0 ** ((torch.arange(channels, device="cuda") % 4).float() - 2)
+    v = (codes * scales).to(dtype)
+    q = torch.zeros(batch, heads * 2, 3, channels, device="cuda", dtype=dtype)
+    packed = risa.prequantize_int8_attention(q, torch.zeros_like(v), v, v_quantization="absmax")
+    padded = packed.v.shape[-1]
+    expected = torch.zeros(batch, heads, channels, padded, device="cuda", dtype=torch.int8)
+    expected[..., :length] = codes.transpose(2, 3).to(torch.int8)
+    order = torch.tensor([0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15], device="cuda")
+    expected = expected.reshape(batch, heads, channels, -1, 16)[..., order]
+    assert torch.equal(packed.v.reshape_as(expected), expected)
+    assert torch.equal(packed.v_scale.reshape(batch, heads, channels),
+                       scales.expand(batch, heads, channels))
+    assert torch.count_nonzero(packed.v_center) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("dim", [64, 128, 256])
+def test_lse_shift(ref, dtype, dim):
+    from risaattention_b200 import _backend
+
+    torch.manual_seed(35)
+    q = torch.randn(2, 17, 4, dim, device="cuda", dtype=dtype).transpose(1, 2)
+    k = torch.randn(2, 9, 2, dim, device="cuda", dtype=dtype).transpose(1, 2)
+    anchors = torch.tensor([[-1, 0], [3, 2]], device="cuda", dtype=torch.int32)
+    out = torch.empty(2, 4, 17, device="cuda")
+    _backend._C.risa_lse_shift(q, k, anchors, out, dim ** -0.5,
+                               torch.cuda.current_stream().cuda_stream)
+    assert torch.equal(out, ref.lse_shift(q, k, anchors, dim ** -0.5))
+    sel = k.gather(2, anchors.clamp_min(0).long()[..., None, None].expand(2, 2, 1, dim))
+    sel = sel.float() * (anchors >= 0)[..., None, None]
+    expect = (q.float() * sel.repeat_interleave(2, 1)).sum(-1) * dim ** -0.5
+    torch.testing.assert_close(out, expect, rtol=2e-5, atol=5e-6)
+    assert torch.count_nonzero(out[0, :2]) == 0
