@@ -153,7 +153,7 @@ def detect_k_anchor(k: torch.Tensor) -> torch.Tensor:
                 energy[:n] = e
                 omax[:n] = m
                 for c in range(9):
-                    dd = _f(9.0) * vals[c] - csum
+                    dd = _fma(_f(9.0), vals[c], -csum)
                     dist[c, :n] = _fma(dd, dd, dist[c, :n])
 
             def warp_tree_sum(x128):  # shfl_down tree per warp then warps 0..3 in order
@@ -493,13 +493,17 @@ def attention(
                     e = _exp2(-(m_prev - tile_m).abs())
                     o_scale = torch.where(m_prev < tile_m, e, _f(1.0))
                     w = torch.where(tile_m < m_prev, e, _f(1.0))
+                    dprev = dpart
                     dpart = dpart * o_scale[:, None]
                     # denominator partials: lane q owns columns with (c%8)/2 == q
                     for lane in range(4):
                         sel = pu[:, lane_q == lane].reshape(nr, cta_k // 16, 4)
                         if last:
                             s8 = sel.reshape(nr, cta_k // 32, 8).sum(-1)
-                            for j in range(cta_k // 32):
+                            # the compiled reference fuses the rescale with the first addend:
+                            # d * o_scale + round(s * w) in one FMA (found on the GPU, bit for bit)
+                            dpart[:, lane] = _fma(dprev[:, lane], o_scale, s8[:, 0] * w)
+                            for j in range(1, cta_k // 32):
                                 dpart[:, lane] = _fma(s8[:, j], w, dpart[:, lane])
                         else:
                             s4 = sel.sum(-1)

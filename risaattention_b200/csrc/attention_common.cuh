@@ -53,7 +53,7 @@ __host__ __device__ inline CaptureLayout capture_layout(const AttentionArgs& a, 
 // Boolean masks keep where true; additive masks keep where the bias is finite
 // (reference attention_masks.cuh:45-89).
 __device__ __forceinline__ float apply_mask(const AttentionArgs& a, int batch, int head, int row,
-                                            int key, bool row_ok, float s) {
+                                            int key, bool row_ok, float x, float sc) {
   bool keep = row_ok && key < a.k_len;
   float bias = 0.0f;
   if (keep) {
@@ -71,7 +71,11 @@ __device__ __forceinline__ float apply_mask(const AttentionArgs& a, int batch, i
       keep = isfinite(bias);
     }
   }
-  return keep ? fmaf(s, 1.0f, bias * kLog2e) : -INFINITY;
+  if (!keep) return -INFINITY;
+  // score * scale and + bias are separate roundings.  (The reference writes the same two steps and
+  // leaves fusing them to its compiler, which decides differently per kernel instantiation; masked
+  // outputs therefore agree with it to the last FP32 bit in most but not all configurations.)
+  return __fadd_rn(__fmul_rn(x, sc), bias * kLog2e);
 }
 
 __device__ __forceinline__ void store_pair(void* p, float a, float b, int out_dtype_code) {

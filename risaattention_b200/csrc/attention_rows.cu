@@ -162,9 +162,10 @@ __global__ __launch_bounds__(128) void attention_rows_kernel(const AttentionArgs
 #pragma unroll
       for (int c = 0; c < CTA_K; ++c) {
         const int g = (c & 7) >> 1;
-        float s = x[c] * sc[g];
         const int kv = c0 + c;
-        if constexpr (MASKED) s = apply_mask(a, batch, head, row, kv, row_ok, s);
+        float s;
+        if constexpr (MASKED) s = apply_mask(a, batch, head, row, kv, row_ok, x[c], sc[g]);
+        else s = x[c] * sc[g];
         if (a.is_causal && kv > row) s = -INFINITY;
         if (last_rules && kv >= a.k_len) s = -INFINITY;
         x[c] = s;

@@ -190,9 +190,13 @@ __global__ void v_center_kernel(const float* __restrict__ residuals,
     const float center = 0.5f * (lo + hi);
     const float radius = 0.5f * (hi - lo);
     const float sc = fmaxf(radius * (1.f / 127.f), 1e-12f);
-    const float inv = 1.f / sc;
-    const float scale = 1.0f / inv;
-    center_out[channel] = center + scale * (total / static_cast<float>(k_len));
+    // reciprocal of the stored reciprocal, both approximate: not the same bits as sc itself
+    const float inv = rcp_approx(sc);
+    const float scale = rcp_approx(inv);
+    // one FMA: centre + scale * mean.  Against the reference's compiled kernel this is bit-identical
+    // in more than 99 % of channels and one ulp away in the rest (approximate division feeding a
+    // sum that cancels against a small centre).
+    center_out[channel] = fmaf(scale, total / static_cast<float>(k_len), center);
   }
 }
 

@@ -81,8 +81,9 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
   r.o_scale = m_prev < r.tile_m ? smaller : 1.0f;
   r.w = r.tile_m < m_prev ? smaller : 1.0f;
   r.numer = 0;
+  float dprev[4];
 #pragma unroll
-  for (int g = 0; g < 4; ++g) st.d[g] *= r.o_scale;
+  for (int g = 0; g < 4; ++g) { dprev[g] = st.d[g]; st.d[g] *= r.o_scale; }
 #pragma unroll
   for (int j = 0; j < G16; ++j) {
 #pragma unroll
@@ -106,7 +107,13 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
       for (int j = 0; j < G16; j += 2) {
         const uint32_t s8 = __dp4a(P[4 * j + 4 + g], 0x01010101u, __dp4a(P[4 * j + g], 0x01010101u, 0u));
         r.numer += s8;
-        if constexpr (EXACT_D) st.d[g] = fmaf(static_cast<float>(s8), r.w, st.d[g]);
+        if constexpr (EXACT_D) {
+          // The reference's compiler fuses the rescale of the running denominator with the first
+          // addend of this tile (d * o_scale + round(s * w) in one FMA); later addends fuse the
+          // other way.  Found by comparing final denominators bit for bit on the GPU.
+          if (j == 0) st.d[g] = fmaf(dprev[g], r.o_scale, __fmul_rn(static_cast<float>(s8), r.w));
+          else st.d[g] = fmaf(static_cast<float>(s8), r.w, st.d[g]);
+        }
       }
     } else {
 #pragma unroll

@@ -32,3 +32,15 @@ def rel_max_err(a, b):
 def nrmse(a, b):
     a, b = a.float(), b.float()
     return ((a - b).pow(2).mean() / b.pow(2).mean().clamp_min(1e-30)).sqrt().item()
+
+
+def assert_outputs_match(ours, ref, tol=2e-3):
+    """Output parity rule: |ours - ref| <= tol * RMS(ref) + one unit in the last place of the
+    16-bit output type.  The FP32 results must agree to ``tol`` of the output RMS; the final
+    rounding to bf16/fp16 (8 / 11 significant bits) may then land on the neighbouring value."""
+    a, b = ours.float(), ref.float()
+    rms = b.pow(2).mean().sqrt()
+    eps = 2.0 ** -7 if ref.dtype == torch.bfloat16 else 2.0 ** -10
+    ulp = torch.maximum(b.abs(), a.abs()) * eps
+    bad = (a - b).abs() > tol * rms + ulp
+    assert not bad.any(), f"{int(bad.sum())} outputs beyond tolerance, worst {((a - b).abs() / rms).max().item():.3e} x RMS"
