@@ -79,6 +79,12 @@ int risa_b200_attention(const void* q, const void* k, const void* v, void* o, co
  * the two).  Process-wide; returns the previous value. */
 int risa_b200_set_attention_path(int path);
 
+/* Reads (and clears) the device status word of the tensor-core attention kernel.  Every wait inside
+ * that kernel is bounded; if one expires the kernel records where, drains and exits, and this call
+ * returns RISA_B200_DEVICE with the site in risa_b200_last_error().  Synchronises the device.  No
+ * counterpart in the reference, whose kernels have no waits that can expire. */
+int risa_b200_device_status(void);
+
 /* Retained-mass prefix selection over descending-sorted block masses and CSR packing.  Replaces
  * launch_select_retained_mass + retained_mass_selector_workspace_size (csrc/launchers.h:61-67;
  * csrc/kernels/sparse_selection.cu:9-159).  summary receives {selected mass, total mass, number of

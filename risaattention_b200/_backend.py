@@ -33,6 +33,7 @@ _SIGNATURES = {
         [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
                                                                    c_i32, c_vp, c_vp, c_vp]),
     "risa_b200_set_attention_path": (c_i32, [c_i32]),
+    "risa_b200_device_status": (c_i32, []),
     "risa_b200_selector_workspace_size": (c_sz, [c_i32]),
     "risa_b200_select_retained_mass": (
         c_i32, [c_vp] * 9 + [c_sz, c_i32, c_i32, c_f64, c_vp]),
@@ -156,6 +157,10 @@ class _Native:
             _ptr(q), _ptr(k), _ptr(anchors), _ptr(out), b, hq, k.shape[1], lq, d, q.stride(0),
             q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), scale,
             DTYPE_CODES[q.dtype], stream_ptr))
+
+    def device_status(self) -> None:
+        """Raises if the tensor-core kernel recorded an expired wait (synchronises the device)."""
+        self._check(self.lib.risa_b200_device_status())
 
     def set_attention_path(self, path: int) -> int:
         return int(self.lib.risa_b200_set_attention_path(path))

@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 (OBJ / f"{unit}.ptxas.log").write_text(log)
     if rebuilt or not LIB.exists():
         objs = [str(OBJ / f"{u}.o") for u in UNITS]
-        subprocess.run(["nvcc", "-shared", "-o", str(LIB), *objs, "-lcudart", "-lcuda"], check=True)
+        subprocess.run(["nvcc", "-shared", "-o", str(LIB), *objs, "-lcudart"], check=True)
     return LIB
 
 

@@ -10,6 +10,9 @@
 // lanes".  The probability bytes of virtual lane g inside 16-key group j are exactly storage bytes
 // 4g..4g+3 of that group in the packed V order {0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15}, so the
 // packed word P[4j+g] is both the MMA operand word and the lane's four-probability sum operand.
+//
+// The tile is processed in chunks of 32 key columns (two 16-key groups) in two passes -- maxima,
+// then exponentials -- so a thread never needs more than one chunk of scores in registers.
 #pragma once
 #include "common.cuh"
 
@@ -39,53 +42,82 @@ __device__ __forceinline__ uint32_t to_u8(float p) {
   return q;
 }
 
-// Column of virtual lane g, 16-key group j, element e (0..3).
+// Column (inside a 32-key chunk) of virtual lane g, 16-key group j (0/1), element e (0..3).
 __device__ __forceinline__ constexpr int lane_column(int j, int g, int e) {
   return 16 * j + 2 * g + (e & 1) + 8 * (e >> 1);
 }
 
-struct TileResult {
-  float tile_m;    // tile maximum (log2 domain, offset included)
-  float o_scale;   // factor for the running output / denominator
-  float w;         // weight of this tile's integer products
-  uint32_t numer;  // sum of the tile's U8 probabilities
+struct TileMax {
+  float g[4];
 };
 
-// x: scores of the tile as floats; for kScoresInt they are exact integers (tail keys already
-// replaced by -1e30 in the last tile), for kScoresScaled they are already in the log2 domain with
-// masked entries at -inf.  sc: per virtual lane scale (unused for kScoresScaled).  LAST selects the
-// reference's generic last-visited-tile arithmetic: lane maxima start at -50000 and the
-// denominator takes one FMA per pair of 16-key groups.  P receives CTA_K/4 packed words in storage
-// order.  When EXACT_D is false the denominator is kept as a single partial (d[0]); outputs then
-// agree with the reference to rounding, not bit for bit.
-template <int CTA_K, int KIND, bool LAST, bool EXACT_D>
-__device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], const float (&sc)[4],
-                                                   RowState& st, uint32_t (&P)[CTA_K / 4]) {
-  constexpr int G16 = CTA_K / 16;
-  float gmax[4];
+// LAST selects the reference's generic last-visited-tile arithmetic: lane maxima start at -50000
+// (as they always do for pre-scaled scores) instead of being unbounded below.
+template <int KIND, bool LAST>
+__device__ __forceinline__ void tile_max_init(TileMax& t) {
+  const float init = (KIND == kScoresInt && !LAST) ? -3.0e38f : -50000.0f;
+  t.g[0] = t.g[1] = t.g[2] = t.g[3] = init;
+}
+
+// x: 32 consecutive key columns starting at a multiple of 32.  For kScoresInt they are exact
+// integers (tail keys already replaced by -1e30 in the last tile), for kScoresScaled they are in
+// the log2 domain with masked entries at -inf.
+__device__ __forceinline__ void tile_max_chunk(const float* x, TileMax& t) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) t.g[g] = fmaxf(t.g[g], x[lane_column(j, g, e)]);
+}
+
+// Tile maximum in the log2 domain, U8 offset included.  sc: per virtual lane score scale.
+template <int KIND>
+__device__ __forceinline__ float tile_max_finish(const TileMax& t, const float (&sc)[4]) {
+  float v[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    v[g] = KIND == kScoresScaled ? t.g[g] - kU8Offset : fmaf(t.g[g], sc[g], -kU8Offset);
+  return fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+}
+
+struct TileScales {
+  float tile_m;    // tile maximum
+  float o_scale;   // factor for the running output / denominator
+  float w;         // weight of this tile's integer products
+  float dprev[4];  // denominator partials before rescaling (first addend of the last tile)
+};
+
+__device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
+  TileScales s;
+  s.tile_m = tile_m;
+  const float m_prev = st.m;
+  st.m = fmaxf(m_prev, tile_m);
+  const float smaller = ex2_approx(-fabsf(m_prev - tile_m));
+  s.o_scale = m_prev < tile_m ? smaller : 1.0f;
+  s.w = tile_m < m_prev ? smaller : 1.0f;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    float mx = (KIND == kScoresInt && !LAST) ? -3.0e38f : -50000.0f;
-#pragma unroll
-    for (int j = 0; j < G16; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) mx = fmaxf(mx, x[lane_column(j, g, e)]);
-    gmax[g] = KIND == kScoresScaled ? mx - kU8Offset : fmaf(mx, sc[g], -kU8Offset);
+    s.dprev[g] = st.d[g];
+    st.d[g] *= s.o_scale;
   }
-  TileResult r;
-  r.tile_m = fmaxf(fmaxf(gmax[0], gmax[1]), fmaxf(gmax[2], gmax[3]));
-  const float neg_m = -r.tile_m;
-  const float m_prev = st.m;
-  st.m = fmaxf(m_prev, r.tile_m);
-  const float smaller = ex2_approx(-fabsf(m_prev - r.tile_m));
-  r.o_scale = m_prev < r.tile_m ? smaller : 1.0f;
-  r.w = r.tile_m < m_prev ? smaller : 1.0f;
-  r.numer = 0;
-  float dprev[4];
+  return s;
+}
+
+// Probabilities of one 32-key chunk: P receives 8 packed words in storage order (word 4j+g = lane
+// g of 16-key group j); numer accumulates the U8 sum; with EXACT_D the four denominator partials
+// advance in the reference's order (one FMA per 16-key group; in the last visited tile one FMA per
+// pair of groups, the very first fused with the rescale of the running partial -- d * o_scale +
+// round(s * w) in a single FMA -- which is how the reference's compiled code rounds; found by
+// comparing final denominators bit for bit on the GPU).  Without EXACT_D the caller folds numer
+// into one partial and results agree with the reference to rounding, not bit for bit.
+template <int KIND, bool LAST, bool EXACT_D>
+__device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4],
+                                               const TileScales& ts, bool first_chunk,
+                                               RowState& st, uint32_t* P, uint32_t& numer) {
+  const float neg_m = -ts.tile_m;
 #pragma unroll
-  for (int g = 0; g < 4; ++g) { dprev[g] = st.d[g]; st.d[g] *= r.o_scale; }
-#pragma unroll
-  for (int j = 0; j < G16; ++j) {
+  for (int j = 0; j < 2; ++j) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       uint32_t word = 0;
@@ -93,7 +125,7 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
       for (int e = 0; e < 4; ++e) {
         const float s = x[lane_column(j, g, e)];
         const float p = KIND == kScoresScaled ? ex2_approx(s + neg_m)
-                                            : ex2_approx(fmaf(s, sc[g], neg_m));
+                                              : ex2_approx(fmaf(s, sc[g], neg_m));
         word |= to_u8(p) << (8 * e);
       }
       P[4 * j + g] = word;
@@ -102,30 +134,50 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     if constexpr (LAST) {
-      // generic path of the last visited tile: one FMA per pair of 16-key groups
-#pragma unroll
-      for (int j = 0; j < G16; j += 2) {
-        const uint32_t s8 = __dp4a(P[4 * j + 4 + g], 0x01010101u, __dp4a(P[4 * j + g], 0x01010101u, 0u));
-        r.numer += s8;
-        if constexpr (EXACT_D) {
-          // The reference's compiler fuses the rescale of the running denominator with the first
-          // addend of this tile (d * o_scale + round(s * w) in one FMA); later addends fuse the
-          // other way.  Found by comparing final denominators bit for bit on the GPU.
-          if (j == 0) st.d[g] = fmaf(dprev[g], r.o_scale, __fmul_rn(static_cast<float>(s8), r.w));
-          else st.d[g] = fmaf(static_cast<float>(s8), r.w, st.d[g]);
-        }
+      const uint32_t s8 = __dp4a(P[4 + g], 0x01010101u, __dp4a(P[g], 0x01010101u, 0u));
+      numer += s8;
+      if constexpr (EXACT_D) {
+        if (first_chunk)
+          st.d[g] = fmaf(ts.dprev[g], ts.o_scale, __fmul_rn(static_cast<float>(s8), ts.w));
+        else
+          st.d[g] = fmaf(static_cast<float>(s8), ts.w, st.d[g]);
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < G16; ++j) {
+      for (int j = 0; j < 2; ++j) {
         const uint32_t s4 = __dp4a(P[4 * j + g], 0x01010101u, 0u);
-        r.numer += s4;
-        if constexpr (EXACT_D) st.d[g] = fmaf(static_cast<float>(s4), r.w, st.d[g]);
+        numer += s4;
+        if constexpr (EXACT_D) st.d[g] = fmaf(static_cast<float>(s4), ts.w, st.d[g]);
       }
     }
   }
-  if constexpr (!EXACT_D) st.d[0] = fmaf(static_cast<float>(r.numer), r.w, st.d[0]);
-  return r;
+}
+
+template <bool EXACT_D>
+__device__ __forceinline__ void tile_end(RowState& st, const TileScales& ts, uint32_t numer) {
+  if constexpr (!EXACT_D) st.d[0] = fmaf(static_cast<float>(numer), ts.w, st.d[0]);
+}
+
+struct TileResult {
+  float tile_m, o_scale, w;
+  uint32_t numer;
+};
+
+// Whole tile from a register array (row-per-thread kernel).
+template <int CTA_K, int KIND, bool LAST, bool EXACT_D>
+__device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], const float (&sc)[4],
+                                                   RowState& st, uint32_t (&P)[CTA_K / 4]) {
+  TileMax tm;
+  tile_max_init<KIND, LAST>(tm);
+#pragma unroll
+  for (int c = 0; c < CTA_K / 32; ++c) tile_max_chunk(&x[32 * c], tm);
+  const TileScales ts = tile_begin(st, tile_max_finish<KIND>(tm, sc));
+  uint32_t numer = 0;
+#pragma unroll
+  for (int c = 0; c < CTA_K / 32; ++c)
+    tile_exp_chunk<KIND, LAST, EXACT_D>(&x[32 * c], sc, ts, c == 0, st, &P[8 * c], numer);
+  tile_end<EXACT_D>(st, ts, numer);
+  return {ts.tile_m, ts.o_scale, ts.w, numer};
 }
 
 __device__ __forceinline__ float row_denominator(const RowState& st) {
