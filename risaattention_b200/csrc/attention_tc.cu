@@ -3,27 +3,31 @@
 // TMA into 128-byte-swizzled shared memory; the FP32 online softmax, the per-tile FP32 rescale of
 // the output and the epilogue run on ordinary warps that read the accumulators with tcgen05.ld.
 //
-// One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Warp roles:
-//   warps 0-3  softmax:    thread r owns query row r (tensor-memory lane r): two passes over the
-//                          128 scores of a tile (maxima, then U8 probabilities written to shared
-//                          memory as the A operand of P.V, bytes placed in the packed V order);
-//   warps 4-7  correction: thread r owns the FP32 output row r in registers; per tile
-//                          O = O * o_scale + float(P.V) * w, then the epilogue and the store;
-//   warp 8     producer:   TMA loads of Q and of the K / V tile ring;
-//   warp 9     MMA issue:  one thread issues the MMAs; QK^T of tile t+1 is issued before P.V of
-//                          tile t so the tensor pipe works while the softmax of tile t runs.
-// Tensor memory (512 columns): S double-buffered (2 x 128), P.V accumulator double-buffered
-// (2 x 128).  The U8 probabilities are scaled to the TILE maximum (full 8-bit resolution per tile),
-// so every tile's integer P.V has its own weight and must be folded into FP32 by the correction
-// warps; nothing accumulates across tiles inside tensor memory.
-// Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh; the integer
-// products are exact, so probabilities, capture statistics and block masses are bit-identical to the
-// row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
+// One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Four warpgroups:
+//   WG0 / WG1  softmax of even / odd tiles.  Thread r owns query row r (tensor-memory lane r) and
+//              makes two passes over the tile's 128 scores: maxima, then U8 probabilities written to
+//              shared memory as the A operand of P.V (bytes placed in the packed V order).  The U8
+//              codes depend only on the TILE maximum, so the two groups work on different tiles at
+//              the same time with no state shared between them.
+//   WG2        correction.  Thread r owns the FP32 output row r in registers and everything that is
+//              sequential over tiles: running maximum, denominator, per-tile weights,
+//              O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
+//   WG3        warp 12: TMA producer (Q, K ring, V ring); warp 13: MMA issue (one thread); QK^T of
+//              tile t+2 is issued right after P.V of tile t, so the tensor pipe never waits for the
+//              softmax of the tile it just produced.
+// Tensor memory (512 columns): S double-buffered (2 x 128, one per softmax group), P.V accumulator
+// double-buffered (2 x 128).  Probabilities are scaled to the tile maximum (full 8-bit resolution
+// in every tile), so each tile's integer P.V has its own weight and is folded into FP32 by the
+// correction group; nothing accumulates across tiles inside tensor memory.
+// Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh.  The integer
+// products are exact, so probabilities, capture statistics and block masses are bit-identical to
+// the row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
 // Every mbarrier wait is bounded (tc_ptx.cuh): a protocol error sets a device status word and the
 // CTA drains and exits instead of spinning.
 #include "attention_common.cuh"
 #include "tc_ptx.cuh"
 
+#include <climits>
 #include <cuda.h>
 #include <mutex>
 
@@ -32,21 +36,23 @@ namespace {
 
 using namespace tc;
 
-constexpr int kStages = 3;            // K / V ring depth
+constexpr int kKStages = 4;           // K ring depth (K runs two tiles ahead of V)
+constexpr int kVStages = 3;           // V ring depth
 constexpr int kTile = 128 * 128;      // bytes of one 128 x 128 INT8 tile
-constexpr int kThreads = 320;
+constexpr int kThreads = 512;
+constexpr int kRegsSoftmax = 120, kRegsCorrection = 216, kRegsIssue = 40;
 
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
 
 struct SmemLayout {
   static constexpr int q = 0;
   static constexpr int k = q + kTile;
-  static constexpr int v = k + kStages * kTile;
-  static constexpr int p = v + kStages * kTile;
-  static constexpr int scales = p + 2 * kTile;          // float2 [2][128]
-  static constexpr int fin = scales + 2 * 128 * 8;      // float2 [128]
-  static constexpr int bars = fin + 128 * 8;            // 8-byte mbarriers
-  static constexpr int n_bars = 2 + 4 * kStages + 10;
+  static constexpr int v = k + kKStages * kTile;
+  static constexpr int p = v + kVStages * kTile;
+  static constexpr int stats = p + 2 * kTile;             // float2 [2][128]: tile max, U8 sum
+  static constexpr int sums = stats + 2 * 128 * 8;        // uint16 [2][128][32] (capture only)
+  static constexpr int bars = sums + 2 * 128 * 64;        // 8-byte mbarriers
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 12;
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int total = tmem_slot + 16;
 };
@@ -75,6 +81,117 @@ __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t
   return s;
 }
 
+struct Bars {
+  uint32_t base;
+  static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
+                       VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages, SFREE = SFULL + 2,
+                       PFULL = SFREE + 2, PFREE = PFULL + 2, OFULL = PFREE + 2, OFREE = OFULL + 2;
+  __device__ __forceinline__ uint32_t operator()(int i) const { return base + 8u * i; }
+};
+
+// ---- softmax of one tile by the thread that owns the row -----------------------------------------
+// Common case: exact integer scores, not the last visited tile.  Pass 1 takes the maxima on the
+// raw integers (no conversion), pass 2 converts, scales, exponentiates and packs.
+template <bool CAPTURE>
+__device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
+                                                 unsigned char* p_row, int swz, float2* stat,
+                                                 uint16_t* sums) {
+  uint32_t raw[2][32];
+  int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  tmem_load32(tmem_row, raw[0]);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tmem_load_wait();
+    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) imax[(i & 7) >> 1] = max(imax[(i & 7) >> 1], int(raw[c & 1][i]));
+  }
+  tmem_load32(tmem_row, raw[0]);
+  float gm[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) gm[g] = fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset);
+  const float tile_m = fmaxf(fmaxf(gm[0], gm[1]), fmaxf(gm[2], gm[3]));
+  const float neg_m = -tile_m;
+  uint32_t numer = 0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tmem_load_wait();
+    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[c & 1][i]));
+    uint32_t P[8], s4[8];
+    tile_exp_chunk<kScoresInt>(x, sc, neg_m, P, s4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) numer += s4[i];
+    if constexpr (CAPTURE) {
+#pragma unroll
+      for (int i = 0; i < 8; i += 2)
+        *reinterpret_cast<uint32_t*>(sums + 8 * c + i) = s4[i] | (s4[i + 1] << 16);
+    }
+    *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ swz) << 4)) = make_uint4(P[0], P[1], P[2], P[3]);
+    *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ swz) << 4)) =
+        make_uint4(P[4], P[5], P[6], P[7]);
+  }
+  *stat = make_float2(tile_m, __uint_as_float(numer));
+}
+
+// Every other case (last visited tile, causal, scale <= 0): float scores with the masks applied.
+template <bool CAPTURE>
+__device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const float (&sc)[4],
+                                                     unsigned char* p_row, int swz, float2* stat,
+                                                     uint16_t* sums, bool int_scores, bool last,
+                                                     bool causal, int row, int c0, int k_len) {
+  auto load_chunk = [&](int c, float* x) {
+    uint32_t raw[32];
+    tmem_load32(tmem_row + 32 * c, raw);
+    tmem_load_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int kv = c0 + 32 * c + i;
+      float s = static_cast<float>(int(raw[i]));
+      if (int_scores) {
+        if (last && kv >= k_len) s = -1.0e30f;
+      } else {
+        s *= sc[(i & 7) >> 1];
+        if (causal && kv > row) s = -INFINITY;
+        if (last && kv >= k_len) s = -INFINITY;
+      }
+      x[i] = s;
+    }
+  };
+  TileMax tm;
+  tile_max_init<kScoresScaled, true>(tm);  // maxima start at -50000 in all of these cases
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float x[32];
+    load_chunk(c, x);
+    tile_max_chunk(x, tm);
+  }
+  const float tile_m = int_scores ? tile_max_finish<kScoresInt>(tm, sc)
+                                  : tile_max_finish<kScoresScaled>(tm, sc);
+  uint32_t numer = 0;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float x[32];
+    uint32_t P[8], s4[8];
+    load_chunk(c, x);
+    if (int_scores) tile_exp_chunk<kScoresInt>(x, sc, -tile_m, P, s4);
+    else tile_exp_chunk<kScoresScaled>(x, sc, -tile_m, P, s4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) numer += s4[i];
+    if constexpr (CAPTURE) {
+#pragma unroll
+      for (int i = 0; i < 8; i += 2)
+        *reinterpret_cast<uint32_t*>(sums + 8 * c + i) = s4[i] | (s4[i + 1] << 16);
+    }
+    *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ swz) << 4)) = make_uint4(P[0], P[1], P[2], P[3]);
+    *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ swz) << 4)) =
+        make_uint4(P[4], P[5], P[6], P[7]);
+  }
+  *stat = make_float2(tile_m, __uint_as_float(numer));
+}
+
 template <bool CAPTURE>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -84,41 +201,36 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
   const int bx = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const int n_k = (a.k_len + 127) / 128, n_q = gridDim.x;
   const int64_t bh = int64_t(batch) * a.q_heads + head;
   const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
   unsigned int* error = &g_tc_status;
-
-  // barrier addresses
-  const uint32_t bar0 = sbase + SmemLayout::bars;
-  auto bar = [&](int i) { return bar0 + 8u * i; };
-  const int B_QFULL = 0, B_FIN = 1, B_KFULL = 2, B_KEMPTY = B_KFULL + kStages,
-            B_VFULL = B_KEMPTY + kStages, B_VEMPTY = B_VFULL + kStages,
-            B_SFULL = B_VEMPTY + kStages, B_SFREE = B_SFULL + 2, B_PFULL = B_SFREE + 2,
-            B_PFREE = B_PFULL + 2, B_OFULL = B_PFREE + 2, B_OFREE = B_OFULL + 2;
+  Bars bar{sbase + SmemLayout::bars};
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(B_QFULL), 1);
-    mbar_init(bar(B_FIN), 128);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(B_KFULL + s), 1);
-      mbar_init(bar(B_KEMPTY + s), 1);
-      mbar_init(bar(B_VFULL + s), 1);
-      mbar_init(bar(B_VEMPTY + s), 1);
+    mbar_init(bar(Bars::QFULL), 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(bar(Bars::KFULL + s), 1);
+      mbar_init(bar(Bars::KEMPTY + s), 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(bar(Bars::VFULL + s), 1);
+      mbar_init(bar(Bars::VEMPTY + s), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_SFREE + b), 128);
-      mbar_init(bar(B_PFULL + b), 128);
-      mbar_init(bar(B_PFREE + b), 1);
-      mbar_init(bar(B_OFULL + b), 1);
-      mbar_init(bar(B_OFREE + b), 128);
+      mbar_init(bar(Bars::SFULL + b), 1);
+      mbar_init(bar(Bars::SFREE + b), 128);
+      mbar_init(bar(Bars::PFULL + b), 128);
+      mbar_init(bar(Bars::PFREE + b), 1);
+      mbar_init(bar(Bars::OFULL + b), 1);
+      mbar_init(bar(Bars::OFREE + b), 128);
     }
     mbar_init_fence();
   }
-  if (warp == 9) tmem_alloc(sbase + SmemLayout::tmem_slot, 512);
+  if (warp == 13) tmem_alloc(sbase + SmemLayout::tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -127,78 +239,82 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   const uint32_t tmem_o[2] = {tmem + 256, tmem + 384};
 
   const TileSeq seq = tile_sequence(a, bh, bx, n_q, n_k, CAPTURE);
-  float2* scales = reinterpret_cast<float2*>(smem + SmemLayout::scales);
-  float2* fin = reinterpret_cast<float2*>(smem + SmemLayout::fin);
+  float2* stats = reinterpret_cast<float2*>(smem + SmemLayout::stats);
+  uint16_t* sums = reinterpret_cast<uint16_t*>(smem + SmemLayout::sums);
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+  if (wg == 3) {
+    regs_dec<kRegsIssue>();
+    if (warp == 12 && lane == 0) {
+      // ---------------------------------------------------------------- producer
       tma_prefetch_descriptor(&map_q);
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_v);
-      mbar_expect_tx(bar(B_QFULL), kTile);
-      tma_load_3d(sbase + SmemLayout::q, &map_q, bar(B_QFULL), 0, bx * 128, int(bh));
+      mbar_expect_tx(bar(Bars::QFULL), kTile);
+      tma_load_3d(sbase + SmemLayout::q, &map_q, bar(Bars::QFULL), 0, bx * 128, int(bh));
       bool ok = true;
-      int issued = 0;
-      for (int it = 0; it < seq.n_iter && ok; ++it) {
-        const int s = it % kStages, r = it / kStages;
-        const int tile = seq.tile(it);
-        ok = mbar_wait(bar(B_KEMPTY + s), (r & 1) ^ 1, error, 101);
-        if (!ok) break;
-        mbar_expect_tx(bar(B_KFULL + s), kTile);
-        tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(B_KFULL + s), 0, tile * 128,
-                    int(kvh));
-        ok = mbar_wait(bar(B_VEMPTY + s), (r & 1) ^ 1, error, 102);
-        if (!ok) {
-          // the K load of this stage is in flight: let it land before the CTA can exit
-          mbar_wait(bar(B_KFULL + s), r & 1, error, 103);
-          break;
+      int k_issued = 0, v_issued = 0;
+      // K runs two tiles ahead of V, matching the order in which the MMA warp consumes them.
+      for (int step = 0; step < seq.n_iter + 2 && ok; ++step) {
+        if (step < seq.n_iter) {
+          const int s = step % kKStages, r = step / kKStages;
+          ok = mbar_wait(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
+          if (!ok) break;
+          mbar_expect_tx(bar(Bars::KFULL + s), kTile);
+          tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
+                      seq.tile(step) * 128, int(kvh));
+          k_issued = step + 1;
         }
-        mbar_expect_tx(bar(B_VFULL + s), kTile);
-        tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(B_VFULL + s), tile * 128, 0,
-                    int(kvh));
-        issued = it + 1;
+        const int it = step - 2;
+        if (it >= 0) {
+          const int s = it % kVStages, r = it / kVStages;
+          ok = mbar_wait(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
+          if (!ok) break;
+          mbar_expect_tx(bar(Bars::VFULL + s), kTile);
+          tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
+                      seq.tile(it) * 128, 0, int(kvh));
+          v_issued = it + 1;
+        }
       }
       if (!ok) {
-        // drain: every issued load must have completed before shared memory is released
-        mbar_wait(bar(B_QFULL), 0, error, 104);
-        for (int it = max(0, issued - kStages); it < issued; ++it) {
-          const int s = it % kStages, r = it / kStages;
-          mbar_wait(bar(B_KFULL + s), r & 1, error, 105);
-          mbar_wait(bar(B_VFULL + s), r & 1, error, 106);
-        }
+        // drain: every issued load must land before shared memory can be released
+        mbar_wait(bar(Bars::QFULL), 0, error, 104);
+        for (int it = max(0, k_issued - kKStages); it < k_issued; ++it)
+          mbar_wait(bar(Bars::KFULL + it % kKStages), (it / kKStages) & 1, error, 105);
+        for (int it = max(0, v_issued - kVStages); it < v_issued; ++it)
+          mbar_wait(bar(Bars::VFULL + it % kVStages), (it / kVStages) & 1, error, 106);
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
+    } else if (warp == 13 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issue
       constexpr uint32_t idesc_qk = idesc_i8(true, true, 128);
       constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
       const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
-      bool ok = mbar_wait(bar(B_QFULL), 0, error, 201);
+      bool ok = mbar_wait(bar(Bars::QFULL), 0, error, 201);
       auto issue_qk = [&](int it) -> bool {
-        const int b = it & 1, u = it >> 1, s = it % kStages, r = it / kStages;
-        if (!mbar_wait(bar(B_KFULL + s), r & 1, error, 202)) return false;
-        if (!mbar_wait(bar(B_SFREE + b), (u & 1) ^ 1, error, 203)) return false;
+        const int b = it & 1, u = it >> 1, s = it % kKStages, r = it / kKStages;
+        if (!mbar_wait(bar(Bars::KFULL + s), r & 1, error, 202)) return false;
+        if (!mbar_wait(bar(Bars::SFREE + b), (u & 1) ^ 1, error, 203)) return false;
         tc_fence_after();
         const uint64_t desc_k = smem_desc_k128(sbase + SmemLayout::k + s * kTile);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_i8(tmem_s[b], desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
-        mma_commit(bar(B_SFULL + b));
-        mma_commit(bar(B_KEMPTY + s));
+        mma_commit(bar(Bars::SFULL + b));
+        mma_commit(bar(Bars::KEMPTY + s));
         return true;
       };
       if (ok && seq.n_iter > 0) ok = issue_qk(0);
+      if (ok && seq.n_iter > 1) ok = issue_qk(1);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
-        if (it + 1 < seq.n_iter) {
-          ok = issue_qk(it + 1);
+        const int b = it & 1, u = it >> 1, s = it % kVStages, r = it / kVStages;
+        ok = mbar_wait(bar(Bars::PFULL + b), u & 1, error, 204);
+        if (!ok) break;
+        // the group that just finished tile `it` gets its next scores first, then P.V(it)
+        if (it + 2 < seq.n_iter) {
+          ok = issue_qk(it + 2);
           if (!ok) break;
         }
-        const int b = it & 1, u = it >> 1, s = it % kStages, r = it / kStages;
-        ok = mbar_wait(bar(B_PFULL + b), u & 1, error, 204) &&
-             mbar_wait(bar(B_VFULL + s), r & 1, error, 205) &&
-             mbar_wait(bar(B_OFREE + b), (u & 1) ^ 1, error, 206);
+        ok = mbar_wait(bar(Bars::VFULL + s), r & 1, error, 205) &&
+             mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 206);
         if (!ok) break;
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + b * kTile);
@@ -206,110 +322,83 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_i8(tmem_o[b], desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
-        mma_commit(bar(B_OFULL + b));
-        mma_commit(bar(B_VEMPTY + s));
-        mma_commit(bar(B_PFREE + b));
+        mma_commit(bar(Bars::OFULL + b));
+        mma_commit(bar(Bars::VEMPTY + s));
+        mma_commit(bar(Bars::PFREE + b));
       }
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ softmax
-    const int row_in = threadIdx.x;  // 0..127 == tensor-memory lane
+  } else if (wg < 2) {
+    // ------------------------------------------------------------------ softmax of tiles it = wg, wg+2, ...
+    regs_dec<kRegsSoftmax>();
+    const int b = wg;
+    const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
-    const bool row_ok = row < a.q_len;
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const uint32_t tmem_row = tmem_s[b] + (uint32_t((warp & 3) * 32) << 16);
     const bool int_scores = !a.is_causal && a.sm_scale > 0.0f;
     const float scale2 = a.sm_scale * kLog2e;
-    const int q_groups_per_head = n_q * 32;
-    const float q_scale = __ldg(a.q_scale + bh * q_groups_per_head + (row / 32) * 8 + (row & 7));
+    const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
     const float* k_scale = a.k_scale + kvh * (n_k * 4);
-    CaptureLayout cap;
-    if constexpr (CAPTURE) cap = capture_layout(a, n_q, n_k);
-    const int64_t grow = bh * a.q_len + row;
-    unsigned char* p_row[2] = {smem + SmemLayout::p + row_in * 128,
-                               smem + SmemLayout::p + kTile + row_in * 128};
-    RowState st;
-    row_state_init(st);
+    unsigned char* p_row = smem + SmemLayout::p + b * kTile + row_in * 128;
+    float2* stat = stats + b * 128 + row_in;
+    uint16_t* my_sums = sums + (b * 128 + row_in) * 32;
     bool ok = true;
-
-    for (int it = 0; it < seq.n_iter && ok; ++it) {
-      const int b = it & 1, u = it >> 1;
+    for (int it = b; it < seq.n_iter && ok; it += 2) {
+      const int u = it >> 1;
       const int tile = seq.tile(it);
       const bool last = it == seq.n_iter - 1;
-      const int c0 = tile * 128;
       float sc[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) sc[g] = scale2 * (q_scale * __ldg(k_scale + tile * 4 + g));
-      ok = mbar_wait(bar(B_SFULL + b), u & 1, error, 301);
+      // P buffer and the statistics slot of this group are free once P.V and the correction of
+      // its previous tile are done; S is ready when the MMA warp says so
+      ok = mbar_wait(bar(Bars::PFREE + b), (u & 1) ^ 1, error, 302) &&
+           mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 303) &&
+           mbar_wait(bar(Bars::SFULL + b), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
-
-      // scores of one 32-column chunk as the floats the softmax consumes
-      auto load_chunk = [&](int c, float* x) {
-        uint32_t raw[32];
-        tmem_load32(tmem_s[b] + lane_base + 32 * c, raw);
-        tmem_load_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = c0 + 32 * c + i;
-          float s = static_cast<float>(static_cast<int>(raw[i]));
-          if (int_scores) {
-            if (last && kv >= a.k_len) s = -1.0e30f;
-          } else {
-            s *= sc[(i & 7) >> 1];
-            if (a.is_causal && kv > row) s = -INFINITY;
-            if (last && kv >= a.k_len) s = -INFINITY;
-          }
-          x[i] = s;
-        }
-      };
-
-      // pass 1: tile maximum
-      TileMax tm;
-      if (int_scores && !last) tile_max_init<kScoresInt, false>(tm);
-      else tile_max_init<kScoresScaled, true>(tm);  // -50000 start (every other case)
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float x[32];
-        load_chunk(c, x);
-        tile_max_chunk(x, tm);
-      }
-      const float tile_m = int_scores ? tile_max_finish<kScoresInt>(tm, sc)
-                                      : tile_max_finish<kScoresScaled>(tm, sc);
-      const TileScales ts = tile_begin(st, tile_m);
-
-      // hand (o_scale, w) to the correction warps once they are done with this buffer's last use
-      ok = mbar_wait(bar(B_OFREE + b), (u & 1) ^ 1, error, 302) &&
-           mbar_wait(bar(B_PFREE + b), (u & 1) ^ 1, error, 303);
-      if (!ok) break;
-      scales[b * 128 + row_in] = make_float2(ts.o_scale, ts.w);
-
-      // pass 2: probabilities -> shared memory (128-byte swizzle: 16-byte chunk index ^ row % 8)
-      uint32_t numer = 0;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float x[32];
-        uint32_t P[8];
-        load_chunk(c, x);
-        if (int_scores) {
-          if (last) tile_exp_chunk<kScoresInt, true, CAPTURE>(x, sc, ts, c == 0, st, P, numer);
-          else tile_exp_chunk<kScoresInt, false, CAPTURE>(x, sc, ts, c == 0, st, P, numer);
-        } else {
-          if (last) tile_exp_chunk<kScoresScaled, true, CAPTURE>(x, sc, ts, c == 0, st, P, numer);
-          else tile_exp_chunk<kScoresScaled, false, CAPTURE>(x, sc, ts, c == 0, st, P, numer);
-        }
-        const int sw = row_in & 7;
-        *reinterpret_cast<uint4*>(p_row[b] + (((2 * c) ^ sw) << 4)) =
-            make_uint4(P[0], P[1], P[2], P[3]);
-        *reinterpret_cast<uint4*>(p_row[b] + (((2 * c + 1) ^ sw) << 4)) =
-            make_uint4(P[4], P[5], P[6], P[7]);
-      }
-      tile_end<CAPTURE>(st, ts, numer);
+      if (int_scores && !last)
+        softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums);
+      else
+        softmax_tile_general<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums, int_scores,
+                                      last, a.is_causal != 0, row, tile * 128, a.k_len);
       tc_fence_before();
-      mbar_arrive(bar(B_SFREE + b));
+      mbar_arrive(bar(Bars::SFREE + b));
       fence_async_smem();
-      mbar_arrive(bar(B_PFULL + b));
-
+      mbar_arrive(bar(Bars::PFULL + b));
+    }
+  } else {
+    // ------------------------------------------------------------------ correction + epilogue
+    regs_inc<kRegsCorrection>();
+    const int row_in = threadIdx.x & 127;
+    const int row = bx * 128 + row_in;
+    const bool row_ok = row < a.q_len;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    CaptureLayout cap;
+    if constexpr (CAPTURE) cap = capture_layout(a, n_q, n_k);
+    const int64_t grow = bh * a.q_len + row;
+    RowState st;
+    row_state_init(st);
+    float O[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) O[i] = 0.0f;
+    bool ok = true;
+    for (int it = 0; it < seq.n_iter && ok; ++it) {
+      const int b = it & 1, u = it >> 1;
+      const bool last = it == seq.n_iter - 1;
+      ok = mbar_wait(bar(Bars::PFULL + b), u & 1, error, 401);
+      if (!ok) break;
+      const float2 stat = stats[b * 128 + row_in];
+      const uint32_t numer = __float_as_uint(stat.y);
+      const TileScales ts = tile_begin(st, stat.x);
       if constexpr (CAPTURE) {
+        const uint16_t* s16 = sums + (b * 128 + row_in) * 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint16_t s4[8];
+          *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
+          if (last) denominator_chunk<true>(st, ts, c == 0, s4);
+          else denominator_chunk<false>(st, ts, c == 0, s4);
+        }
         if (row_ok) {
           if (last) {
             float* slot = cap.last + grow * 2;
@@ -321,53 +410,36 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
             slot[1] = __float_as_uint(ts.tile_m);
           }
         }
+      } else {
+        denominator_single(st, ts, numer);
       }
+      ok = mbar_wait(bar(Bars::OFULL + b), u & 1, error, 402);
+      if (!ok) break;
+      tc_fence_after();
+      const bool rescale = __any_sync(0xffffffffu, ts.o_scale != 1.0f);
+      uint32_t acc[2][32];
+      tmem_load32(tmem_o[b] + lane_base, acc[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_load_wait();
+        if (c < 3) tmem_load32(tmem_o[b] + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
+        if (rescale) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) O[32 * c + i] *= ts.o_scale;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          O[32 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), ts.w, O[32 * c + i]);
+      }
+      tc_fence_before();
+      mbar_arrive(bar(Bars::OFREE + b));
     }
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
-    fin[row_in] = make_float2(denom, st.m);
-    mbar_arrive(bar(B_FIN));
-    if constexpr (CAPTURE) {
-      if (row_ok && ok) {
+    if (ok && row_ok) {
+      if constexpr (CAPTURE) {
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
-    }
-  } else {
-    // ------------------------------------------------------------------ correction + epilogue
-    const int row_in = threadIdx.x - 128;
-    const int row = bx * 128 + row_in;
-    const uint32_t lane_base = uint32_t((warp - 4) * 32) << 16;
-    float O[128];
-#pragma unroll
-    for (int i = 0; i < 128; ++i) O[i] = 0.0f;
-    bool ok = true;
-    for (int it = 0; it < seq.n_iter && ok; ++it) {
-      const int b = it & 1, u = it >> 1;
-      ok = mbar_wait(bar(B_PFULL + b), u & 1, error, 401);
-      if (!ok) break;
-      const float2 sw = scales[b * 128 + row_in];
-      ok = mbar_wait(bar(B_OFULL + b), u & 1, error, 402);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t acc[32];
-        tmem_load32(tmem_o[b] + lane_base + 32 * c, acc);
-        tmem_load_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float o = O[32 * c + i];
-          o *= sw.x;
-          O[32 * c + i] = fmaf(static_cast<float>(static_cast<int>(acc[i])), sw.y, o);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(bar(B_OFREE + b));
-    }
-    if (ok) ok = mbar_wait(bar(B_FIN), 0, error, 403);
-    if (ok && row < a.q_len) {
-      const float2 f = fin[row_in];
-      const float denom = f.x;
       const float inv = rcp_approx(denom);
       const bool zero = a.is_causal && !(denom > 0.0f);
       const float* vs = a.v_scale + kvh * 128;
@@ -394,13 +466,13 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         *reinterpret_cast<uint4*>(o_row + 2 * ch) =
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      if (a.lse) a.lse[bh * a.q_len + row] = row_lse(denom, f.y);
+      if (a.lse) a.lse[grow] = row_lse(denom, st.m);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 13) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }

@@ -36,12 +36,6 @@ __device__ __forceinline__ void row_state_init(RowState& s) {
   s.d[0] = s.d[1] = s.d[2] = s.d[3] = 0.0f;
 }
 
-__device__ __forceinline__ uint32_t to_u8(float p) {
-  uint32_t q;
-  asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(p));
-  return q;
-}
-
 // Column (inside a 32-key chunk) of virtual lane g, 16-key group j (0/1), element e (0..3).
 __device__ __forceinline__ constexpr int lane_column(int j, int g, int e) {
   return 16 * j + 2 * g + (e & 1) + 8 * (e >> 1);
@@ -104,58 +98,61 @@ __device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
   return s;
 }
 
+// U8 codes of four probabilities in [0, 255.5): adding 2^23 rounds to nearest-even into the low
+// mantissa byte (the same integers cvt.rni.sat.u8 gives on this range) and three byte permutes pack
+// them, which keeps the conversion off the half-rate conversion pipe.
+__device__ __forceinline__ uint32_t pack_u8x4(float p0, float p1, float p2, float p3) {
+  const uint32_t a = __float_as_uint(p0 + 8388608.0f), b = __float_as_uint(p1 + 8388608.0f);
+  const uint32_t c = __float_as_uint(p2 + 8388608.0f), d = __float_as_uint(p3 + 8388608.0f);
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
 // Probabilities of one 32-key chunk: P receives 8 packed words in storage order (word 4j+g = lane
-// g of 16-key group j); numer accumulates the U8 sum; with EXACT_D the four denominator partials
-// advance in the reference's order (one FMA per 16-key group; in the last visited tile one FMA per
-// pair of groups, the very first fused with the rescale of the running partial -- d * o_scale +
-// round(s * w) in a single FMA -- which is how the reference's compiled code rounds; found by
-// comparing final denominators bit for bit on the GPU).  Without EXACT_D the caller folds numer
-// into one partial and results agree with the reference to rounding, not bit for bit.
-template <int KIND, bool LAST, bool EXACT_D>
-__device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4],
-                                               const TileScales& ts, bool first_chunk,
-                                               RowState& st, uint32_t* P, uint32_t& numer) {
-  const float neg_m = -ts.tile_m;
+// g of 16-key group j), s4 the U8 sum of each word.
+template <int KIND>
+__device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
+                                               uint32_t* P, uint32_t* s4) {
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      uint32_t word = 0;
+      float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float s = x[lane_column(j, g, e)];
-        const float p = KIND == kScoresScaled ? ex2_approx(s + neg_m)
-                                              : ex2_approx(fmaf(s, sc[g], neg_m));
-        word |= to_u8(p) << (8 * e);
+        p[e] = KIND == kScoresScaled ? ex2_approx(s + neg_m) : ex2_approx(fmaf(s, sc[g], neg_m));
       }
-      P[4 * j + g] = word;
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    if constexpr (LAST) {
-      const uint32_t s8 = __dp4a(P[4 + g], 0x01010101u, __dp4a(P[g], 0x01010101u, 0u));
-      numer += s8;
-      if constexpr (EXACT_D) {
-        if (first_chunk)
-          st.d[g] = fmaf(ts.dprev[g], ts.o_scale, __fmul_rn(static_cast<float>(s8), ts.w));
-        else
-          st.d[g] = fmaf(static_cast<float>(s8), ts.w, st.d[g]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const uint32_t s4 = __dp4a(P[4 * j + g], 0x01010101u, 0u);
-        numer += s4;
-        if constexpr (EXACT_D) st.d[g] = fmaf(static_cast<float>(s4), ts.w, st.d[g]);
-      }
+      P[4 * j + g] = pack_u8x4(p[0], p[1], p[2], p[3]);
+      s4[4 * j + g] = __dp4a(P[4 * j + g], 0x01010101u, 0u);
     }
   }
 }
 
-template <bool EXACT_D>
-__device__ __forceinline__ void tile_end(RowState& st, const TileScales& ts, uint32_t numer) {
-  if constexpr (!EXACT_D) st.d[0] = fmaf(static_cast<float>(numer), ts.w, st.d[0]);
+// Advances the four denominator partials over one chunk in the reference's order: one FMA per
+// 16-key group; in the last visited tile one FMA per pair of groups, the very first fused with the
+// rescale of the running partial -- d * o_scale + round(s * w) in a single FMA -- which is how the
+// reference's compiled code rounds (found by comparing final denominators bit for bit on the GPU).
+template <bool LAST, typename SumT>
+__device__ __forceinline__ void denominator_chunk(RowState& st, const TileScales& ts,
+                                                  bool first_chunk, const SumT* s4) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if constexpr (LAST) {
+      const float s8 = static_cast<float>(uint32_t(s4[g]) + uint32_t(s4[4 + g]));
+      if (first_chunk) st.d[g] = fmaf(ts.dprev[g], ts.o_scale, __fmul_rn(s8, ts.w));
+      else st.d[g] = fmaf(s8, ts.w, st.d[g]);
+    } else {
+      st.d[g] = fmaf(static_cast<float>(uint32_t(s4[g])), ts.w, st.d[g]);
+      st.d[g] = fmaf(static_cast<float>(uint32_t(s4[4 + g])), ts.w, st.d[g]);
+    }
+  }
+}
+
+// Single-partial denominator for paths that only need the output tolerance, not the reference's
+// bits: d = d * o_scale + numer * w.
+__device__ __forceinline__ void denominator_single(RowState& st, const TileScales& ts,
+                                                   uint32_t numer) {
+  st.d[0] = fmaf(static_cast<float>(numer), ts.w, st.d[0]);
 }
 
 struct TileResult {
@@ -174,9 +171,14 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
   const TileScales ts = tile_begin(st, tile_max_finish<KIND>(tm, sc));
   uint32_t numer = 0;
 #pragma unroll
-  for (int c = 0; c < CTA_K / 32; ++c)
-    tile_exp_chunk<KIND, LAST, EXACT_D>(&x[32 * c], sc, ts, c == 0, st, &P[8 * c], numer);
-  tile_end<EXACT_D>(st, ts, numer);
+  for (int c = 0; c < CTA_K / 32; ++c) {
+    uint32_t s4[8];
+    tile_exp_chunk<KIND>(&x[32 * c], sc, -ts.tile_m, &P[8 * c], s4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) numer += s4[i];
+    if constexpr (EXACT_D) denominator_chunk<LAST>(st, ts, c == 0, s4);
+  }
+  if constexpr (!EXACT_D) denominator_single(st, ts, numer);
   return {ts.tile_m, ts.o_scale, ts.w, numer};
 }
 
