@@ -36,23 +36,31 @@ namespace {
 
 using namespace tc;
 
-constexpr int kKStages = 4;           // K ring depth (K runs two tiles ahead of V)
+constexpr int kKStages = 3;           // K ring depth (K runs two tiles ahead of V)
 constexpr int kVStages = 3;           // V ring depth
 constexpr int kTile = 128 * 128;      // bytes of one 128 x 128 INT8 tile
 constexpr int kThreads = 512;
 constexpr int kRegsSoftmax = 120, kRegsCorrection = 216, kRegsIssue = 40;
 
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
+#ifdef RISA_TC_PROFILE
+__device__ unsigned long long g_prof[16];
+#define PROF_T0() long long prof_t = clock64()
+#define PROF(slot) do { long long now = clock64(); if ((threadIdx.x & 31) == 0 && blockIdx.x == 3 && (slot) >= 0) atomicAdd(&g_prof[slot], (unsigned long long)(now - prof_t)); prof_t = now; } while (0)
+#else
+#define PROF_T0()
+#define PROF(slot)
+#endif
 
 struct SmemLayout {
   static constexpr int q = 0;
   static constexpr int k = q + kTile;
   static constexpr int v = k + kKStages * kTile;
   static constexpr int p = v + kVStages * kTile;
-  static constexpr int stats = p + 2 * kTile;             // float2 [2][128]: tile max, U8 sum
-  static constexpr int sums = stats + 2 * 128 * 8;        // uint16 [2][128][32] (capture only)
-  static constexpr int bars = sums + 2 * 128 * 64;        // 8-byte mbarriers
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 12;
+  static constexpr int stats = p + 4 * kTile;             // float2 [4][128]: tile max, U8 sum
+  static constexpr int sums = stats + 4 * 128 * 8;        // uint16 [4][128][32] (capture only)
+  static constexpr int bars = sums + 4 * 128 * 64;        // 8-byte mbarriers
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int total = tmem_slot + 16;
 };
@@ -85,7 +93,11 @@ struct Bars {
   uint32_t base;
   static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
                        VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages, SFREE = SFULL + 2,
-                       PFULL = SFREE + 2, PFREE = PFULL + 2, OFULL = PFREE + 2, OFREE = OFULL + 2;
+                       PFULL = SFREE + 2, PFREE = PFULL + 4, OFULL = PFREE + 4, OFREE = OFULL + 2,
+                       STATFREE = OFREE + 2;
+  // S and the P.V accumulator have two buffers (tile it uses it & 1); the probability tiles and the
+  // per-row statistics have four slots (it & 3), so a softmax group can start its next tile while
+  // P.V and the correction of its previous one are still in flight.
   __device__ __forceinline__ uint32_t operator()(int i) const { return base + 8u * i; }
 };
 
@@ -95,18 +107,27 @@ struct Bars {
 template <bool CAPTURE>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
-                                                 uint16_t* sums) {
+                                                 uint16_t* sums, uint32_t s_free_bar) {
   uint32_t raw[2][32];
   int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  PROF_T0();
   tmem_load32(tmem_row, raw[0]);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     tmem_load_wait();
     if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+    // columns of K scale group g inside the chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
 #pragma unroll
-    for (int i = 0; i < 32; ++i) imax[(i & 7) >> 1] = max(imax[(i & 7) >> 1], int(raw[c & 1][i]));
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t* r = raw[c & 1];
+      imax[g] = __vimax3_s32(imax[g], int(r[2 * g]), int(r[2 * g + 1]));
+      imax[g] = __vimax3_s32(imax[g], int(r[8 + 2 * g]), int(r[9 + 2 * g]));
+      imax[g] = __vimax3_s32(imax[g], int(r[16 + 2 * g]), int(r[17 + 2 * g]));
+      imax[g] = __vimax3_s32(imax[g], int(r[24 + 2 * g]), int(r[25 + 2 * g]));
+    }
   }
   tmem_load32(tmem_row, raw[0]);
+  PROF(2);
   float gm[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) gm[g] = fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset);
@@ -116,7 +137,13 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     tmem_load_wait();
-    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+    if (c < 3) {
+      tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+    } else {
+      // all scores of the tile are in registers: the MMA warp may overwrite S with the next tile
+      tc_fence_before();
+      mbar_arrive(s_free_bar);
+    }
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[c & 1][i]));
@@ -134,6 +161,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
         make_uint4(P[4], P[5], P[6], P[7]);
   }
   *stat = make_float2(tile_m, __uint_as_float(numer));
+  PROF(3);
 }
 
 // Every other case (last visited tile, causal, scale <= 0): float scores with the masks applied.
@@ -223,10 +251,13 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(Bars::SFULL + b), 1);
       mbar_init(bar(Bars::SFREE + b), 128);
-      mbar_init(bar(Bars::PFULL + b), 128);
-      mbar_init(bar(Bars::PFREE + b), 1);
       mbar_init(bar(Bars::OFULL + b), 1);
       mbar_init(bar(Bars::OFREE + b), 128);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(Bars::STATFREE + i), 128);
+      mbar_init(bar(Bars::PFULL + i), 128);
+      mbar_init(bar(Bars::PFREE + i), 1);
     }
     mbar_init_fence();
   }
@@ -289,10 +320,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
       const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
       bool ok = mbar_wait(bar(Bars::QFULL), 0, error, 201);
+      PROF_T0();
       auto issue_qk = [&](int it) -> bool {
         const int b = it & 1, u = it >> 1, s = it % kKStages, r = it / kKStages;
+        PROF(-1);
         if (!mbar_wait(bar(Bars::KFULL + s), r & 1, error, 202)) return false;
+        PROF(9);
         if (!mbar_wait(bar(Bars::SFREE + b), (u & 1) ^ 1, error, 203)) return false;
+        PROF(10);
         tc_fence_after();
         const uint64_t desc_k = smem_desc_k128(sbase + SmemLayout::k + s * kTile);
 #pragma unroll
@@ -306,25 +341,30 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (ok && seq.n_iter > 1) ok = issue_qk(1);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
         const int b = it & 1, u = it >> 1, s = it % kVStages, r = it / kVStages;
-        ok = mbar_wait(bar(Bars::PFULL + b), u & 1, error, 204);
-        if (!ok) break;
-        // the group that just finished tile `it` gets its next scores first, then P.V(it)
+        // the group that is finishing tile `it` gets its next scores as soon as it has read S
         if (it + 2 < seq.n_iter) {
           ok = issue_qk(it + 2);
           if (!ok) break;
         }
-        ok = mbar_wait(bar(Bars::VFULL + s), r & 1, error, 205) &&
-             mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 206);
+        PROF(-1);
+        const int slot = it & 3, j = it >> 2;
+        ok = mbar_wait(bar(Bars::PFULL + slot), j & 1, error, 204);
+        if (!ok) break;
+        PROF(11);
+        ok = mbar_wait(bar(Bars::VFULL + s), r & 1, error, 205);
+        PROF(12);
+        ok = ok && mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 206);
+        PROF(13);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + b * kTile);
+        const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + slot * kTile);
         const uint64_t desc_v = smem_desc_k128(sbase + SmemLayout::v + s * kTile);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_i8(tmem_o[b], desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
         mma_commit(bar(Bars::OFULL + b));
         mma_commit(bar(Bars::VEMPTY + s));
-        mma_commit(bar(Bars::PFREE + b));
+        mma_commit(bar(Bars::PFREE + slot));
       }
     }
   } else if (wg < 2) {
@@ -338,33 +378,52 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const float scale2 = a.sm_scale * kLog2e;
     const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
     const float* k_scale = a.k_scale + kvh * (n_k * 4);
-    unsigned char* p_row = smem + SmemLayout::p + b * kTile + row_in * 128;
-    float2* stat = stats + b * 128 + row_in;
-    uint16_t* my_sums = sums + (b * 128 + row_in) * 32;
     bool ok = true;
+    float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
+    if (b < seq.n_iter) {
+      const int first_tile = seq.tile(b);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + first_tile * 4 + g);
+    }
+    PROF_T0();
     for (int it = b; it < seq.n_iter && ok; it += 2) {
       const int u = it >> 1;
       const int tile = seq.tile(it);
       const bool last = it == seq.n_iter - 1;
       float sc[4];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) sc[g] = scale2 * (q_scale * __ldg(k_scale + tile * 4 + g));
-      // P buffer and the statistics slot of this group are free once P.V and the correction of
-      // its previous tile are done; S is ready when the MMA warp says so
-      ok = mbar_wait(bar(Bars::PFREE + b), (u & 1) ^ 1, error, 302) &&
-           mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 303) &&
-           mbar_wait(bar(Bars::SFULL + b), u & 1, error, 301);
+      for (int g = 0; g < 4; ++g) sc[g] = scale2 * (q_scale * ks_next[g]);
+      if (it + 2 < seq.n_iter) {  // next tile's K scales travel while this tile is processed
+        const int next_tile = seq.tile(it + 2);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + next_tile * 4 + g);
+      }
+      // The P buffer is free once P.V of this group's previous tile is done, the statistics slot
+      // once the correction group has read the tile four back; S is ready when the MMA warp says so.
+      const int slot = it & 3;
+      float2* stat = stats + slot * 128 + row_in;
+      uint16_t* my_sums = sums + (slot * 128 + row_in) * 32;
+      unsigned char* p_row = smem + SmemLayout::p + slot * kTile + row_in * 128;
+      ok = mbar_wait(bar(Bars::PFREE + slot), ((it >> 2) & 1) ^ 1, error, 302);
+      PROF(7);
+      ok = ok && mbar_wait(bar(Bars::STATFREE + slot), ((it >> 2) & 1) ^ 1, error, 303);
+      PROF(8);
+      ok = ok && mbar_wait(bar(Bars::SFULL + b), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
+      PROF(0);
       if (int_scores && !last)
-        softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums);
-      else
+        softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
+                                  bar(Bars::SFREE + b));
+      else {
         softmax_tile_general<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums, int_scores,
                                       last, a.is_causal != 0, row, tile * 128, a.k_len);
-      tc_fence_before();
-      mbar_arrive(bar(Bars::SFREE + b));
+        tc_fence_before();
+        mbar_arrive(bar(Bars::SFREE + b));
+      }
       fence_async_smem();
-      mbar_arrive(bar(Bars::PFULL + b));
+      mbar_arrive(bar(Bars::PFULL + slot));
+      PROF(1);
     }
   } else {
     // ------------------------------------------------------------------ correction + epilogue
@@ -382,16 +441,19 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < 128; ++i) O[i] = 0.0f;
     bool ok = true;
+    PROF_T0();
     for (int it = 0; it < seq.n_iter && ok; ++it) {
       const int b = it & 1, u = it >> 1;
       const bool last = it == seq.n_iter - 1;
-      ok = mbar_wait(bar(Bars::PFULL + b), u & 1, error, 401);
+      ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
       if (!ok) break;
-      const float2 stat = stats[b * 128 + row_in];
+      PROF(4);
+      const int slot = it & 3;
+      const float2 stat = stats[slot * 128 + row_in];
       const uint32_t numer = __float_as_uint(stat.y);
       const TileScales ts = tile_begin(st, stat.x);
       if constexpr (CAPTURE) {
-        const uint16_t* s16 = sums + (b * 128 + row_in) * 32;
+        const uint16_t* s16 = sums + (slot * 128 + row_in) * 32;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint16_t s4[8];
@@ -413,16 +475,24 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       } else {
         denominator_single(st, ts, numer);
       }
+      mbar_arrive(bar(Bars::STATFREE + slot));
       ok = mbar_wait(bar(Bars::OFULL + b), u & 1, error, 402);
       if (!ok) break;
       tc_fence_after();
+      PROF(5);
       const bool rescale = __any_sync(0xffffffffu, ts.o_scale != 1.0f);
       uint32_t acc[2][32];
       tmem_load32(tmem_o[b] + lane_base, acc[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         tmem_load_wait();
-        if (c < 3) tmem_load32(tmem_o[b] + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
+        if (c < 3) {
+          tmem_load32(tmem_o[b] + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
+        } else {
+          // the accumulator is in registers: P.V of the tile after next may overwrite it
+          tc_fence_before();
+          mbar_arrive(bar(Bars::OFREE + b));
+        }
         if (rescale) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) O[32 * c + i] *= ts.o_scale;
@@ -431,8 +501,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         for (int i = 0; i < 32; ++i)
           O[32 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), ts.w, O[32 * c + i]);
       }
-      tc_fence_before();
-      mbar_arrive(bar(Bars::OFREE + b));
+      PROF(6);
     }
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {
@@ -558,3 +627,11 @@ extern "C" int risa_b200_device_status(void) {
   }
   return RISA_B200_OK;
 }
+
+#ifdef RISA_TC_PROFILE
+extern "C" void risa_b200_prof_read(unsigned long long* out) {
+  cudaMemcpyFromSymbol(out, risa_b200::g_prof, sizeof(unsigned long long) * 16);
+  unsigned long long zero[16] = {0};
+  cudaMemcpyToSymbol(risa_b200::g_prof, zero, sizeof(zero));
+}
+#endif
