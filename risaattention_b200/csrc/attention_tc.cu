@@ -134,23 +134,23 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   const float tile_m = fmaxf(fmaxf(gm[0], gm[1]), fmaxf(gm[2], gm[3]));
   const float neg_m = -tile_m;
   uint32_t numer = 0;
-#pragma unroll
+  // One copy of the chunk body (rolled loop): the chunk is converted to floats as soon as it
+  // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
+#pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     tmem_load_wait();
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[0][i]));
     if (c < 3) {
-      tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
+      tmem_load32(tmem_row + 32 * (c + 1), raw[0]);
     } else {
       // all scores of the tile are in registers: the MMA warp may overwrite S with the next tile
       tc_fence_before();
       mbar_arrive(s_free_bar);
     }
-    float x[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[c & 1][i]));
     uint32_t P[8], s4[8];
-    tile_exp_chunk<kScoresInt>(x, sc, neg_m, P, s4);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) numer += s4[i];
+    tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, neg_m, P, numer, s4);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
@@ -204,10 +204,8 @@ __device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const fl
     float x[32];
     uint32_t P[8], s4[8];
     load_chunk(c, x);
-    if (int_scores) tile_exp_chunk<kScoresInt>(x, sc, -tile_m, P, s4);
-    else tile_exp_chunk<kScoresScaled>(x, sc, -tile_m, P, s4);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) numer += s4[i];
+    if (int_scores) tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, -tile_m, P, numer, s4);
+    else tile_exp_chunk<kScoresScaled, CAPTURE>(x, sc, -tile_m, P, numer, s4);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)

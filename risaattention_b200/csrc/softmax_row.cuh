@@ -98,32 +98,41 @@ __device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
   return s;
 }
 
-// U8 codes of four probabilities in [0, 255.5): adding 2^23 rounds to nearest-even into the low
+// Probabilities of one 32-key chunk.  P receives 8 packed words in storage order (word 4j+g = lane
+// g of 16-key group j), numer accumulates their U8 sum, s4 (optional) receives the sum of each word.
+// U8 codes: adding 2^23 to a probability in [0, 255.5) rounds it to nearest-even into the low
 // mantissa byte (the same integers cvt.rni.sat.u8 gives on this range) and three byte permutes pack
-// them, which keeps the conversion off the half-rate conversion pipe.
-__device__ __forceinline__ uint32_t pack_u8x4(float p0, float p1, float p2, float p3) {
-  const uint32_t a = __float_as_uint(p0 + 8388608.0f), b = __float_as_uint(p1 + 8388608.0f);
-  const uint32_t c = __float_as_uint(p2 + 8388608.0f), d = __float_as_uint(p3 + 8388608.0f);
-  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
-}
-
-// Probabilities of one 32-key chunk: P receives 8 packed words in storage order (word 4j+g = lane
-// g of 16-key group j), s4 the U8 sum of each word.
-template <int KIND>
+// four of them, which keeps the conversion off the half-rate conversion pipe.  The work is written
+// stage by stage over all 32 columns (scale, exponential, round, pack) so that 32 independent
+// operations are in flight per stage instead of one dependent chain per word.
+template <int KIND, bool WANT_SUMS>
 __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
-                                               uint32_t* P, uint32_t* s4) {
+                                               uint32_t* P, uint32_t& numer, uint32_t* s4) {
+  float p[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    p[i] = KIND == kScoresScaled ? x[i] + neg_m : fmaf(x[i], sc[(i & 7) >> 1], neg_m);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) p[i] = ex2_approx(p[i]);
+  uint32_t u[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(p[i] + 8388608.0f);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      float p[4];
+      const uint32_t lo = __byte_perm(u[lane_column(j, g, 0)], u[lane_column(j, g, 1)], 0x0040);
+      const uint32_t hi = __byte_perm(u[lane_column(j, g, 2)], u[lane_column(j, g, 3)], 0x0040);
+      P[4 * j + g] = __byte_perm(lo, hi, 0x5410);
+    }
+  }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float s = x[lane_column(j, g, e)];
-        p[e] = KIND == kScoresScaled ? ex2_approx(s + neg_m) : ex2_approx(fmaf(s, sc[g], neg_m));
-      }
-      P[4 * j + g] = pack_u8x4(p[0], p[1], p[2], p[3]);
-      s4[4 * j + g] = __dp4a(P[4 * j + g], 0x01010101u, 0u);
+  for (int w = 0; w < 8; ++w) {
+    if constexpr (WANT_SUMS) {
+      s4[w] = __dp4a(P[w], 0x01010101u, 0u);
+      numer += s4[w];
+    } else {
+      numer = __dp4a(P[w], 0x01010101u, numer);
     }
   }
 }
@@ -173,9 +182,7 @@ __device__ __forceinline__ TileResult softmax_tile(const float (&x)[CTA_K], cons
 #pragma unroll
   for (int c = 0; c < CTA_K / 32; ++c) {
     uint32_t s4[8];
-    tile_exp_chunk<KIND>(&x[32 * c], sc, -ts.tile_m, &P[8 * c], s4);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) numer += s4[i];
+    tile_exp_chunk<KIND, EXACT_D>(&x[32 * c], sc, -ts.tile_m, &P[8 * c], numer, s4);
     if constexpr (EXACT_D) denominator_chunk<LAST>(st, ts, c == 0, s4);
   }
   if constexpr (!EXACT_D) denominator_single(st, ts, numer);
