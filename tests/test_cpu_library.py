@@ -1,0 +1,87 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header declares, the
+Python API keeps the reference's names and error contracts, and nothing computes without a GPU."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "risa_b200.h").read_text()
+    declared = set(re.findall(r"\b(risa_b200_\w+)\s*\(", header))
+    assert len(declared) >= 12
+    lib = ctypes.CDLL(str(ROOT / "risaattention_b200" / "librisa_b200.so"))
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/risa_b200.h but not exported"
+    lib.risa_b200_abi_version.restype = ctypes.c_int
+    assert lib.risa_b200_abi_version() == 1
+
+
+def test_contract_violations_are_reported_not_computed():
+    lib = ctypes.CDLL(str(ROOT / "risaattention_b200" / "librisa_b200.so"))
+    lib.risa_b200_last_error.restype = ctypes.c_char_p
+    # null tensors / bad head_dim are rejected before any CUDA call
+    lib.risa_b200_quantize_v_workspace_size.restype = ctypes.c_size_t
+    assert lib.risa_b200_quantize_v_workspace_size(1, 4, 32768, 128) > 0
+    assert lib.risa_b200_quantize_v_workspace_size(0, 4, 32768, 128) == 0
+
+
+def test_public_names_match_reference():
+    import risaattention_b200 as risa
+
+    for name in ["KVPermutation", "prepare_kv_permutation", "PrequantizedInt8Attention",
+                 "RetainedMassPattern", "build_retained_mass_pattern",
+                 "construct_sparse_int8_attention",
+                 "construct_sparse_int8_attention_from_prequantized", "int8_attention",
+                 "int8_attention_from_prequantized", "int8_attention_is_available",
+                 "measure_pattern_recall", "prequantize_int8_attention", "sparse_int8_attention"]:
+        assert hasattr(risa, name)
+    assert sorted(risa.__all__) == sorted(n for n in risa.__all__)
+    fields = [f for f in risa.PrequantizedInt8Attention.__dataclass_fields__]
+    assert fields == ["q", "k", "v", "q_scale", "k_scale", "v_scale", "v_center",
+                      "original_head_dim", "input_dtype", "attention_scale", "cta_k", "attn_mask",
+                      "v_quantization", "is_causal", "lse_shift", "kv_permuted"]
+
+
+def test_no_cpu_fallback():
+    import risaattention_b200 as risa
+
+    assert not risa.int8_attention_is_available("cpu")
+    x = torch.zeros(1, 2, 4, 64)
+    with pytest.raises(ValueError, match="CUDA device"):
+        risa.int8_attention(x, x, x)
+    with pytest.raises(ValueError, match="shape"):
+        risa.int8_attention(x[0], x, x)
+    with pytest.raises(TypeError, match="float32, float16, or bfloat16"):
+        risa.int8_attention(x.double(), x.double(), x.double())
+
+
+def test_validation_helpers():
+    from risaattention_b200._validation import (apply_score_mask, pad_key_length,
+                                                select_key_block_size, uses_centered_values)
+
+    assert select_key_block_size(128, 1025, has_mask=False) == 128
+    assert select_key_block_size(128, 1024, has_mask=False) == 64
+    assert select_key_block_size(64, 4096, has_mask=False) == 64
+    assert select_key_block_size(256, 4096, has_mask=True) == 64
+    assert pad_key_length(1025, 128) == 1152
+    with pytest.raises(ValueError, match="v_quantization"):
+        uses_centered_values("fp8")
+    s = torch.zeros(1, 1, 3, 4)
+    m = apply_score_mask(s, None, True, 0)
+    assert torch.isneginf(m[0, 0, 0, 1:]).all() and m[0, 0, 2, 2] == 0
+
+
+def test_pattern_properties():
+    import risaattention_b200 as risa
+
+    p = risa.RetainedMassPattern(
+        row_offsets=torch.tensor([0, 2, 3], dtype=torch.int32),
+        block_indices=torch.tensor([0, 3, 1], dtype=torch.int32), batch_size=1, q_heads=1,
+        q_length=256, kv_length=512, query_block_size=128, key_block_size=128,
+        attention_scale=0.1, retained_mass_target=0.9, measured_retained_mass=0.95)
+    assert p.coverage == 3 / 8 and p.sparsity == 5 / 8 and p.index_bytes == 24
