@@ -82,6 +82,22 @@ def block_structured_inputs(seq_len, device, seed=0):
     return q, k, v, g
 
 
+def video_blocks_inputs(seq_len, device, seed=0, clusters=2, prototype_norm=8.0):
+    """The reference's own sparse-benchmark generator (benchmarks/sparse.py:33-52): N(0,1) q/k/v
+    plus, per KV head, `clusters` unit-direction prototypes of norm 8 added to Q and K by
+    128-token block (block index modulo clusters)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(B, HQ, seq_len, D, device=device, generator=g).bfloat16()
+    k = torch.randn(B, HKV, seq_len, D, device=device, generator=g).bfloat16()
+    v = torch.randn(B, HKV, seq_len, D, device=device, generator=g).bfloat16()
+    proto = torch.randn(B, HKV, clusters, D, device=device, generator=g)
+    proto *= prototype_norm / proto.norm(dim=-1, keepdim=True)
+    cluster = torch.arange(seq_len, device=device).div(128, rounding_mode="floor") % clusters
+    q = q + proto.repeat_interleave(HQ // HKV, dim=1)[:, :, cluster].to(q.dtype)
+    k = k + proto[:, :, cluster].to(k.dtype)
+    return q, k, v, g
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle sampling during the timed region."""
 
@@ -231,10 +247,13 @@ def reference_kernels_leg(q, k, v, seq_len, steps):
         return {"error": str(error)[:200]}
 
 
-def sparse_leg(seq_len, device, steps):
+def sparse_leg(seq_len, device, steps, generator="video_blocks"):
     import risaattention_b200 as risa
 
-    q, k, v, g = block_structured_inputs(seq_len, device)
+    if generator == "video_blocks":
+        q, k, v, g = video_blocks_inputs(seq_len, device)
+    else:
+        q, k, v, g = block_structured_inputs(seq_len, device)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     _, pattern = risa.construct_sparse_int8_attention(q, k, v, theta=0.99)
@@ -244,7 +263,10 @@ def sparse_leg(seq_len, device, steps):
         lambda: risa.construct_sparse_int8_attention(q, k, v, theta=0.99), 2, 1))
 
     def drift(x):
-        return (0.95 * x.float() + 0.05 * torch.randn(x.shape, device=device, generator=g)).bfloat16()
+        noise = torch.randn(x.shape, device=device, generator=g)
+        if generator == "video_blocks":  # additive drift, as the reference benchmark
+            return (x.float() + 0.05 * noise).bfloat16()
+        return (0.95 * x.float() + 0.05 * noise).bfloat16()
 
     q2, k2, v2 = drift(q), drift(k), drift(v)
     sparse_ms = event_time_ms(lambda: risa.sparse_int8_attention(q2, k2, v2, pattern), steps, 3)
@@ -252,7 +274,9 @@ def sparse_leg(seq_len, device, steps):
     return {"seq_len": seq_len, "theta": 0.99, "coverage": pattern.coverage,
             "construct_ms": construct_ms, "sparse_ms": sparse_ms, "dense_ms": dense_ms,
             "speedup_vs_dense": dense_ms / sparse_ms,
-            "inputs": "per-128-token-block centroids + 0.5 N(0,1); reuse on 0.95 x + 0.05 N(0,1)"}
+            "inputs": ("reference generator: 2 alternating prototypes of norm 8 per KV head added to "
+                       "N(0,1) Q/K, additive drift 0.05" if generator == "video_blocks" else
+                       "per-128-token-block centroids + 0.5 N(0,1); reuse on 0.95 x + 0.05 N(0,1)")}
 
 
 def run_ours(args):
@@ -361,6 +385,8 @@ def run_ours(args):
         if not args.no_sparse:
             try:
                 line["sparse_reuse"] = sparse_leg(L, device, max(3, args.steps // 2))
+                line["sparse_reuse_block_centroids"] = sparse_leg(L, device, max(3, args.steps // 2),
+                                                                  "block_centroids")
             except Exception as error:
                 line["sparse_reuse"] = {"error": str(error)[:200]}
         if not args.no_cpu:
