@@ -59,6 +59,28 @@ int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_
                          const int32_t* perm, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* V quantisation for callers that must not allocate.  Some users of this library cannot obtain
+ * device memory at call time: a serving process that fixes its memory budget at start-up and
+ * forbids cudaMalloc afterwards (it stalls every stream of the device and can fail once memory is
+ * fragmented), or a host runtime bound through cgo / JNI / ctypes that owns no device allocator at
+ * all.  For them the scratch of risa_b200_quantize_v lives inside the library, in a fixed device
+ * array of risa_b200_quantize_v_static_limit() bytes (4 MiB) that every GPU loading the library
+ * keeps until the process exits.  The caller passes inputs and outputs only; the call allocates
+ * nothing and frees nothing.  Problems whose risa_b200_quantize_v_workspace_size() exceeds the limit
+ * are refused with RISA_B200_INVALID (B*Hkv*D = 512 channels at 32768 keys need 1.25 MiB).
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call before any stream capture starts.  All calls on a device share the one
+ * array: it keeps the previous call's contents (nothing needs clearing, every word read is written
+ * earlier in the same call), and two calls that overlap on the GPU -- different streams without
+ * ordering -- race on it.  Results are identical to risa_b200_quantize_v.  No counterpart in the
+ * reference, whose V kernel needs no scratch. */
+size_t risa_b200_quantize_v_static_limit(void);
+int risa_b200_quantize_v_static(const void* v, void* v_codes, float* v_scale, float* v_center,
+                                int batch, int kv_heads, int k_len, int head_dim, int padded_len,
+                                int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                int dtype_code, int midpoint_affine, const int32_t* perm,
+                                void* stream);
+
 /* Fused INT8 attention over packed operands: dense, masked, causal, CSR sparse reuse, block-mass
  * capture, optional LSE.  Replaces launch_attention (csrc/launchers.h:49-60; kernels
  * csrc/kernels/attention_int8.cuh:145-1088, attention_dispatch.cu:113-296).  Same argument

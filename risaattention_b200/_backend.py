@@ -28,6 +28,9 @@ _SIGNATURES = {
     "risa_b200_quantize_v_workspace_size": (c_sz, [c_i32] * 4),
     "risa_b200_quantize_v": (
         c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 3 + [c_i32] * 2 + [c_vp, c_vp, c_sz, c_vp]),
+    "risa_b200_quantize_v_static_limit": (c_sz, []),
+    "risa_b200_quantize_v_static": (
+        c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 3 + [c_i32] * 2 + [c_vp, c_vp]),
     "risa_b200_attention": (
         c_i32,
         [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,

@@ -15,6 +15,7 @@
 // Compiled with --use_fast_math like the reference so 1.f / x and x / float(L) lower identically.
 #include "common.cuh"
 #include <cfloat>
+#include <mutex>
 
 namespace risa_b200 {
 namespace {
@@ -277,4 +278,62 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
     }
   });
   return check_launch("quantize_v");
+}
+
+// ---- allocation-free variant --------------------------------------------------------------------
+// Scratch for callers that cannot hand over device memory of their own.  The array lives in the
+// library's device image: every GPU that loads the library carries these bytes until the process
+// exits, which is why the ceiling is kept modest.
+namespace {
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_v_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// In host code `g_v_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use has to be asked for, per device, with that device current.
+int static_scratch_for_current_device(void** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail(RISA_B200_CUDA, "quantize_v_static: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= kMaxDevices)
+    return fail(RISA_B200_INVALID, "quantize_v_static: device index %d not supported", device);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_v_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(RISA_B200_CUDA, "quantize_v_static: cannot resolve the scratch array: %s",
+                  cudaGetErrorString(e));
+    g_static_scratch_ptr[device] = ptr;
+  }
+  *out = g_static_scratch_ptr[device];
+  return RISA_B200_OK;
+}
+}  // namespace
+
+extern "C" size_t risa_b200_quantize_v_static_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int risa_b200_quantize_v_static(const void* v, void* v_codes, float* v_scale,
+                                           float* v_center, int batch, int kv_heads, int k_len,
+                                           int head_dim, int padded_len, int64_t stride_b,
+                                           int64_t stride_h, int64_t stride_n, int dtype_code,
+                                           int midpoint_affine, const int32_t* perm,
+                                           void* stream_ptr) {
+  const size_t need = risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim);
+  RISA_REQUIRE(need != 0, "quantize_v_static: sizes must be positive");
+  RISA_REQUIRE(need <= kStaticScratchBytes,
+               "quantize_v_static: this problem needs %zu bytes of scratch but the built-in "
+               "scratch holds %zu; use risa_b200_quantize_v with a caller workspace",
+               need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int status = static_scratch_for_current_device(&scratch);
+  if (status != RISA_B200_OK) return status;
+  // Nothing in the scratch has to start at zero: the range and residual partials a call reads are
+  // all written earlier in the same call.  Whatever the previous call left is simply overwritten.
+  return risa_b200_quantize_v(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
+                              padded_len, stride_b, stride_h, stride_n, dtype_code,
+                              midpoint_affine, perm, scratch, kStaticScratchBytes, stream_ptr);
 }
