@@ -12,9 +12,8 @@
 //   WG2        correction.  Thread r owns the FP32 output row r in registers and everything that is
 //              sequential over tiles: running maximum, denominator, per-tile weights,
 //              O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
-//   WG3        warp 12: TMA producer (Q, K ring, V ring); warp 13: MMA issue (one thread); QK^T of
-//              tile t+2 is issued right after P.V of tile t, so the tensor pipe never waits for the
-//              softmax of the tile it just produced.
+//   WG3        warp 12: TMA producer (Q, K ring, V ring); warp 13: one thread issues the QK^T MMAs,
+//              two tiles ahead of the softmax; warp 14: one thread issues the P.V MMAs.
 // Tensor memory (512 columns): S double-buffered (2 x 128, one per softmax group), P.V accumulator
 // double-buffered (2 x 128).  Probabilities are scaled to the tile maximum (full 8-bit resolution
 // in every tile), so each tile's integer P.V has its own weight and is folded into FP32 by the
@@ -60,7 +59,7 @@ struct SmemLayout {
   static constexpr int stats = p + 4 * kTile;             // float2 [4][128]: tile max, U8 sum
   static constexpr int sums = stats + 4 * 128 * 8;        // uint16 [4][128][32] (capture only)
   static constexpr int bars = sums + 4 * 128 * 64;        // 8-byte mbarriers
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int total = tmem_slot + 16;
 };
@@ -92,12 +91,13 @@ __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t
 struct Bars {
   uint32_t base;
   static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
-                       VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages, SFREE = SFULL + 2,
-                       PFULL = SFREE + 2, PFREE = PFULL + 4, OFULL = PFREE + 4, OFREE = OFULL + 2,
-                       STATFREE = OFREE + 2;
-  // S and the P.V accumulator have two buffers (tile it uses it & 1); the probability tiles and the
-  // per-row statistics have four slots (it & 3), so a softmax group can start its next tile while
-  // P.V and the correction of its previous one are still in flight.
+                       VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages, SFREE = SFULL + 3,
+                       PFULL = SFREE + 3, PFREE = PFULL + 4, OFULL = PFREE + 4, OFREE = OFULL + 1,
+                       STATFREE = OFREE + 1;
+  // S has three buffers (tile it uses it % 3), so the scores of a group's next tile are computed
+  // while it is still busy with the current one; the P.V accumulator has one buffer, handed back
+  // as soon as the correction group has it in registers; the probability tiles and the per-row
+  // statistics have four slots (it & 3).
   __device__ __forceinline__ uint32_t operator()(int i) const { return base + 8u * i; }
 };
 
@@ -111,6 +111,9 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   uint32_t raw[2][32];
   int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
   PROF_T0();
+#ifdef RISA_ABLATE_PASS1
+  imax[0] = imax[1] = imax[2] = imax[3] = 100000;
+#else
   tmem_load32(tmem_row, raw[0]);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -126,6 +129,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
       imax[g] = __vimax3_s32(imax[g], int(r[24 + 2 * g]), int(r[25 + 2 * g]));
     }
   }
+#endif
   tmem_load32(tmem_row, raw[0]);
   PROF(2);
   float gm[4];
@@ -138,7 +142,9 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
+    PROF(-1);
     tmem_load_wait();
+    PROF(9);
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[0][i]));
@@ -149,16 +155,23 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
       tc_fence_before();
       mbar_arrive(s_free_bar);
     }
+    PROF(10);
     uint32_t P[8], s4[8];
     tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, neg_m, P, numer, s4);
+    PROF(11);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
         *reinterpret_cast<uint32_t*>(sums + 8 * c + i) = s4[i] | (s4[i + 1] << 16);
     }
+#ifndef RISA_ABLATE_PSTORE
     *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ swz) << 4)) = make_uint4(P[0], P[1], P[2], P[3]);
     *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ swz) << 4)) =
         make_uint4(P[4], P[5], P[6], P[7]);
+#else
+    numer += P[0] ^ P[1] ^ P[2] ^ P[3] ^ P[4] ^ P[5] ^ P[6] ^ P[7];
+#endif
+    PROF(12);
   }
   *stat = make_float2(tile_m, __uint_as_float(numer));
   PROF(3);
@@ -246,12 +259,12 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       mbar_init(bar(Bars::VFULL + s), 1);
       mbar_init(bar(Bars::VEMPTY + s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 3; ++b) {
       mbar_init(bar(Bars::SFULL + b), 1);
       mbar_init(bar(Bars::SFREE + b), 128);
-      mbar_init(bar(Bars::OFULL + b), 1);
-      mbar_init(bar(Bars::OFREE + b), 128);
     }
+    mbar_init(bar(Bars::OFULL), 1);
+    mbar_init(bar(Bars::OFREE), 128);
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(Bars::STATFREE + i), 128);
       mbar_init(bar(Bars::PFULL + i), 128);
@@ -264,8 +277,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::tmem_slot);
-  const uint32_t tmem_s[2] = {tmem, tmem + 128};
-  const uint32_t tmem_o[2] = {tmem + 256, tmem + 384};
+  const uint32_t tmem_o = tmem + 384;  // S buffers at columns 0, 128, 256
 
   const TileSeq seq = tile_sequence(a, bh, bx, n_q, n_k, CAPTURE);
   float2* stats = reinterpret_cast<float2*>(smem + SmemLayout::stats);
@@ -286,21 +298,33 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       for (int step = 0; step < seq.n_iter + 2 && ok; ++step) {
         if (step < seq.n_iter) {
           const int s = step % kKStages, r = step / kKStages;
-          ok = mbar_wait(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
+          ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
           if (!ok) break;
+#ifdef RISA_ABLATE_TMA
+          if (step >= kKStages) mbar_arrive(bar(Bars::KFULL + s)); else {
+#endif
           mbar_expect_tx(bar(Bars::KFULL + s), kTile);
           tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
                       seq.tile(step) * 128, int(kvh));
+#ifdef RISA_ABLATE_TMA
+          }
+#endif
           k_issued = step + 1;
         }
         const int it = step - 2;
         if (it >= 0) {
           const int s = it % kVStages, r = it / kVStages;
-          ok = mbar_wait(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
+          ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
           if (!ok) break;
+#ifdef RISA_ABLATE_TMA
+          if (it >= kVStages) mbar_arrive(bar(Bars::VFULL + s)); else {
+#endif
           mbar_expect_tx(bar(Bars::VFULL + s), kTile);
           tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
                       seq.tile(it) * 128, 0, int(kvh));
+#ifdef RISA_ABLATE_TMA
+          }
+#endif
           v_issued = it + 1;
         }
       }
@@ -313,54 +337,47 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           mbar_wait(bar(Bars::VFULL + it % kVStages), (it / kVStages) & 1, error, 106);
       }
     } else if (warp == 13 && lane == 0) {
-      // ---------------------------------------------------------------- MMA issue
+      // ---------------------------------------------------------------- MMA issue: S = Q.K^T
+      // Tile it goes to S buffer it & 1 as soon as the softmax group has read that buffer's
+      // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
+      // round-trips on each, which otherwise bound the whole pipeline.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, 128);
-      constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
       const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
-      bool ok = mbar_wait(bar(Bars::QFULL), 0, error, 201);
-      PROF_T0();
-      auto issue_qk = [&](int it) -> bool {
-        const int b = it & 1, u = it >> 1, s = it % kKStages, r = it / kKStages;
-        PROF(-1);
-        if (!mbar_wait(bar(Bars::KFULL + s), r & 1, error, 202)) return false;
-        PROF(9);
-        if (!mbar_wait(bar(Bars::SFREE + b), (u & 1) ^ 1, error, 203)) return false;
-        PROF(10);
+      bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
+      for (int it = 0; it < seq.n_iter && ok; ++it) {
+        const int b = it % 3, u = it / 3, s = it % kKStages, r = it / kKStages;
+        ok = mbar_wait2<true>(bar(Bars::KFULL + s), r & 1, bar(Bars::SFREE + b), (u & 1) ^ 1,
+                              error, 202);
+        if (!ok) break;
         tc_fence_after();
         const uint64_t desc_k = smem_desc_k128(sbase + SmemLayout::k + s * kTile);
+#ifndef RISA_ABLATE_QK
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          mma_i8(tmem_s[b], desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
+          mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
+#endif
         mma_commit(bar(Bars::SFULL + b));
         mma_commit(bar(Bars::KEMPTY + s));
-        return true;
-      };
-      if (ok && seq.n_iter > 0) ok = issue_qk(0);
-      if (ok && seq.n_iter > 1) ok = issue_qk(1);
+      }
+    } else if (warp == 14 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issue: P.V
+      constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
+      bool ok = true;
       for (int it = 0; it < seq.n_iter && ok; ++it) {
-        const int b = it & 1, u = it >> 1, s = it % kVStages, r = it / kVStages;
-        // the group that is finishing tile `it` gets its next scores as soon as it has read S
-        if (it + 2 < seq.n_iter) {
-          ok = issue_qk(it + 2);
-          if (!ok) break;
-        }
-        PROF(-1);
+        const int s = it % kVStages, r = it / kVStages;
         const int slot = it & 3, j = it >> 2;
-        ok = mbar_wait(bar(Bars::PFULL + slot), j & 1, error, 204);
-        if (!ok) break;
-        PROF(11);
-        ok = mbar_wait(bar(Bars::VFULL + s), r & 1, error, 205);
-        PROF(12);
-        ok = ok && mbar_wait(bar(Bars::OFREE + b), (u & 1) ^ 1, error, 206);
-        PROF(13);
+        ok = mbar_wait3<true>(bar(Bars::PFULL + slot), j & 1, bar(Bars::VFULL + s), r & 1,
+                              bar(Bars::OFREE), (it & 1) ^ 1, error, 204);
         if (!ok) break;
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + slot * kTile);
         const uint64_t desc_v = smem_desc_k128(sbase + SmemLayout::v + s * kTile);
+#ifndef RISA_ABLATE_PV
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          mma_i8(tmem_o[b], desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
-        mma_commit(bar(Bars::OFULL + b));
+          mma_i8(tmem_o, desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
+#endif
+        mma_commit(bar(Bars::OFULL));
         mma_commit(bar(Bars::VEMPTY + s));
         mma_commit(bar(Bars::PFREE + slot));
       }
@@ -371,7 +388,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int b = wg;
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
-    const uint32_t tmem_row = tmem_s[b] + (uint32_t((warp & 3) * 32) << 16);
+    const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
     const bool int_scores = !a.is_causal && a.sm_scale > 0.0f;
     const float scale2 = a.sm_scale * kLog2e;
     const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
@@ -385,7 +402,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     }
     PROF_T0();
     for (int it = b; it < seq.n_iter && ok; it += 2) {
-      const int u = it >> 1;
+      const int sb = it % 3, u = it / 3;
+      const uint32_t tmem_row = tmem_lane + 128 * sb;
       const int tile = seq.tile(it);
       const bool last = it == seq.n_iter - 1;
       float sc[4];
@@ -402,22 +420,19 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       float2* stat = stats + slot * 128 + row_in;
       uint16_t* my_sums = sums + (slot * 128 + row_in) * 32;
       unsigned char* p_row = smem + SmemLayout::p + slot * kTile + row_in * 128;
-      ok = mbar_wait(bar(Bars::PFREE + slot), ((it >> 2) & 1) ^ 1, error, 302);
-      PROF(7);
-      ok = ok && mbar_wait(bar(Bars::STATFREE + slot), ((it >> 2) & 1) ^ 1, error, 303);
-      PROF(8);
-      ok = ok && mbar_wait(bar(Bars::SFULL + b), u & 1, error, 301);
+      ok = mbar_wait3(bar(Bars::PFREE + slot), ((it >> 2) & 1) ^ 1, bar(Bars::STATFREE + slot),
+                      ((it >> 2) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
       PROF(0);
       if (int_scores && !last)
         softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
-                                  bar(Bars::SFREE + b));
+                                  bar(Bars::SFREE + sb));
       else {
         softmax_tile_general<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums, int_scores,
                                       last, a.is_causal != 0, row, tile * 128, a.k_len);
         tc_fence_before();
-        mbar_arrive(bar(Bars::SFREE + b));
+        mbar_arrive(bar(Bars::SFREE + sb));
       }
       fence_async_smem();
       mbar_arrive(bar(Bars::PFULL + slot));
@@ -440,66 +455,84 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     for (int i = 0; i < 128; ++i) O[i] = 0.0f;
     bool ok = true;
     PROF_T0();
-    for (int it = 0; it < seq.n_iter && ok; ++it) {
-      const int b = it & 1, u = it >> 1;
-      const bool last = it == seq.n_iter - 1;
-      ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
-      if (!ok) break;
-      PROF(4);
-      const int slot = it & 3;
-      const float2 stat = stats[slot * 128 + row_in];
-      const uint32_t numer = __float_as_uint(stat.y);
-      const TileScales ts = tile_begin(st, stat.x);
-      if constexpr (CAPTURE) {
-        const uint16_t* s16 = sums + (slot * 128 + row_in) * 32;
+    // Software-pipelined by one tile: the statistics of tile `it` (running maximum, denominator,
+    // weights) are consumed as soon as its probabilities exist, while the accumulator that is
+    // folded into O in the same iteration is the one of tile it - 1, whose P.V had the whole
+    // softmax time of tile `it` to finish.  The group therefore never idles on a P.V in flight.
+    float prev_o_scale = 1.0f, prev_w = 0.0f;
+    for (int it = 0; it <= seq.n_iter && ok; ++it) {
+      float cur_o_scale = 1.0f, cur_w = 0.0f;
+      if (it < seq.n_iter) {
+        const bool last = it == seq.n_iter - 1;
+        ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
+        if (!ok) break;
+        PROF(4);
+        const int slot = it & 3;
+        const float2 stat = stats[slot * 128 + row_in];
+        const uint32_t numer = __float_as_uint(stat.y);
+        const TileScales ts = tile_begin(st, stat.x);
+        cur_o_scale = ts.o_scale;
+        cur_w = ts.w;
+        if constexpr (CAPTURE) {
+          const uint16_t* s16 = sums + (slot * 128 + row_in) * 32;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint16_t s4[8];
+            *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
+            if (last) denominator_chunk<true>(st, ts, c == 0, s4);
+            else denominator_chunk<false>(st, ts, c == 0, s4);
+          }
+          if (row_ok) {
+            if (last) {
+              float* out = cap.last + grow * 2;
+              out[0] = static_cast<float>(numer);
+              out[1] = ts.tile_m;
+            } else {
+              uint32_t* out = cap.full + (grow * (n_k - 1) + it) * 2;
+              out[0] = numer;
+              out[1] = __float_as_uint(ts.tile_m);
+            }
+          }
+        } else {
+          denominator_single(st, ts, numer);
+        }
+        mbar_arrive(bar(Bars::STATFREE + slot));
+      }
+      if (it >= 1) {
+        const int j = it - 1;
+        ok = mbar_wait(bar(Bars::OFULL), j & 1, error, 402);
+        if (!ok) break;
+        tc_fence_after();
+        PROF(5);
+        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
+        uint32_t acc[2][32];
+        tmem_load32(tmem_o + lane_base, acc[0]);
+#ifdef RISA_TC_PROFILE
+        tmem_load_wait();
+        PROF(14);
+#endif
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint16_t s4[8];
-          *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
-          if (last) denominator_chunk<true>(st, ts, c == 0, s4);
-          else denominator_chunk<false>(st, ts, c == 0, s4);
-        }
-        if (row_ok) {
-          if (last) {
-            float* slot = cap.last + grow * 2;
-            slot[0] = static_cast<float>(numer);
-            slot[1] = ts.tile_m;
+          tmem_load_wait();
+          if (c < 3) {
+            tmem_load32(tmem_o + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
           } else {
-            uint32_t* slot = cap.full + (grow * (n_k - 1) + it) * 2;
-            slot[0] = numer;
-            slot[1] = __float_as_uint(ts.tile_m);
+            // the accumulator is in registers: P.V of the tile after next may overwrite it
+            tc_fence_before();
+            mbar_arrive(bar(Bars::OFREE));
           }
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) O[32 * c + i] *= prev_o_scale;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            O[32 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), prev_w, O[32 * c + i]);
         }
-      } else {
-        denominator_single(st, ts, numer);
+        PROF(6);
       }
-      mbar_arrive(bar(Bars::STATFREE + slot));
-      ok = mbar_wait(bar(Bars::OFULL + b), u & 1, error, 402);
-      if (!ok) break;
-      tc_fence_after();
-      PROF(5);
-      const bool rescale = __any_sync(0xffffffffu, ts.o_scale != 1.0f);
-      uint32_t acc[2][32];
-      tmem_load32(tmem_o[b] + lane_base, acc[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_load_wait();
-        if (c < 3) {
-          tmem_load32(tmem_o[b] + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
-        } else {
-          // the accumulator is in registers: P.V of the tile after next may overwrite it
-          tc_fence_before();
-          mbar_arrive(bar(Bars::OFREE + b));
-        }
-        if (rescale) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) O[32 * c + i] *= ts.o_scale;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          O[32 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), ts.w, O[32 * c + i]);
-      }
-      PROF(6);
+      prev_o_scale = cur_o_scale;
+      prev_w = cur_w;
     }
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {

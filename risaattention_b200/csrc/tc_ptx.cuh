@@ -33,9 +33,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-// The hint lets the hardware park the thread until the phase completes (or the time passes)
-// instead of spinning through issue slots that the working warps of the same scheduler need.
-constexpr uint32_t kSuspendHintNs = 100000;
+// Non-blocking test of a phase (no suspend): used for the fast path and by the issue warps, whose
+// waits sit on the critical path of every tile.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Same with a suspend-time hint: the hardware may park the thread until the phase completes (or the
+// time passes) instead of spinning through issue slots that the working warps of the same
+// scheduler need.  Used by the softmax and correction groups when a first test fails.
+#ifndef RISA_SUSPEND_HINT_NS
+#define RISA_SUSPEND_HINT_NS 2000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -45,7 +63,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
+      : "r"(bar), "r"(parity), "r"(uint32_t(RISA_SUSPEND_HINT_NS))
       : "memory");
   return ok != 0;
 }
@@ -54,20 +72,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // site in *error and reports failure, so a protocol bug ends the kernel instead of hanging the GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
+template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* error,
                                           unsigned int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test(bar, parity)) return true;
   const uint64_t start = global_timer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 16; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < (SPIN ? 256 : 16); ++i)
+      if (SPIN ? mbar_test(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if (*reinterpret_cast<volatile unsigned int*>(error) != 0) return false;  // someone gave up
     if (global_timer_ns() - start > kWaitLimitNs) {
       atomicCAS(error, 0u, site);
       return false;
     }
   }
+}
+
+// Waits for several phases at once: the tests are issued back to back so their latencies overlap
+// (in steady state all of them are already complete), then any that failed is waited for in turn.
+template <bool SPIN = false>
+__device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
+                                           unsigned int* error, unsigned int site) {
+  const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1);
+  if (r0 & r1) return true;
+  return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
+         (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1));
+}
+template <bool SPIN = false>
+__device__ __forceinline__ bool mbar_wait3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
+                                           uint32_t b2, uint32_t p2, unsigned int* error,
+                                           unsigned int site) {
+  const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1), r2 = mbar_test(b2, p2);
+  if (r0 & r1 & r2) return true;
+  return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
+         (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1)) &&
+         (r2 || mbar_wait<SPIN>(b2, p2, error, site + 2));
 }
 
 // ---- proxies / fences --------------------------------------------------------------------------
