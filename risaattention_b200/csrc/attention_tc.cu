@@ -3,17 +3,17 @@
 // TMA into 128-byte-swizzled shared memory; the FP32 online softmax, the per-tile FP32 rescale of
 // the output and the epilogue run on ordinary warps that read the accumulators with tcgen05.ld.
 //
-// One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Four warpgroups:
-//   WG0 / WG1  softmax of even / odd tiles.  Thread r owns query row r (tensor-memory lane r) and
+// One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Five warpgroups:
+//   WG0-WG2    softmax of tiles it % 3 == 0 / 1 / 2.  Thread r owns query row r (tensor-memory lane r) and
 //              makes two passes over the tile's 128 scores: maxima, then U8 probabilities written to
 //              shared memory as the A operand of P.V (bytes placed in the packed V order).  The U8
 //              codes depend only on the TILE maximum, so the two groups work on different tiles at
 //              the same time with no state shared between them.
-//   WG2        correction.  Thread r owns the FP32 output row r in registers and everything that is
+//   WG3        correction.  Thread r owns the FP32 output row r in registers and everything that is
 //              sequential over tiles: running maximum, denominator, per-tile weights,
 //              O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
-//   WG3        warp 12: TMA producer (Q, K ring, V ring); warp 13: one thread issues the QK^T MMAs,
-//              two tiles ahead of the softmax; warp 14: one thread issues the P.V MMAs.
+//   WG4        warp 16: TMA producer (Q, K ring, V ring); warp 17: one thread issues the QK^T MMAs,
+//              ahead of the softmax; warp 18: one thread issues the P.V MMAs.
 // Tensor memory (512 columns): S double-buffered (2 x 128, one per softmax group), P.V accumulator
 // double-buffered (2 x 128).  Probabilities are scaled to the tile maximum (full 8-bit resolution
 // in every tile), so each tile's integer P.V has its own weight and is folded into FP32 by the
@@ -38,8 +38,15 @@ using namespace tc;
 constexpr int kKStages = 3;           // K ring depth (K runs two tiles ahead of V)
 constexpr int kVStages = 3;           // V ring depth
 constexpr int kTile = 128 * 128;      // bytes of one 128 x 128 INT8 tile
-constexpr int kThreads = 512;
-constexpr int kRegsSoftmax = 120, kRegsCorrection = 216, kRegsIssue = 40;
+constexpr int kThreads = 640;
+constexpr int kSoftmaxGroups = 3;     // softmax warpgroups; tile it is handled by group it % 3
+constexpr int kRegsLaunch = 96;        // what ptxas gives 640 threads (65536 / 640, multiple of 8)
+constexpr int kRegsSoftmax = 96, kRegsCorrection = 168, kRegsIssue = 24;
+// setmaxnreg redistributes the registers the CTA was launched with (threads x launch count); a
+// request beyond that pool would block forever, outside the reach of the bounded barrier waits.
+static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue) <=
+                  kThreads * kRegsLaunch,
+              "register budget exceeds the launch pool");
 
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
 #ifdef RISA_TC_PROFILE
@@ -157,7 +164,11 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     }
     PROF(10);
     uint32_t P[8], s4[8];
+#ifndef RISA_ABLATE_PASS2
     tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, neg_m, P, numer, s4);
+#else
+    for (int i = 0; i < 8; ++i) { P[i] = __float_as_uint(x[4 * i]); s4[i] = 0; }
+#endif
     PROF(11);
     if constexpr (CAPTURE) {
 #pragma unroll
@@ -272,7 +283,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     }
     mbar_init_fence();
   }
-  if (warp == 13) tmem_alloc(sbase + SmemLayout::tmem_slot, 512);
+  if (warp == 17) tmem_alloc(sbase + SmemLayout::tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -283,9 +294,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   float2* stats = reinterpret_cast<float2*>(smem + SmemLayout::stats);
   uint16_t* sums = reinterpret_cast<uint16_t*>(smem + SmemLayout::sums);
 
-  if (wg == 3) {
+  if (wg == 4) {
     regs_dec<kRegsIssue>();
-    if (warp == 12 && lane == 0) {
+    if (warp == 16 && lane == 0) {
       // ---------------------------------------------------------------- producer
       tma_prefetch_descriptor(&map_q);
       tma_prefetch_descriptor(&map_k);
@@ -336,7 +347,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         for (int it = max(0, v_issued - kVStages); it < v_issued; ++it)
           mbar_wait(bar(Bars::VFULL + it % kVStages), (it / kVStages) & 1, error, 106);
       }
-    } else if (warp == 13 && lane == 0) {
+    } else if (warp == 17 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: S = Q.K^T
       // Tile it goes to S buffer it & 1 as soon as the softmax group has read that buffer's
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
@@ -359,7 +370,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         mma_commit(bar(Bars::SFULL + b));
         mma_commit(bar(Bars::KEMPTY + s));
       }
-    } else if (warp == 14 && lane == 0) {
+    } else if (warp == 18 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: P.V
       constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
       bool ok = true;
@@ -382,9 +393,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         mma_commit(bar(Bars::PFREE + slot));
       }
     }
-  } else if (wg < 2) {
-    // ------------------------------------------------------------------ softmax of tiles it = wg, wg+2, ...
-    regs_dec<kRegsSoftmax>();
+  } else if (wg < kSoftmaxGroups) {
+    // ------------------------------------------------------------------ softmax of tiles it = wg, wg+3, ...
+    if constexpr (kRegsSoftmax > kRegsLaunch) regs_inc<kRegsSoftmax>();
     const int b = wg;
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
@@ -401,7 +412,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + first_tile * 4 + g);
     }
     PROF_T0();
-    for (int it = b; it < seq.n_iter && ok; it += 2) {
+    for (int it = b; it < seq.n_iter && ok; it += kSoftmaxGroups) {
       const int sb = it % 3, u = it / 3;
       const uint32_t tmem_row = tmem_lane + 128 * sb;
       const int tile = seq.tile(it);
@@ -409,8 +420,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       float sc[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) sc[g] = scale2 * (q_scale * ks_next[g]);
-      if (it + 2 < seq.n_iter) {  // next tile's K scales travel while this tile is processed
-        const int next_tile = seq.tile(it + 2);
+      if (it + kSoftmaxGroups < seq.n_iter) {  // next tile's K scales travel during this tile
+        const int next_tile = seq.tile(it + kSoftmaxGroups);
 #pragma unroll
         for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + next_tile * 4 + g);
       }
@@ -505,29 +516,25 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         tc_fence_after();
         PROF(5);
         const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
-        uint32_t acc[2][32];
-        tmem_load32(tmem_o + lane_base, acc[0]);
-#ifdef RISA_TC_PROFILE
-        tmem_load_wait();
-        PROF(14);
-#endif
+        uint32_t acc[2][16];
+        tmem_load16(tmem_o + lane_base, acc[0]);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 8; ++c) {
           tmem_load_wait();
-          if (c < 3) {
-            tmem_load32(tmem_o + lane_base + 32 * (c + 1), acc[(c + 1) & 1]);
+          if (c < 7) {
+            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc[(c + 1) & 1]);
           } else {
-            // the accumulator is in registers: P.V of the tile after next may overwrite it
+            // the accumulator is in registers: P.V of the next tile may overwrite it
             tc_fence_before();
             mbar_arrive(bar(Bars::OFREE));
           }
           if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) O[32 * c + i] *= prev_o_scale;
+            for (int i = 0; i < 16; ++i) O[16 * c + i] *= prev_o_scale;
           }
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            O[32 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), prev_w, O[32 * c + i]);
+          for (int i = 0; i < 16; ++i)
+            O[16 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), prev_w, O[16 * c + i]);
         }
         PROF(6);
       }
@@ -572,7 +579,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -666,3 +673,4 @@ extern "C" void risa_b200_prof_read(unsigned long long* out) {
   cudaMemcpyToSymbol(risa_b200::g_prof, zero, sizeof(zero));
 }
 #endif
+

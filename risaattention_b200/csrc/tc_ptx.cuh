@@ -72,7 +72,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // site in *error and reports failure, so a protocol bug ends the kernel instead of hanging the GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-template <bool SPIN = false>
+#ifdef RISA_ALL_SPIN
+#define RISA_SPIN_DEFAULT true
+#else
+#define RISA_SPIN_DEFAULT false
+#endif
+template <bool SPIN = RISA_SPIN_DEFAULT>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* error,
                                           unsigned int site) {
   if (mbar_test(bar, parity)) return true;
@@ -91,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
 
 // Waits for several phases at once: the tests are issued back to back so their latencies overlap
 // (in steady state all of them are already complete), then any that failed is waited for in turn.
-template <bool SPIN = false>
+template <bool SPIN = RISA_SPIN_DEFAULT>
 __device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
                                            unsigned int* error, unsigned int site) {
   const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1);
@@ -99,7 +104,7 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1
   return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
          (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1));
 }
-template <bool SPIN = false>
+template <bool SPIN = RISA_SPIN_DEFAULT>
 __device__ __forceinline__ bool mbar_wait3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
                                            uint32_t b2, uint32_t p2, unsigned int* error,
                                            unsigned int site) {
