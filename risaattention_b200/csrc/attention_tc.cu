@@ -4,20 +4,20 @@
 // the output and the epilogue run on ordinary warps that read the accumulators with tcgen05.ld.
 //
 // One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Five warpgroups:
-//   WG0-WG2    softmax of tiles it % 3 == 0 / 1 / 2.  Thread r owns query row r (tensor-memory lane r) and
-//              makes two passes over the tile's 128 scores: maxima, then U8 probabilities written to
-//              shared memory as the A operand of P.V (bytes placed in the packed V order).  The U8
-//              codes depend only on the TILE maximum, so the two groups work on different tiles at
-//              the same time with no state shared between them.
-//   WG3        correction.  Thread r owns the FP32 output row r in registers and everything that is
-//              sequential over tiles: running maximum, denominator, per-tile weights,
-//              O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
+//   WG0-WG2    softmax of tiles it % 3 == 0 / 1 / 2.  Thread r owns query row r (tensor-memory lane
+//              r) and makes two passes over the tile's 128 scores: maxima on the raw integers, then
+//              U8 probabilities written to shared memory as the A operand of P.V (bytes placed in
+//              the packed V order).  The U8 codes depend only on the TILE maximum, so the groups
+//              work on different tiles at the same time with no state shared between them.
+//   WG3        correction.  Thread r owns the FP32 output row r in registers (as packed FP32 pairs)
+//              and everything that is sequential over tiles: running maximum, denominator, per-tile
+//              weights, O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
 //   WG4        warp 16: TMA producer (Q, K ring, V ring); warp 17: one thread issues the QK^T MMAs,
-//              ahead of the softmax; warp 18: one thread issues the P.V MMAs.
-// Tensor memory (512 columns): S double-buffered (2 x 128, one per softmax group), P.V accumulator
-// double-buffered (2 x 128).  Probabilities are scaled to the tile maximum (full 8-bit resolution
-// in every tile), so each tile's integer P.V has its own weight and is folded into FP32 by the
-// correction group; nothing accumulates across tiles inside tensor memory.
+//              up to three tiles ahead of the softmax; warp 18: one thread issues the P.V MMAs.
+// Tensor memory (512 columns): three S buffers of 128 columns (tile it in buffer it % 3) and one
+// P.V accumulator of 128 columns.  Probabilities are scaled to the tile maximum (full 8-bit
+// resolution in every tile), so each tile's integer P.V has its own weight and is folded into FP32
+// by the correction group; nothing accumulates across tiles inside tensor memory.
 // Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh.  The integer
 // products are exact, so probabilities, capture statistics and block masses are bit-identical to
 // the row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
@@ -49,14 +49,6 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
               "register budget exceeds the launch pool");
 
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
-#ifdef RISA_TC_PROFILE
-__device__ unsigned long long g_prof[16];
-#define PROF_T0() long long prof_t = clock64()
-#define PROF(slot) do { long long now = clock64(); if ((threadIdx.x & 31) == 0 && blockIdx.x == 3 && (slot) >= 0) atomicAdd(&g_prof[slot], (unsigned long long)(now - prof_t)); prof_t = now; } while (0)
-#else
-#define PROF_T0()
-#define PROF(slot)
-#endif
 
 struct SmemLayout {
   static constexpr int q = 0;
@@ -115,30 +107,24 @@ template <bool CAPTURE>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
                                                  uint16_t* sums, uint32_t s_free_bar) {
-  uint32_t raw[2][32];
+  uint32_t raw[32];
   int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
-  PROF_T0();
-#ifdef RISA_ABLATE_PASS1
-  imax[0] = imax[1] = imax[2] = imax[3] = 100000;
-#else
-  tmem_load32(tmem_row, raw[0]);
+  tmem_load32(tmem_row, raw);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     tmem_load_wait();
-    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw[(c + 1) & 1]);
     // columns of K scale group g inside the chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const uint32_t* r = raw[c & 1];
+      const uint32_t* r = raw;
       imax[g] = __vimax3_s32(imax[g], int(r[2 * g]), int(r[2 * g + 1]));
       imax[g] = __vimax3_s32(imax[g], int(r[8 + 2 * g]), int(r[9 + 2 * g]));
       imax[g] = __vimax3_s32(imax[g], int(r[16 + 2 * g]), int(r[17 + 2 * g]));
       imax[g] = __vimax3_s32(imax[g], int(r[24 + 2 * g]), int(r[25 + 2 * g]));
     }
+    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw);
   }
-#endif
-  tmem_load32(tmem_row, raw[0]);
-  PROF(2);
+  tmem_load32(tmem_row, raw);
   float gm[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) gm[g] = fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset);
@@ -149,43 +135,29 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
-    PROF(-1);
     tmem_load_wait();
-    PROF(9);
     float x[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[0][i]));
+    for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[i]));
     if (c < 3) {
-      tmem_load32(tmem_row + 32 * (c + 1), raw[0]);
+      tmem_load32(tmem_row + 32 * (c + 1), raw);
     } else {
       // all scores of the tile are in registers: the MMA warp may overwrite S with the next tile
       tc_fence_before();
       mbar_arrive(s_free_bar);
     }
-    PROF(10);
     uint32_t P[8], s4[8];
-#ifndef RISA_ABLATE_PASS2
     tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, neg_m, P, numer, s4);
-#else
-    for (int i = 0; i < 8; ++i) { P[i] = __float_as_uint(x[4 * i]); s4[i] = 0; }
-#endif
-    PROF(11);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
         *reinterpret_cast<uint32_t*>(sums + 8 * c + i) = s4[i] | (s4[i + 1] << 16);
     }
-#ifndef RISA_ABLATE_PSTORE
     *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ swz) << 4)) = make_uint4(P[0], P[1], P[2], P[3]);
     *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ swz) << 4)) =
         make_uint4(P[4], P[5], P[6], P[7]);
-#else
-    numer += P[0] ^ P[1] ^ P[2] ^ P[3] ^ P[4] ^ P[5] ^ P[6] ^ P[7];
-#endif
-    PROF(12);
   }
   *stat = make_float2(tile_m, __uint_as_float(numer));
-  PROF(3);
 }
 
 // Every other case (last visited tile, causal, scale <= 0): float scores with the masks applied.
@@ -311,15 +283,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           const int s = step % kKStages, r = step / kKStages;
           ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
           if (!ok) break;
-#ifdef RISA_ABLATE_TMA
-          if (step >= kKStages) mbar_arrive(bar(Bars::KFULL + s)); else {
-#endif
           mbar_expect_tx(bar(Bars::KFULL + s), kTile);
           tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
                       seq.tile(step) * 128, int(kvh));
-#ifdef RISA_ABLATE_TMA
-          }
-#endif
           k_issued = step + 1;
         }
         const int it = step - 2;
@@ -327,15 +293,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           const int s = it % kVStages, r = it / kVStages;
           ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
           if (!ok) break;
-#ifdef RISA_ABLATE_TMA
-          if (it >= kVStages) mbar_arrive(bar(Bars::VFULL + s)); else {
-#endif
           mbar_expect_tx(bar(Bars::VFULL + s), kTile);
           tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
                       seq.tile(it) * 128, 0, int(kvh));
-#ifdef RISA_ABLATE_TMA
-          }
-#endif
           v_issued = it + 1;
         }
       }
@@ -349,9 +309,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
     } else if (warp == 17 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: S = Q.K^T
-      // Tile it goes to S buffer it & 1 as soon as the softmax group has read that buffer's
+      // Tile it goes to S buffer it % 3 as soon as the softmax group has read that buffer's
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
-      // round-trips on each, which otherwise bound the whole pipeline.
+      // round-trips on each.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, 128);
       const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
       bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
@@ -362,11 +322,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         if (!ok) break;
         tc_fence_after();
         const uint64_t desc_k = smem_desc_k128(sbase + SmemLayout::k + s * kTile);
-#ifndef RISA_ABLATE_QK
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
-#endif
         mma_commit(bar(Bars::SFULL + b));
         mma_commit(bar(Bars::KEMPTY + s));
       }
@@ -383,11 +341,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + slot * kTile);
         const uint64_t desc_v = smem_desc_k128(sbase + SmemLayout::v + s * kTile);
-#ifndef RISA_ABLATE_PV
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_i8(tmem_o, desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
-#endif
         mma_commit(bar(Bars::OFULL));
         mma_commit(bar(Bars::VEMPTY + s));
         mma_commit(bar(Bars::PFREE + slot));
@@ -411,7 +367,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
       for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + first_tile * 4 + g);
     }
-    PROF_T0();
     for (int it = b; it < seq.n_iter && ok; it += kSoftmaxGroups) {
       const int sb = it % 3, u = it / 3;
       const uint32_t tmem_row = tmem_lane + 128 * sb;
@@ -435,7 +390,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
                       ((it >> 2) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
-      PROF(0);
       if (int_scores && !last)
         softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
                                   bar(Bars::SFREE + sb));
@@ -447,7 +401,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
       fence_async_smem();
       mbar_arrive(bar(Bars::PFULL + slot));
-      PROF(1);
     }
   } else {
     // ------------------------------------------------------------------ correction + epilogue
@@ -461,11 +414,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int64_t grow = bh * a.q_len + row;
     RowState st;
     row_state_init(st);
-    float O[128];
+    uint64_t O2[64];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) O[i] = 0.0f;
+    for (int i = 0; i < 64; ++i) O2[i] = 0ull;
     bool ok = true;
-    PROF_T0();
     // Software-pipelined by one tile: the statistics of tile `it` (running maximum, denominator,
     // weights) are consumed as soon as its probabilities exist, while the accumulator that is
     // folded into O in the same iteration is the one of tile it - 1, whose P.V had the whole
@@ -477,7 +429,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         const bool last = it == seq.n_iter - 1;
         ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
         if (!ok) break;
-        PROF(4);
         const int slot = it & 3;
         const float2 stat = stats[slot * 128 + row_in];
         const uint32_t numer = __float_as_uint(stat.y);
@@ -514,33 +465,38 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         ok = mbar_wait(bar(Bars::OFULL), j & 1, error, 402);
         if (!ok) break;
         tc_fence_after();
-        PROF(5);
         const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
-        uint32_t acc[2][16];
-        tmem_load16(tmem_o + lane_base, acc[0]);
+        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
+        uint32_t acc[16];
+        tmem_load16(tmem_o + lane_base, acc);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           tmem_load_wait();
+          uint64_t f2[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
+                               static_cast<float>(int(acc[2 * i + 1])));
           if (c < 7) {
-            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc[(c + 1) & 1]);
+            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
           } else {
-            // the accumulator is in registers: P.V of the next tile may overwrite it
             tc_fence_before();
             mbar_arrive(bar(Bars::OFREE));
           }
           if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) O[16 * c + i] *= prev_o_scale;
+            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
           }
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            O[16 * c + i] = fmaf(static_cast<float>(int(acc[c & 1][i])), prev_w, O[16 * c + i]);
+          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
         }
-        PROF(6);
       }
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
     }
+    float O[128];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {
       if constexpr (CAPTURE) {
@@ -666,11 +622,4 @@ extern "C" int risa_b200_device_status(void) {
   return RISA_B200_OK;
 }
 
-#ifdef RISA_TC_PROFILE
-extern "C" void risa_b200_prof_read(unsigned long long* out) {
-  cudaMemcpyFromSymbol(out, risa_b200::g_prof, sizeof(unsigned long long) * 16);
-  unsigned long long zero[16] = {0};
-  cudaMemcpyToSymbol(risa_b200::g_prof, zero, sizeof(zero));
-}
-#endif
 

@@ -113,11 +113,7 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
   for (int i = 0; i < 32; ++i)
     p[i] = KIND == kScoresScaled ? x[i] + neg_m : fmaf(x[i], sc[(i & 7) >> 1], neg_m);
 #pragma unroll
-#ifndef RISA_ABLATE_EX2
   for (int i = 0; i < 32; ++i) p[i] = ex2_approx(p[i]);
-#else
-  for (int i = 0; i < 32; ++i) p[i] = p[i] * 0.001f + 1.0f;
-#endif
   uint32_t u[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(p[i] + 8388608.0f);

@@ -51,9 +51,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Same with a suspend-time hint: the hardware may park the thread until the phase completes (or the
 // time passes) instead of spinning through issue slots that the working warps of the same
 // scheduler need.  Used by the softmax and correction groups when a first test fails.
-#ifndef RISA_SUSPEND_HINT_NS
-#define RISA_SUSPEND_HINT_NS 2000
-#endif
+constexpr uint32_t kSuspendHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -63,7 +61,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(uint32_t(RISA_SUSPEND_HINT_NS))
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -72,12 +70,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // site in *error and reports failure, so a protocol bug ends the kernel instead of hanging the GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-#ifdef RISA_ALL_SPIN
-#define RISA_SPIN_DEFAULT true
-#else
-#define RISA_SPIN_DEFAULT false
-#endif
-template <bool SPIN = RISA_SPIN_DEFAULT>
+template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* error,
                                           unsigned int site) {
   if (mbar_test(bar, parity)) return true;
@@ -96,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
 
 // Waits for several phases at once: the tests are issued back to back so their latencies overlap
 // (in steady state all of them are already complete), then any that failed is waited for in turn.
-template <bool SPIN = RISA_SPIN_DEFAULT>
+template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
                                            unsigned int* error, unsigned int site) {
   const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1);
@@ -104,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1
   return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
          (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1));
 }
-template <bool SPIN = RISA_SPIN_DEFAULT>
+template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
                                            uint32_t b2, uint32_t p2, unsigned int* error,
                                            unsigned int site) {
@@ -181,6 +174,27 @@ __device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- packed FP32 pairs --------------------------------------------------------------------------
+// Two FP32 lanes in one 64-bit register: one instruction does both fused multiply-adds.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 // ---- register budget per warpgroup (all four warps of an aligned group of 128 threads) ----------
