@@ -108,15 +108,33 @@ __device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
 template <int KIND, bool WANT_SUMS>
 __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
                                                uint32_t* P, uint32_t& numer, uint32_t* s4) {
+  // Columns 2k and 2k + 1 share a K scale group, so scale and magic add run as packed FP32 pairs
+  // (one instruction for two columns, same per-lane rounding as the scalar form).
   float p[32];
+  const uint64_t nm2 = pack_f32x2(neg_m, neg_m);
 #pragma unroll
-  for (int i = 0; i < 32; ++i)
-    p[i] = KIND == kScoresScaled ? x[i] + neg_m : fmaf(x[i], sc[(i & 7) >> 1], neg_m);
+  for (int i = 0; i < 32; i += 2) {
+    const uint64_t x2 = pack_f32x2(x[i], x[i + 1]);
+    uint64_t r;
+    if (KIND == kScoresScaled) {
+      r = add_f32x2(x2, nm2);
+    } else {
+      const float s = sc[(i & 7) >> 1];
+      r = fma_f32x2(x2, pack_f32x2(s, s), nm2);
+    }
+    unpack_f32x2(r, p[i], p[i + 1]);
+  }
 #pragma unroll
   for (int i = 0; i < 32; ++i) p[i] = ex2_approx(p[i]);
   uint32_t u[32];
+  const uint64_t magic2 = pack_f32x2(8388608.0f, 8388608.0f);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(p[i] + 8388608.0f);
+  for (int i = 0; i < 32; i += 2) {
+    float a, b;
+    unpack_f32x2(add_f32x2(pack_f32x2(p[i], p[i + 1]), magic2), a, b);
+    u[i] = __float_as_uint(a);
+    u[i + 1] = __float_as_uint(b);
+  }
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
 #pragma unroll
