@@ -107,24 +107,26 @@ template <bool CAPTURE>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
                                                  uint16_t* sums, uint32_t s_free_bar) {
-  uint32_t raw[32];
+  // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
+  // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
+  // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
+  uint32_t raw_a[32], raw[32];
   int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
-  tmem_load32(tmem_row, raw);
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int h = 0; h < 2; ++h) {
+    tmem_load32(tmem_row + 64 * h, raw_a);
+    tmem_load32(tmem_row + 64 * h + 32, raw);
     tmem_load_wait();
-    // columns of K scale group g inside the chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
+    // columns of K scale group g inside a chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const uint32_t* r = raw;
-      imax[g] = __vimax3_s32(imax[g], int(r[2 * g]), int(r[2 * g + 1]));
-      imax[g] = __vimax3_s32(imax[g], int(r[8 + 2 * g]), int(r[9 + 2 * g]));
-      imax[g] = __vimax3_s32(imax[g], int(r[16 + 2 * g]), int(r[17 + 2 * g]));
-      imax[g] = __vimax3_s32(imax[g], int(r[24 + 2 * g]), int(r[25 + 2 * g]));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        imax[g] = __vimax3_s32(imax[g], int(raw_a[8 * k + 2 * g]), int(raw_a[8 * k + 2 * g + 1]));
+        imax[g] = __vimax3_s32(imax[g], int(raw[8 * k + 2 * g]), int(raw[8 * k + 2 * g + 1]));
+      }
     }
-    if (c < 3) tmem_load32(tmem_row + 32 * (c + 1), raw);
   }
-  tmem_load32(tmem_row, raw);
   float gm[4];
 #pragma unroll
   for (int g = 0; g < 4; ++g) gm[g] = fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset);
@@ -134,13 +136,13 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   // One copy of the chunk body (rolled loop): the chunk is converted to floats as soon as it
   // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 3; c >= 0; --c) {
     tmem_load_wait();
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[i]));
-    if (c < 3) {
-      tmem_load32(tmem_row + 32 * (c + 1), raw);
+    if (c > 0) {
+      tmem_load32(tmem_row + 32 * (c - 1), raw);
     } else {
       // all scores of the tile are in registers: the MMA warp may overwrite S with the next tile
       tc_fence_before();
