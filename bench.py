@@ -45,6 +45,9 @@ if str(ROOT) not in sys.path:
 
 B, HQ, HKV, D = 1, 16, 4, 128
 METRIC = "dense_equiv_int8_tops_32k_full_call"
+# DRAM bytes (read + written) of one attention_tc_kernel launch from an ncu capture of this script,
+# keyed by (sequence length, query heads on the GPU); other shapes report null.
+NCU_DRAM_BYTES_PER_LAUNCH = {(32768, 16): 101759232 + 90783232}
 
 
 def dense_ops(batch, heads, lq, lk, d):
@@ -374,7 +377,9 @@ def run_ours(args):
                      "kernel_ms": att_ms,
                      "peak_source": f"2 x {peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s "
                                     "(no INT8 figure in MEASURED_PEAKS.json)",
-                     "traffic": None},
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((L, q.shape[1])),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
+                                       "profiles/attention_tc_kernel_dense32k_dram_traffic.md"},
         "prep_roofline": {"bound": "hbm", "achieved": prep_bytes / prep_ms / 1e6,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s",
                           "frac": prep_bytes / prep_ms / 1e6 / peaks["hbm_gbs"],
