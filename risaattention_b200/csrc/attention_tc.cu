@@ -67,20 +67,34 @@ constexpr size_t kSmemBytes = SmemLayout::total + 1024;  // room to align the ba
 struct TileSeq {
   int n_iter;
   const int32_t* ids;
+  bool key_list;  // ids come from a key-mask tile list: the list may stop before the last key tile
+  int n_k;
   __device__ __forceinline__ int tile(int it) const { return ids ? __ldg(ids + it) : it; }
+  // The reference's generic last-visited-tile arithmetic applies on the last iteration, unless a
+  // key-mask list ends on a tile that is not the final key tile (attention_int8.cuh:552-566).
+  __device__ __forceinline__ bool last_rules(int it, int tile_id) const {
+    return it == n_iter - 1 && !(key_list && tile_id + 1 < n_k);
+  }
 };
 
+template <int CTA_K>
 __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t bh, int bx,
                                                  int n_q, int n_k, bool capture) {
   TileSeq s;
   s.ids = nullptr;
+  s.key_list = false;
+  s.n_k = n_k;
   if (a.row_offsets) {
     const int64_t r = bh * n_q + bx;
     const int start = __ldg(a.row_offsets + r);
     s.n_iter = __ldg(a.row_offsets + r + 1) - start;
     s.ids = a.block_indices + start;
+  } else if (a.key_mask_tiles) {
+    s.ids = a.key_mask_tiles + bh * (n_k + 1);
+    s.n_iter = __ldg(s.ids + n_k);
+    s.key_list = true;
   } else if (a.is_causal && !capture) {
-    s.n_iter = (min(a.k_len, (bx + 1) * 128) + 127) / 128;
+    s.n_iter = (min(a.k_len, (bx + 1) * 128) + CTA_K - 1) / CTA_K;
   } else {
     s.n_iter = n_k;
   }
@@ -103,7 +117,7 @@ struct Bars {
 // ---- softmax of one tile by the thread that owns the row -----------------------------------------
 // Common case: exact integer scores, not the last visited tile.  Pass 1 takes the maxima on the
 // raw integers (no conversion), pass 2 converts, scales, exponentiates and packs.
-template <bool CAPTURE>
+template <bool CAPTURE, int CTA_K>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
                                                  uint16_t* sums, uint32_t s_free_bar) {
@@ -113,7 +127,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   uint32_t raw_a[32], raw[32];
   int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < CTA_K / 64; ++h) {
     tmem_load32(tmem_row + 64 * h, raw_a);
     tmem_load32(tmem_row + 64 * h + 32, raw);
     tmem_load_wait();
@@ -136,7 +150,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   // One copy of the chunk body (rolled loop): the chunk is converted to floats as soon as it
   // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
 #pragma unroll 1
-  for (int c = 3; c >= 0; --c) {
+  for (int c = CTA_K / 32 - 1; c >= 0; --c) {
     tmem_load_wait();
     float x[32];
 #pragma unroll
@@ -163,11 +177,14 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
 }
 
 // Every other case (last visited tile, causal, scale <= 0): float scores with the masks applied.
-template <bool CAPTURE>
-__device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const float (&sc)[4],
-                                                     unsigned char* p_row, int swz, float2* stat,
-                                                     uint16_t* sums, bool int_scores, bool last,
-                                                     bool causal, int row, int c0, int k_len) {
+template <bool CAPTURE, int CTA_K>
+__device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int batch, int head,
+                                                     bool row_ok, uint32_t tmem_row,
+                                                     const float (&sc)[4], unsigned char* p_row,
+                                                     int swz, float2* stat, uint16_t* sums,
+                                                     bool int_scores, bool last, int row, int c0) {
+  const bool causal = a.is_causal != 0, masked = a.mask != nullptr;
+  const int k_len = a.k_len;
   auto load_chunk = [&](int c, float* x) {
     uint32_t raw[32];
     tmem_load32(tmem_row + 32 * c, raw);
@@ -179,7 +196,8 @@ __device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const fl
       if (int_scores) {
         if (last && kv >= k_len) s = -1.0e30f;
       } else {
-        s *= sc[(i & 7) >> 1];
+        if (masked) s = apply_mask(a, batch, head, row, kv, row_ok, s, sc[(i & 7) >> 1]);
+        else s *= sc[(i & 7) >> 1];
         if (causal && kv > row) s = -INFINITY;
         if (last && kv >= k_len) s = -INFINITY;
       }
@@ -189,7 +207,7 @@ __device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const fl
   TileMax tm;
   tile_max_init<kScoresScaled, true>(tm);  // maxima start at -50000 in all of these cases
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < CTA_K / 32; ++c) {
     float x[32];
     load_chunk(c, x);
     tile_max_chunk(x, tm);
@@ -198,7 +216,7 @@ __device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const fl
                                   : tile_max_finish<kScoresScaled>(tm, sc);
   uint32_t numer = 0;
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < CTA_K / 32; ++c) {
     float x[32];
     uint32_t P[8], s4[8];
     load_chunk(c, x);
@@ -216,7 +234,7 @@ __device__ __forceinline__ void softmax_tile_general(uint32_t tmem_row, const fl
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
-template <bool CAPTURE>
+template <bool CAPTURE, int CTA_K>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
@@ -228,7 +246,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   const int wg = warp >> 2;
   const int bx = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / (a.q_heads / a.kv_heads);
-  const int n_k = (a.k_len + 127) / 128, n_q = gridDim.x;
+  const int n_k = (a.k_len + CTA_K - 1) / CTA_K, n_q = gridDim.x;
   const int64_t bh = int64_t(batch) * a.q_heads + head;
   const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
   unsigned int* error = &g_tc_status;
@@ -264,7 +282,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::tmem_slot);
   const uint32_t tmem_o = tmem + 384;  // S buffers at columns 0, 128, 256
 
-  const TileSeq seq = tile_sequence(a, bh, bx, n_q, n_k, CAPTURE);
+  const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE);
   float2* stats = reinterpret_cast<float2*>(smem + SmemLayout::stats);
   uint16_t* sums = reinterpret_cast<uint16_t*>(smem + SmemLayout::sums);
 
@@ -285,9 +303,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           const int s = step % kKStages, r = step / kKStages;
           ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
           if (!ok) break;
-          mbar_expect_tx(bar(Bars::KFULL + s), kTile);
+          mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * 128);
           tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
-                      seq.tile(step) * 128, int(kvh));
+                      seq.tile(step) * CTA_K, int(kvh));
           k_issued = step + 1;
         }
         const int it = step - 2;
@@ -295,9 +313,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           const int s = it % kVStages, r = it / kVStages;
           ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
           if (!ok) break;
+          // V always arrives as the 128-key slab that holds the tile (64-key tiles use half of it):
+          // rows stay 128 bytes wide, so one swizzle mode and one descriptor form serve both widths
           mbar_expect_tx(bar(Bars::VFULL + s), kTile);
           tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
-                      seq.tile(it) * 128, 0, int(kvh));
+                      (seq.tile(it) * CTA_K) & ~127, 0, int(kvh));
           v_issued = it + 1;
         }
       }
@@ -314,7 +334,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       // Tile it goes to S buffer it % 3 as soon as the softmax group has read that buffer's
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
       // round-trips on each.
-      constexpr uint32_t idesc_qk = idesc_i8(true, true, 128);
+      constexpr uint32_t idesc_qk = idesc_i8(true, true, CTA_K);
       const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
       bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
@@ -343,9 +363,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + slot * kTile);
         const uint64_t desc_v = smem_desc_k128(sbase + SmemLayout::v + s * kTile);
+        // a 64-key tile is the first or second half (64 bytes per row) of its 128-key V slab
+        const uint32_t v_k0 = CTA_K == 64 ? 4u * (seq.tile(it) & 1) : 0u;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_i8(tmem_o, desc_p + 2 * kk, desc_v + 2 * kk, idesc_pv, kk > 0);
+        for (int kk = 0; kk < CTA_K / 32; ++kk)
+          mma_i8(tmem_o, desc_p + 2 * kk, desc_v + v_k0 + 2 * kk, idesc_pv, kk > 0);
         mma_commit(bar(Bars::OFULL));
         mma_commit(bar(Bars::VEMPTY + s));
         mma_commit(bar(Bars::PFREE + slot));
@@ -358,7 +380,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
-    const bool int_scores = !a.is_causal && a.sm_scale > 0.0f;
+    const bool int_scores = !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const bool row_ok = row < a.q_len;
     const float scale2 = a.sm_scale * kLog2e;
     const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
     const float* k_scale = a.k_scale + kvh * (n_k * 4);
@@ -373,7 +396,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const int sb = it % 3, u = it / 3;
       const uint32_t tmem_row = tmem_lane + 128 * sb;
       const int tile = seq.tile(it);
-      const bool last = it == seq.n_iter - 1;
+      const bool last = seq.last_rules(it, tile);
       float sc[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) sc[g] = scale2 * (q_scale * ks_next[g]);
@@ -393,11 +416,12 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (!ok) break;
       tc_fence_after();
       if (int_scores && !last)
-        softmax_tile_int<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
-                                  bar(Bars::SFREE + sb));
+        softmax_tile_int<CAPTURE, CTA_K>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
+                                         bar(Bars::SFREE + sb));
       else {
-        softmax_tile_general<CAPTURE>(tmem_row, sc, p_row, row_in & 7, stat, my_sums, int_scores,
-                                      last, a.is_causal != 0, row, tile * 128, a.k_len);
+        softmax_tile_general<CAPTURE, CTA_K>(a, batch, head, row_ok, tmem_row, sc, p_row,
+                                             row_in & 7, stat, my_sums, int_scores, last, row,
+                                             tile * CTA_K);
         tc_fence_before();
         mbar_arrive(bar(Bars::SFREE + sb));
       }
@@ -428,7 +452,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     for (int it = 0; it <= seq.n_iter && ok; ++it) {
       float cur_o_scale = 1.0f, cur_w = 0.0f;
       if (it < seq.n_iter) {
-        const bool last = it == seq.n_iter - 1;
+        const bool last_iter = it == seq.n_iter - 1;
+        const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
         ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
         if (!ok) break;
         const int slot = it & 3;
@@ -440,14 +465,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         if constexpr (CAPTURE) {
           const uint16_t* s16 = sums + (slot * 128 + row_in) * 32;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < CTA_K / 32; ++c) {
             uint16_t s4[8];
             *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
             if (last) denominator_chunk<true>(st, ts, c == 0, s4);
             else denominator_chunk<false>(st, ts, c == 0, s4);
           }
           if (row_ok) {
-            if (last) {
+            if (last_iter) {
               float* out = cap.last + grow * 2;
               out[0] = static_cast<float>(numer);
               out[1] = ts.tile_m;
@@ -506,7 +531,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         cap.state[grow * 2 + 1] = denom;
       }
       const float inv = rcp_approx(denom);
-      const bool zero = a.is_causal && !(denom > 0.0f);
+      const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
       const float* vs = a.v_scale + kvh * 128;
       const float* vc = a.v_center + kvh * 128;
       char* o_row = static_cast<char*>(a.o) +
@@ -563,11 +588,12 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// 3-D byte tensor {inner, rows, slabs} with a {128, 128, 1} box and the 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs) {
+// 3-D byte tensor {inner, rows, slabs} with a {128, box_rows, 1} box and the 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs,
+              uint32_t box_rows) {
   const cuuint64_t dims[3] = {inner, rows, slabs};
   const cuuint64_t strides[2] = {inner, inner * rows};
-  const cuuint32_t box[3] = {128, 128, 1};
+  const cuuint32_t box[3] = {128, box_rows, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides,
                      box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -575,37 +601,50 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-}  // namespace
-
-bool attention_tc_supported(const AttentionArgs& a) {
-  return a.head_dim == 128 && a.cta_k == 128 && a.mask == nullptr && a.key_mask_tiles == nullptr &&
-         encode_fn() != nullptr && reinterpret_cast<uintptr_t>(a.o) % 16 == 0 &&
-         a.o_stride_b % 8 == 0 && a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
-}
-
-int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
-  const int n_k = (a.k_len + 127) / 128;
-  CUtensorMap map_q, map_k, map_v;
-  if (!make_map(&map_q, a.q, 128, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads) ||
-      !make_map(&map_k, a.k, 128, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads) ||
-      !make_map(&map_v, a.v, uint64_t(n_k) * 128, 128, uint64_t(a.batch) * a.kv_heads))
-    return fail(RISA_B200_CUDA, "attention: tensor map creation failed");
-  const bool capture = a.block_mass != nullptr;
-  auto kernel = capture ? attention_tc_kernel<true> : attention_tc_kernel<false>;
-  static thread_local int configured[2] = {-1, -1};
+template <bool CAPTURE, int CTA_K>
+int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
+              const CUtensorMap& map_v, cudaStream_t stream) {
+  auto kernel = attention_tc_kernel<CAPTURE, CTA_K>;
+  static thread_local int configured = -1;  // per instantiation, thread and device
   int device = -1;
   cudaGetDevice(&device);
-  if (configured[capture] != device) {
+  if (configured != device) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          int(kSmemBytes));
     if (e != cudaSuccess)
       return fail(RISA_B200_CUDA, "attention: cannot reserve %zu bytes of shared memory: %s",
                   kSmemBytes, cudaGetErrorString(e));
-    configured[capture] = device;
+    configured = device;
   }
   const dim3 grid((a.q_len + 127) / 128, a.q_heads, a.batch);
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, a);
   return check_launch("attention (tensor-core kernel)");
+}
+
+}  // namespace
+
+// head_dim 128 with 64- or 128-key tiles, every mask form, causal, tile lists, capture.  The packed V
+// row must hold at least one 128-key slab (the V box is always 128 keys wide).
+bool attention_tc_supported(const AttentionArgs& a) {
+  const int64_t padded = int64_t((a.k_len + a.cta_k - 1) / a.cta_k) * a.cta_k;
+  return a.head_dim == 128 && (a.cta_k == 128 || a.cta_k == 64) && padded >= 128 &&
+         encode_fn() != nullptr && reinterpret_cast<uintptr_t>(a.o) % 16 == 0 &&
+         a.o_stride_b % 8 == 0 && a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
+}
+
+int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
+  const int n_k = (a.k_len + a.cta_k - 1) / a.cta_k;
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_map(&map_q, a.q, 128, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads, 128) ||
+      !make_map(&map_k, a.k, 128, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads, a.cta_k) ||
+      !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, 128, uint64_t(a.batch) * a.kv_heads, 128))
+    return fail(RISA_B200_CUDA, "attention: tensor map creation failed");
+  const bool capture = a.block_mass != nullptr;
+  if (a.cta_k == 64)
+    return capture ? launch_tc<true, 64>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<false, 64>(a, map_q, map_k, map_v, stream);
+  return capture ? launch_tc<true, 128>(a, map_q, map_k, map_v, stream)
+                 : launch_tc<false, 128>(a, map_q, map_k, map_v, stream);
 }
 
 }  // namespace risa_b200

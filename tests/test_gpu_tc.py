@@ -81,3 +81,100 @@ def test_tc_fp16_output_and_nhd_layout(ref):
         pk["v_center"], 128, 0.1, 2, torch.cuda.current_stream().cuda_stream)
     _status()
     assert_outputs_match(out, ref.attention(pk, sm_scale=0.1)["out"], TOL)
+
+
+MASK_SHAPES = [
+    # lq, lk, hq, hkv, cta_k
+    (137, 263, 2, 1, 64),
+    (300, 1153, 4, 2, 128),
+    (260, 1000, 4, 4, 64),
+    (128, 129, 1, 1, 64),
+]
+
+
+@pytest.mark.parametrize("shape", MASK_SHAPES)
+@pytest.mark.parametrize("mask_kind", ["none", "key_bias", "row_bool", "bias_4d"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_masks_and_64_key_tiles(ref, shape, mask_kind, causal):
+    """Every mask form and both key-tile widths on the tensor-core path, against the reference's
+    kernels and the row kernel: outputs within 2e-3 x RMS, -inf rows identical, LSE within 2e-4
+    (5e-4 with a mask: masked scores may differ from the reference's in the last FP32 bit, which
+    can flip single U8 probability codes, and this path keeps one denominator partial)."""
+    from tests.test_gpu_attention import _masks
+
+    lq, lk, hq, hkv, cta_k = shape
+    if mask_kind in ("row_bool", "bias_4d") and cta_k == 128:
+        pytest.skip("per-query masks always use 64-key tiles")
+    _, _, _, pk = _packed(ref, 128, lq, lk, hq, hkv, cta_k, affine=True, seed=lq + lk)
+    mask = _masks(mask_kind, 1, hq, lq, lk)
+    for scale in (128 ** -0.5, 0.0, -0.125):
+        want = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, want_lse=True)
+        rows = _ours(pk, sm_scale=scale, path=1, mask=mask, is_causal=causal, want_lse=True)
+        got = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, want_lse=True)
+        _status()
+        assert_outputs_match(got["out"], want["out"], TOL)
+        assert_outputs_match(got["out"], rows["out"], TOL)
+        assert torch.equal(torch.isneginf(got["lse"]), torch.isneginf(want["lse"]))
+        fin = torch.isfinite(want["lse"])
+        torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0,
+                                   atol=2e-4 if mask_kind == "none" else 5e-4)
+        if mask_kind == "row_bool":
+            assert torch.count_nonzero(got["out"][:, :, 0]) == 0
+
+
+@pytest.mark.parametrize("shape", MASK_SHAPES[:3])
+@pytest.mark.parametrize("mask_kind", ["none", "key_bias"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_capture_64_key_tiles_and_masks(ref, shape, mask_kind, causal):
+    """Capture on the tensor-core path: the whole workspace bit for bit without a mask and against
+    the row kernel with one (same arithmetic); against the reference masked masses agree to 1e-4
+    (its compiler fuses score * scale + bias differently per instantiation)."""
+    from risaattention_b200.sparse import select_retained_mass_csr
+    from tests.test_gpu_attention import _masks
+
+    lq, lk, hq, hkv, cta_k = shape
+    _, _, _, pk = _packed(ref, 128, lq, lk, hq, hkv, cta_k, seed=5 + lk)
+    mask = _masks(mask_kind, 1, hq, lq, lk)
+    scale = 128 ** -0.5
+    want = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, capture=True)
+    rows = _ours(pk, sm_scale=scale, path=1, mask=mask, is_causal=causal, capture=True)
+    got = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, capture=True)
+    _status()
+    assert torch.equal(got["workspace"].view(torch.int32), rows["workspace"].view(torch.int32))
+    assert torch.equal(got["out"], rows["out"])
+    n_q, n_k = -(-lq // 128), -(-lk // cta_k)
+    if mask_kind == "none":
+        assert torch.equal(got["workspace"].view(torch.int32), want["workspace"].view(torch.int32))
+    else:
+        torch.testing.assert_close(got["workspace"][: hq * n_q * n_k],
+                                   want["workspace"][: hq * n_q * n_k], rtol=1e-4, atol=1e-5)
+    masses = got["workspace"][: hq * n_q * n_k].view(-1, n_k)
+    ro, bi, _ = select_retained_mass_csr(masses, 0.9)
+    want_s = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, row_offsets=ro,
+                           block_indices=bi)
+    got_s = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, row_offsets=ro,
+                  block_indices=bi)
+    _status()
+    assert_outputs_match(got_s["out"], want_s["out"], TOL)
+
+
+@pytest.mark.parametrize("cta_k", [64, 128])
+def test_tc_key_mask_tile_list(ref, cta_k):
+    d, lq, lk, hq, hkv = 128, 300, 1153, 4, 2
+    _, _, _, pk = _packed(ref, d, lq, lk, hq, hkv, cta_k, b=2, seed=9)
+    visible = torch.ones(2, hq, 1, lk, device="cuda", dtype=torch.bool)
+    visible[..., :128] = False
+    visible[..., 384:768] = False
+    visible[0, 1] = False
+    visible[..., 897:913] = False
+    visible[1, 3, :, 1000:] = False  # the list ends before the last key tile
+    mask = visible.expand(2, hq, lq, lk)
+    tiles = ref.key_mask_tiles(mask, cta_k)
+    want = ref.attention(pk, sm_scale=d ** -0.5, mask=mask, want_lse=True, key_mask_tiles=tiles)
+    got = _ours(pk, sm_scale=d ** -0.5, path=0, mask=mask, want_lse=True, tiles=tiles)
+    _status()
+    assert_outputs_match(got["out"], want["out"], TOL)
+    assert torch.count_nonzero(got["out"][0, 1]) == 0
+    assert torch.isneginf(got["lse"][0, 1]).all()
+    fin = torch.isfinite(want["lse"])
+    torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0, atol=5e-4)
