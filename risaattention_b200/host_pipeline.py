@@ -1,0 +1,75 @@
+"""Attention over host-resident operands, pipelined by head group.
+
+A caller whose Q/K/V live in (pinned) host memory pays two PCIe transfers around the kernels.  The
+path is independent per (batch, KV head) -- the same property the multi-GPU sharding uses -- so the
+call is cut into one stage per KV head and its query heads, and the stages are pipelined over three
+streams: host-to-device copies of stage g+1 and the device-to-host copy of stage g-1 run while
+stage g computes.  Results are identical to a single device-resident call (every stage runs the
+same kernels on the same per-head data).  The reference has no counterpart: its API takes CUDA
+tensors only.
+"""
+from __future__ import annotations
+
+import torch
+
+from .dense import int8_attention
+
+
+def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                             out: torch.Tensor | None = None, *, device=None, **kwargs):
+    """``int8_attention`` for CPU tensors in ``[B, H, L, D]`` layout; returns a pinned CPU tensor.
+
+    ``kwargs`` are passed to :func:`int8_attention` (``scale``, ``is_causal``, ``v_quantization``).
+    Masks, LSE and KV permutations are not supported here.  Pinned inputs make the copies
+    asynchronous; pageable inputs work but serialise.
+    """
+    for name in ("attn_mask", "return_lse", "kv_permutation"):
+        if kwargs.get(name) not in (None, False):
+            raise ValueError(f"int8_attention_from_host does not support {name}")
+    if query.device.type != "cpu" or key.device.type != "cpu" or value.device.type != "cpu":
+        raise ValueError("int8_attention_from_host expects CPU tensors")
+    if query.ndim != 4 or key.shape != value.shape or query.shape[0] != key.shape[0]:
+        raise ValueError("expected q [B, Hq, Lq, D] and k, v [B, Hkv, Lk, D]")
+    batch, q_heads = query.shape[:2]
+    kv_heads = key.shape[1]
+    if q_heads % kv_heads:
+        raise ValueError(f"q head count ({q_heads}) must be divisible by k/v head count ({kv_heads})")
+    group = q_heads // kv_heads
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out_dtype = query.dtype
+    if out is None:
+        out = torch.empty(query.shape, dtype=out_dtype, pin_memory=True)
+    elif out.shape != query.shape or out.device.type != "cpu" or not out.is_contiguous():
+        raise ValueError("out must be a contiguous CPU tensor of q's shape")
+
+    compute = torch.cuda.current_stream(device)
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    start = torch.cuda.Event()
+    start.record(compute)
+    copy_in.wait_event(start)  # inputs written by earlier work on the caller's stream are visible
+    copy_out.wait_event(start)
+    keep = []
+    for b in range(batch):
+        for h in range(kv_heads):
+            qs = slice(h * group, (h + 1) * group)
+            with torch.cuda.stream(copy_in):
+                dq = query[b:b + 1, qs].to(device, non_blocking=True)
+                dk = key[b:b + 1, h:h + 1].to(device, non_blocking=True)
+                dv = value[b:b + 1, h:h + 1].to(device, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_in)
+            compute.wait_event(ready)
+            for t in (dq, dk, dv):
+                t.record_stream(compute)
+            result = int8_attention(dq, dk, dv, **kwargs)
+            done = torch.cuda.Event()
+            done.record(compute)
+            copy_out.wait_event(done)
+            result.record_stream(copy_out)
+            with torch.cuda.stream(copy_out):
+                out[b:b + 1, qs].copy_(result, non_blocking=True)
+            keep.append((dq, dk, dv, result))
+    finished = torch.cuda.Event()
+    finished.record(copy_out)
+    compute.wait_event(finished)  # the caller's stream sees the output once this event has passed
+    return out

@@ -205,3 +205,23 @@ def test_graph_capture_and_streams():
     torch.cuda.current_stream().wait_stream(stream)
     torch.cuda.synchronize()
     assert torch.equal(actual, expected)
+
+
+def test_host_pipeline_matches_device_call():
+    """Host-resident operands, pipelined per KV head over three streams: identical bits to one
+    device-resident call (every stage is independent per head)."""
+    import risaattention_b200 as risa
+
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 8, 300, 128, generator=g).bfloat16().pin_memory()
+    k = torch.randn(2, 2, 1300, 128, generator=g).bfloat16().pin_memory()
+    v = torch.randn(2, 2, 1300, 128, generator=g).bfloat16().pin_memory()
+    for causal in (False, True):
+        want = risa.int8_attention(q.cuda(), k.cuda(), v.cuda(), is_causal=causal,
+                                   v_quantization="midpoint_affine")
+        got = risa.int8_attention_from_host(q, k, v, is_causal=causal,
+                                            v_quantization="midpoint_affine")
+        torch.cuda.synchronize()
+        assert got.is_pinned() and torch.equal(got, want.cpu())
+    with pytest.raises(ValueError, match="does not support"):
+        risa.int8_attention_from_host(q, k, v, return_lse=True)
