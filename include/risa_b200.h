@@ -96,6 +96,26 @@ int risa_b200_attention(const void* q, const void* k, const void* v, void* o, co
                         const int32_t* sparse_block_indices, float* block_mass, int is_causal,
                         float* lse, const int32_t* key_mask_tiles, void* stream);
 
+/* One call for the unmasked dense path: quantise Q, K and V into caller-provided scratch and run
+ * the attention kernel on it.  Same kernels, same results as risa_b200_quantize_qk +
+ * risa_b200_quantize_v + risa_b200_attention issued one after the other on `stream`; it exists so a
+ * host runtime pays one foreign-function call and one scratch allocation per attention call instead
+ * of three calls and nine buffers, which is what bounds short sequences.  The reference's FFI has no
+ * fused entry point (csrc/bindings.cpp:195-461 exposes the two steps separately); its Python
+ * execute_dense_attention (src/risa_attention/_execution.py:28-66) is the caller this serves.
+ * scratch: device memory of at least risa_b200_dense_scratch_size() bytes, 256-byte aligned. */
+size_t risa_b200_dense_scratch_size(int batch, int q_heads, int q_len, int kv_heads, int k_len,
+                                    int head_dim, int cta_k);
+int risa_b200_dense_attention(const void* q, const void* k, const void* v, void* o, void* scratch,
+                              size_t scratch_bytes, int batch, int q_heads, int q_len,
+                              int kv_heads, int k_len, int head_dim, int cta_k,
+                              int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                              int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                              int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_n,
+                              int dtype_code, int midpoint_affine, float sm_scale,
+                              int out_dtype_code, int64_t o_stride_b, int64_t o_stride_n,
+                              int64_t o_stride_h, int is_causal, void* stream);
+
 /* Selects which attention kernel family the library may use: 0 = automatic (tensor-core kernel
  * where it applies), 1 = force the row-per-thread integer kernel (used by parity tests to compare
  * the two).  Process-wide; returns the previous value. */

@@ -35,6 +35,10 @@ _SIGNATURES = {
         c_i32,
         [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
                                                                    c_i32, c_vp, c_vp, c_vp]),
+    "risa_b200_dense_scratch_size": (c_sz, [c_i32] * 7),
+    "risa_b200_dense_attention": (
+        c_i32, [c_vp] * 5 + [c_sz] + [c_i32] * 7 + [c_i64] * 9 + [c_i32, c_i32, c_f32, c_i32] +
+        [c_i64] * 3 + [c_i32, c_vp]),
     "risa_b200_set_attention_path": (c_i32, [c_i32]),
     "risa_b200_device_status": (c_i32, []),
     "risa_b200_selector_workspace_size": (c_sz, [c_i32]),
@@ -87,6 +91,23 @@ class _Native:
             v.stride(0), v.stride(1), v.stride(2), input_dtype_code, int(use_midpoint_affine),
             _ptr(v_perm), _ptr(workspace), workspace.numel() * workspace.element_size(),
             stream_ptr))
+
+    # -- fused unmasked dense call (no counterpart in the reference's native module) ------------
+    def dense_scratch_size(self, batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k) -> int:
+        return int(self.lib.risa_b200_dense_scratch_size(batch, q_heads, q_len, kv_heads, k_len,
+                                                         head_dim, cta_k))
+
+    def risa_dense_attention(self, q, k, v, o, scratch, cta_k, input_dtype_code,
+                             use_midpoint_affine, sm_scale, output_dtype_code, is_causal,
+                             stream_ptr):
+        b, hq, lq, d = q.shape
+        hkv, lk = k.shape[1], k.shape[2]
+        self._check(self.lib.risa_b200_dense_attention(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), scratch.data_ptr(),
+            scratch.numel(), b, hq, lq, hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2),
+            k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
+            input_dtype_code, int(use_midpoint_affine), sm_scale, output_dtype_code, o.stride(0),
+            o.stride(2), o.stride(1), int(is_causal), stream_ptr))
 
     def quantize_v_workspace_size(self, batch, kv_heads, k_len, head_dim) -> int:
         return int(self.lib.risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim))
@@ -178,9 +199,23 @@ except (ImportError, OSError, AttributeError) as error:
     _EXTENSION_ERROR = error
 
 
+_AVAILABLE: dict = {}
+
+
 def is_available(device: torch.device | int | str | None = None) -> bool:
     """True when the library is loaded and ``device`` is a Blackwell datacenter GPU (sm_100)."""
-    if _C is None or not torch.cuda.is_available():
+    if _C is None:
+        return False
+    if isinstance(device, torch.device) and device.type == "cuda" and device.index is not None:
+        known = _AVAILABLE.get(device.index)
+        if known is None:
+            known = _AVAILABLE[device.index] = _probe(device)
+        return known
+    return _probe(device)
+
+
+def _probe(device) -> bool:
+    if not torch.cuda.is_available():
         return False
     try:
         resolved = None

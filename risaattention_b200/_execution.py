@@ -29,17 +29,27 @@ def execute_dense_attention(q, k, v, *, scale=None, attn_mask=None, use_midpoint
     batch, q_heads, q_len, _ = q.shape
     key_block_size = select_key_block_size(
         dim, k.shape[2], has_mask=attn_mask is not None and attn_mask.stride(-2) != 0)
-    buffers = PackedBuffers(q, k, key_block_size)
     out_dtype = _output_dtype(input_dtype)
     output = torch.empty(batch, q_heads, q_len, dim, dtype=out_dtype, device=q.device)
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    tiles = prepare_key_mask_tiles(attn_mask, key_block_size, q_len, attention_scale, is_causal)
-    quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine)
-    _backend._C.risa_sdpa_prequantized(
-        buffers.q_codes, buffers.k_codes, buffers.v_codes, output, buffers.q_scales,
-        buffers.k_scales, buffers.v_scales, buffers.v_centers, key_block_size, attention_scale,
-        DTYPE_CODES[out_dtype], stream, attn_mask=attn_mask, is_causal=is_causal,
-        key_mask_tiles=tiles)
+    if attn_mask is None:
+        # one native call, one scratch allocation: what bounds short sequences is the host side
+        scratch = torch.empty(
+            _backend._C.dense_scratch_size(batch, q_heads, q_len, k.shape[1], k.shape[2], dim,
+                                           key_block_size), dtype=torch.uint8, device=q.device)
+        _backend._C.risa_dense_attention(q, k, v, output, scratch, key_block_size,
+                                         DTYPE_CODES[input_dtype], use_midpoint_affine,
+                                         attention_scale, DTYPE_CODES[out_dtype], is_causal, stream)
+    else:
+        buffers = PackedBuffers(q, k, key_block_size)
+        tiles = prepare_key_mask_tiles(attn_mask, key_block_size, q_len, attention_scale,
+                                       is_causal)
+        quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine)
+        _backend._C.risa_sdpa_prequantized(
+            buffers.q_codes, buffers.k_codes, buffers.v_codes, output, buffers.q_scales,
+            buffers.k_scales, buffers.v_scales, buffers.v_centers, key_block_size,
+            attention_scale, DTYPE_CODES[out_dtype], stream, attn_mask=attn_mask,
+            is_causal=is_causal, key_mask_tiles=tiles)
     if original_head_dim != dim:
         output = output[..., :original_head_dim]
     return output.float() if input_dtype == torch.float32 else output

@@ -144,3 +144,83 @@ extern "C" int risa_b200_attention(
   }
   return RISA_B200_OK;
 }
+
+// ---- fused dense call: quantise into caller scratch, then attend --------------------------------
+namespace {
+
+struct DenseScratch {
+  size_t q_codes, k_codes, v_codes, q_scale, k_scale, v_scale, v_center, anchors, v_work, total;
+};
+
+constexpr size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
+
+DenseScratch dense_scratch_layout(int batch, int q_heads, int q_len, int kv_heads, int k_len,
+                                  int head_dim, int cta_k) {
+  const size_t n_q = (size_t(q_len) + 127) / 128, n_k = (size_t(k_len) + cta_k - 1) / cta_k;
+  const size_t channels = size_t(batch) * kv_heads * head_dim;
+  DenseScratch s;
+  size_t at = 0;
+  auto take = [&at](size_t bytes) { const size_t here = at; at += align256(bytes); return here; };
+  s.q_codes = take(size_t(batch) * q_heads * q_len * head_dim);
+  s.k_codes = take(size_t(batch) * kv_heads * k_len * head_dim);
+  s.v_codes = take(channels * n_k * cta_k);
+  s.q_scale = take(size_t(batch) * q_heads * n_q * (head_dim == 256 ? 64 : 32) * sizeof(float));
+  s.k_scale = take(size_t(batch) * kv_heads * n_k * 4 * sizeof(float));
+  s.v_scale = take(channels * sizeof(float));
+  s.v_center = take(channels * sizeof(float));
+  s.anchors = take(size_t(batch) * kv_heads * sizeof(int32_t));
+  s.v_work = take(risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim));
+  s.total = at;
+  return s;
+}
+
+}  // namespace
+
+extern "C" size_t risa_b200_dense_scratch_size(int batch, int q_heads, int q_len, int kv_heads,
+                                               int k_len, int head_dim, int cta_k) {
+  if (batch <= 0 || q_heads <= 0 || q_len <= 0 || kv_heads <= 0 || k_len <= 0 ||
+      (cta_k != 64 && cta_k != 128) || (head_dim != 64 && head_dim != 128 && head_dim != 256))
+    return 0;
+  return dense_scratch_layout(batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k).total;
+}
+
+extern "C" int risa_b200_dense_attention(
+    const void* q, const void* k, const void* v, void* o, void* scratch, size_t scratch_bytes,
+    int batch, int q_heads, int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n, int64_t k_stride_b,
+    int64_t k_stride_h, int64_t k_stride_n, int64_t v_stride_b, int64_t v_stride_h,
+    int64_t v_stride_n, int dtype_code, int midpoint_affine, float sm_scale, int out_dtype_code,
+    int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, int is_causal, void* stream) {
+  using namespace risa_b200;
+  const size_t need =
+      risa_b200_dense_scratch_size(batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k);
+  RISA_REQUIRE(need != 0, "risa_dense_attention: unsupported shape");
+  RISA_REQUIRE(scratch != nullptr && scratch_bytes >= need &&
+                   reinterpret_cast<uintptr_t>(scratch) % 256 == 0,
+               "risa_dense_attention: scratch must be 256-byte aligned device memory of at least "
+               "risa_b200_dense_scratch_size() bytes");
+  const DenseScratch s =
+      dense_scratch_layout(batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k);
+  char* base = static_cast<char*>(scratch);
+  const int padded = (k_len + cta_k - 1) / cta_k * cta_k;
+  float* q_scale = reinterpret_cast<float*>(base + s.q_scale);
+  float* k_scale = reinterpret_cast<float*>(base + s.k_scale);
+  float* v_scale = reinterpret_cast<float*>(base + s.v_scale);
+  float* v_center = reinterpret_cast<float*>(base + s.v_center);
+  int status = risa_b200_quantize_qk(
+      q, base + s.q_codes, q_scale, k, base + s.k_codes, k_scale, batch, q_heads, q_len, kv_heads,
+      k_len, head_dim, cta_k, q_stride_b, q_stride_h, q_stride_n, k_stride_b, k_stride_h,
+      k_stride_n, dtype_code, reinterpret_cast<int32_t*>(base + s.anchors), nullptr, nullptr,
+      stream);
+  if (status != RISA_B200_OK) return status;
+  status = risa_b200_quantize_v(v, base + s.v_codes, v_scale, v_center, batch, kv_heads, k_len,
+                                head_dim, padded, v_stride_b, v_stride_h, v_stride_n, dtype_code,
+                                midpoint_affine, nullptr, base + s.v_work, s.total - s.v_work,
+                                stream);
+  if (status != RISA_B200_OK) return status;
+  return risa_b200_attention(base + s.q_codes, base + s.k_codes, base + s.v_codes, o, q_scale,
+                             k_scale, v_scale, v_center, nullptr, 0, 0, 0, 0, -1, cta_k, batch,
+                             q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
+                             o_stride_h, sm_scale, out_dtype_code, nullptr, nullptr, nullptr,
+                             is_causal, nullptr, nullptr, stream);
+}
