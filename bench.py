@@ -250,6 +250,45 @@ def reference_kernels_leg(q, k, v, seq_len, steps):
         return {"error": str(error)[:200]}
 
 
+def accuracy_leg(q, k, v, out_ours, seq_len):
+    """NRMSE against FP32 softmax attention on one query head per KV head (all queries, all keys),
+    for this library and, when built, for the reference's kernels on the same inputs."""
+    group = q.shape[1] // k.shape[1]
+    heads = list(range(0, q.shape[1], group))
+    want = torch.empty(q.shape[0], len(heads), seq_len, D, device=q.device)
+    chunk = 2048
+    for i, h in enumerate(heads):
+        kf = k[:, h // group].float()
+        vf = v[:, h // group].float()
+        for start in range(0, seq_len, chunk):
+            qf = q[:, h, start:start + chunk].float() * D ** -0.5
+            want[:, i, start:start + chunk] = torch.softmax(qf @ kf.transpose(-1, -2), -1) @ vf
+
+    def nrmse(x):
+        x = x[:, heads].float()
+        return float(((x - want).pow(2).mean() / want.pow(2).mean()).sqrt())
+
+    result = {"heads_checked": heads, "nrmse_vs_fp32_sdpa": nrmse(out_ours)}
+    try:
+        from oracle import ref_gpu
+        if ref_gpu.available():
+            cta_k = 128 if seq_len > 1024 else 64
+            ref_out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+            ref_gpu.attention(ref_gpu.prequantize(q, k, v, cta_k=cta_k), sm_scale=D ** -0.5,
+                              out=ref_out)
+            result["reference_kernels_nrmse"] = nrmse(ref_out)
+            # parity rule of the tests: |ours - ref| <= 2e-3 RMS + one bf16 unit in the last place
+            a, b = out_ours.float(), ref_out.float()
+            ulp = torch.maximum(a.abs(), b.abs()) * 2.0 ** -7
+            rms = b.pow(2).mean().sqrt()
+            result["max_abs_beyond_one_bf16_ulp_over_rms"] = float(
+                ((a - b).abs() - ulp).clamp_min(0).max() / rms)
+            result["fraction_of_elements_differing"] = float((a != b).float().mean())
+    except Exception as error:  # comparison only
+        result["reference_error"] = str(error)[:200]
+    return result
+
+
 def sparse_leg(seq_len, device, steps, generator="video_blocks"):
     import risaattention_b200 as risa
 
@@ -357,6 +396,11 @@ def run_ours(args):
     prep_ms = event_time_ms(lambda: risa.prequantize_int8_attention(q, k, v), args.steps,
                             args.warmup)
     int8_peak = 2.0 * peaks["bf16_tflops"]  # no INT8 entry in MEASURED_PEAKS: 2 x measured bf16
+    # measured INT8 issue-loop throughput of this GPU (kind::i8 128x256x32 back to back, all SMs)
+    stream_ptr = torch.cuda.current_stream(device).cuda_stream
+    _, loop_ops = _backend._C.mma_i8_issue_loop(8192, stream_ptr)
+    loop_ms = event_time_ms(lambda: _backend._C.mma_i8_issue_loop(8192, stream_ptr), 10, 3)
+    mma_loop_tops = loop_ops / loop_ms / 1e9
     achieved = local_ops / att_ms / 1e9
     prep_bytes = sum(t.numel() * 3 for t in (q, k, v))  # 2 B in + 1 B out per element
     line = {
@@ -375,6 +419,8 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "kernel": "attention_tc_kernel", "achieved": achieved,
                      "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
                      "kernel_ms": att_ms,
+                     "mma_i8_issue_loop_tops": mma_loop_tops,
+                     "frac_of_issue_loop": achieved / mma_loop_tops,
                      "peak_source": f"2 x {peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s "
                                     "(no INT8 figure in MEASURED_PEAKS.json)",
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((L, q.shape[1])),
@@ -386,6 +432,7 @@ def run_ours(args):
                           "kernel_ms": prep_ms, "note": "5 kernels incl. host launch gaps"},
     }
     if world == 1:
+        line["accuracy"] = accuracy_leg(q, k, v, step(), L)
         line["reference_kernels_on_this_gpu"] = reference_kernels_leg(q, k, v, L, args.steps)
         if not args.no_sparse:
             try:

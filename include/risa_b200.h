@@ -116,6 +116,14 @@ int risa_b200_dense_attention(const void* q, const void* k, const void* v, void*
                               int out_dtype_code, int64_t o_stride_b, int64_t o_stride_n,
                               int64_t o_stride_h, int is_causal, void* stream);
 
+/* Measurement aid, no counterpart in the reference: launches one CTA per SM that issues
+ * `mma_per_cta` back-to-back tcgen05.mma kind::i8 128x256x32 instructions on shared-memory
+ * operands.  Timed by the caller (events on `stream`), ops_per_launch / time is the INT8 tensor
+ * issue-loop throughput of this GPU at its current clocks: the measured ceiling the attention
+ * kernel's roofline fraction can be read against.  Writes the CTA count and the operation count
+ * (2*M*N*K per MMA) of one launch. */
+int risa_b200_mma_i8_issue_loop(int mma_per_cta, int* ctas, double* ops_per_launch, void* stream);
+
 /* Selects which attention kernel family the library may use: 0 = automatic (tensor-core kernel
  * where it applies), 1 = force the row-per-thread integer kernel (used by parity tests to compare
  * the two).  Process-wide; returns the previous value. */

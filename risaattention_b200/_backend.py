@@ -39,6 +39,7 @@ _SIGNATURES = {
     "risa_b200_dense_attention": (
         c_i32, [c_vp] * 5 + [c_sz] + [c_i32] * 7 + [c_i64] * 9 + [c_i32, c_i32, c_f32, c_i32] +
         [c_i64] * 3 + [c_i32, c_vp]),
+    "risa_b200_mma_i8_issue_loop": (c_i32, [c_i32, c_vp, c_vp, c_vp]),
     "risa_b200_set_attention_path": (c_i32, [c_i32]),
     "risa_b200_device_status": (c_i32, []),
     "risa_b200_selector_workspace_size": (c_sz, [c_i32]),
@@ -108,6 +109,13 @@ class _Native:
             k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
             input_dtype_code, int(use_midpoint_affine), sm_scale, output_dtype_code, o.stride(0),
             o.stride(2), o.stride(1), int(is_causal), stream_ptr))
+
+    def mma_i8_issue_loop(self, mma_per_cta, stream_ptr) -> tuple[int, float]:
+        """Launches the INT8 tensor-pipe issue loop once; returns (CTAs, operations in the launch)."""
+        ctas, ops = ctypes.c_int(0), ctypes.c_double(0.0)
+        self._check(self.lib.risa_b200_mma_i8_issue_loop(mma_per_cta, ctypes.byref(ctas),
+                                                         ctypes.byref(ops), stream_ptr))
+        return ctas.value, ops.value
 
     def quantize_v_workspace_size(self, batch, kv_heads, k_len, head_dim) -> int:
         return int(self.lib.risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim))

@@ -15,7 +15,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = CSRC / "_obj"
 LIB = PKG / "librisa_b200.so"
-UNITS = ["prep_qk", "prep_v", "misc", "attention_api", "attention_rows", "attention_tc"]
+UNITS = ["prep_qk", "prep_v", "misc", "attention_api", "attention_rows", "attention_tc", "mma_peak"]
 # --use_fast_math is part of the numeric contract shared with the reference's kernels
 # (approximate division / reciprocal, flush-to-zero, contracted multiply-adds).
 NVCC_FLAGS = [
