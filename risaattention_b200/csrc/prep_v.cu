@@ -166,6 +166,110 @@ __global__ __launch_bounds__(kSlotsPerCta) void v_quantize_kernel(
   }
 }
 
+// Same work as v_quantize_kernel for key lengths that are a multiple of 16, organised for the memory
+// system: a CTA owns 32 consecutive slots x 64 channels (thread = one slot, four channels), so a
+// half-warp reads one token's 64 channels as one contiguous segment, and the codes of a 32-token
+// window go through shared memory to leave as 16-byte stores (one aligned 16-token storage group
+// of one channel each) instead of single bytes.  Each (slot, channel) residual is still summed by
+// one thread over tokens Lk-1-slot, Lk-1-slot-slots, ... in that order.
+// grid (slots / 32, B*Hkv*D / 64), 512 threads.
+constexpr int kTiledSlots = 32, kTiledChannels = 64, kTiledThreads = 512;
+
+template <typename T, bool AFFINE>
+__global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
+    const T* __restrict__ v, int8_t* __restrict__ out, float* __restrict__ scale_out,
+    float* __restrict__ center_out, const float2* __restrict__ ranges,
+    float* __restrict__ residuals, int k_len, int padded_len, int kv_heads, int head_dim,
+    int chunks, int slots, int64_t stride_b, int64_t stride_h, int64_t stride_n,
+    const int32_t* __restrict__ perm) {
+  __shared__ float s_inv[kTiledChannels], s_center[kTiledChannels];
+  __shared__ __align__(16) unsigned char s_tile[2][kTiledChannels][48];  // 32 positions + padding
+  const int d_tiles = head_dim / kTiledChannels;
+  const int d_tile = blockIdx.y % d_tiles, bh = blockIdx.y / d_tiles;
+  const int h = bh % kv_heads, b = bh / kv_heads;
+  const int d0 = d_tile * kTiledChannels;
+  const int sl = threadIdx.x >> 4, quad = threadIdx.x & 15;
+  const int slot = blockIdx.x * kTiledSlots + sl;
+  const T* in = v + b * stride_b + h * stride_h + d0 + 4 * quad;
+  const int32_t* row_map = perm ? perm + static_cast<int64_t>(bh) * k_len : nullptr;
+  const int64_t out_row = static_cast<int64_t>(bh) * head_dim + d0;
+
+  if (threadIdx.x < kTiledChannels) {
+    float lo = FLT_MAX, hi = -FLT_MAX;
+    const float2* r = ranges + static_cast<int64_t>(bh) * chunks * head_dim + d0 + threadIdx.x;
+    for (int c = 0; c < chunks; ++c) {
+      const float2 x = __ldg(r + static_cast<int64_t>(c) * head_dim);
+      lo = fminf(lo, x.x);
+      hi = fmaxf(hi, x.y);
+    }
+    float center, radius;
+    if constexpr (AFFINE) {
+      center = 0.5f * (lo + hi);
+      radius = 0.5f * (hi - lo);
+    } else {
+      center = 0.0f;
+      radius = fmaxf(fabsf(lo), fabsf(hi));
+    }
+    const float sc = fmaxf(radius * (1.f / 127.f), 1e-12f);
+    s_inv[threadIdx.x] = 1.f / sc;
+    s_center[threadIdx.x] = center;
+    if (blockIdx.x == 0) {
+      scale_out[out_row + threadIdx.x] = sc;
+      if constexpr (!AFFINE) center_out[out_row + threadIdx.x] = 0.0f;
+    }
+  }
+  __syncthreads();
+  float inv[4], center[4], residual[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    inv[i] = s_inv[4 * quad + i];
+    center[i] = s_center[4 * quad + i];
+    residual[i] = 0.f;
+  }
+  // Window of iteration `it`: tokens [hi - 31, hi], hi = k_len - 1 - 32 * blockIdx.x - slots * it;
+  // with k_len a multiple of 16 the window is two aligned 16-token storage groups.
+  const int first_hi = k_len - 1 - blockIdx.x * kTiledSlots;
+  int buffer = 0;
+  for (int hi = first_hi; hi >= 0; hi -= slots, buffer ^= 1) {
+    const int lo = hi - (kTiledSlots - 1);
+    const int src = hi - sl;
+    if (src >= 0) {
+      float t[4];
+      const int64_t row = row_map ? __ldg(row_map + src) : src;
+      Load4<T>::load(in + row * stride_n, t);
+      const int position = storage_position(src) - lo;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float normalized = (t[i] - center[i]) * inv[i];
+        const uint32_t code = to_s8(normalized);
+        s_tile[buffer][4 * quad + i][position] = static_cast<unsigned char>(code);
+        if constexpr (AFFINE)
+          residual[i] += normalized - static_cast<float>(static_cast<int8_t>(code));
+      }
+    }
+    __syncthreads();  // the other buffer was read before the previous barrier: safe to refill next
+    if (threadIdx.x < 2 * kTiledChannels) {
+      const int channel = threadIdx.x >> 1, group = threadIdx.x & 1;
+      const int base = lo + 16 * group;
+      if (base >= 0)
+        *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + base) =
+            *reinterpret_cast<const uint4*>(&s_tile[buffer][channel][16 * group]);
+    }
+  }
+  if constexpr (AFFINE) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      residuals[(out_row + 4 * quad + i) * slots + slot] = residual[i];
+  }
+  // zero tail [k_len, padded_len): whole 16-byte groups because k_len is a multiple of 16
+  for (int idx = blockIdx.x * kTiledThreads + threadIdx.x;
+       idx < kTiledChannels * ((padded_len - k_len) / 16); idx += gridDim.x * kTiledThreads) {
+    const int channel = idx % kTiledChannels, group = idx / kTiledChannels;
+    *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + k_len + 16 * group) =
+        make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 // grid (B*Hkv*D), `slots` threads: xor butterfly per warp, warps added in order by thread 0.
 __global__ void v_center_kernel(const float* __restrict__ residuals,
                                 const float2* __restrict__ ranges, float* __restrict__ center_out,
@@ -263,7 +367,22 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
         static_cast<const T*>(v), ranges, k_len, head_dim, kv_heads, p.chunks, stride_b, stride_h,
         stride_n, perm);
     const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
-    if (midpoint_affine) {
+    const dim3 tiled_grid(p.slots / kTiledSlots, channels / kTiledChannels);
+    // 16-byte code stores need whole storage groups and an aligned destination
+    const bool tiled = k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0;
+    if (tiled && midpoint_affine) {
+      v_quantize_tiled_kernel<T, true><<<tiled_grid, kTiledThreads, 0, stream>>>(
+          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
+          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
+          stride_n, perm);
+      v_center_kernel<<<channels, p.slots, 0, stream>>>(residuals, ranges, v_center, k_len,
+                                                        head_dim, p.chunks, p.slots);
+    } else if (tiled) {
+      v_quantize_tiled_kernel<T, false><<<tiled_grid, kTiledThreads, 0, stream>>>(
+          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
+          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
+          stride_n, perm);
+    } else if (midpoint_affine) {
       v_quantize_kernel<T, true><<<grid, kSlotsPerCta, 0, stream>>>(
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
           residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
