@@ -24,8 +24,8 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     asynchronous; pageable inputs work but serialise.
     """
     for name in ("attn_mask", "return_lse", "kv_permutation"):
-        value = kwargs.get(name)
-        if value is not None and value is not False:
+        option = kwargs.get(name)
+        if option is not None and option is not False:
             raise ValueError(f"int8_attention_from_host does not support {name}")
     if query.device.type != "cpu" or key.device.type != "cpu" or value.device.type != "cpu":
         raise ValueError("int8_attention_from_host expects CPU tensors")
