@@ -3,7 +3,8 @@
 // TMA into 128-byte-swizzled shared memory; the FP32 online softmax, the per-tile FP32 rescale of
 // the output and the epilogue run on ordinary warps that read the accumulators with tcgen05.ld.
 //
-// One CTA = 128 queries of one (batch, head), key tiles of 128, head_dim 128.  Five warpgroups:
+// One CTA = 128 queries of one (batch, head); key tiles of 64 or 128 and head_dim 64 or 128 are
+// template parameters (the description below uses 128 / 128).  Five warpgroups:
 //   WG0-WG2    softmax of tiles it % 3 == 0 / 1 / 2.  Thread r owns query row r (tensor-memory lane
 //              r) and makes two passes over the tile's 128 scores: maxima on the raw integers, then
 //              U8 probabilities written to shared memory as the A operand of P.V (bytes placed in
@@ -234,7 +235,7 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
-template <bool CAPTURE, int CTA_K>
+template <bool CAPTURE, int CTA_K, int D>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
@@ -293,7 +294,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       tma_prefetch_descriptor(&map_q);
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_v);
-      mbar_expect_tx(bar(Bars::QFULL), kTile);
+      mbar_expect_tx(bar(Bars::QFULL), 128 * D);
       tma_load_3d(sbase + SmemLayout::q, &map_q, bar(Bars::QFULL), 0, bx * 128, int(bh));
       bool ok = true;
       int k_issued = 0, v_issued = 0;
@@ -303,7 +304,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           const int s = step % kKStages, r = step / kKStages;
           ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
           if (!ok) break;
-          mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * 128);
+          mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * D);
           tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
                       seq.tile(step) * CTA_K, int(kvh));
           k_issued = step + 1;
@@ -315,7 +316,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           if (!ok) break;
           // V always arrives as the 128-key slab that holds the tile (64-key tiles use half of it):
           // rows stay 128 bytes wide, so one swizzle mode and one descriptor form serve both widths
-          mbar_expect_tx(bar(Bars::VFULL + s), kTile);
+          mbar_expect_tx(bar(Bars::VFULL + s), D * 128);
           tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
                       (seq.tile(it) * CTA_K) & ~127, 0, int(kvh));
           v_issued = it + 1;
@@ -335,7 +336,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
       // round-trips on each.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, CTA_K);
-      const uint64_t desc_q = smem_desc_k128(sbase + SmemLayout::q);
+      const uint64_t desc_q = smem_desc_kmajor<D>(sbase + SmemLayout::q);
       bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
         const int b = it % 3, u = it / 3, s = it % kKStages, r = it / kKStages;
@@ -343,16 +344,16 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
                               error, 202);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t desc_k = smem_desc_k128(sbase + SmemLayout::k + s * kTile);
+        const uint64_t desc_k = smem_desc_kmajor<D>(sbase + SmemLayout::k + s * kTile);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
+        for (int kk = 0; kk < D / 32; ++kk)
           mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
         mma_commit(bar(Bars::SFULL + b));
         mma_commit(bar(Bars::KEMPTY + s));
       }
     } else if (warp == 18 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: P.V
-      constexpr uint32_t idesc_pv = idesc_i8(false, true, 128);
+      constexpr uint32_t idesc_pv = idesc_i8(false, true, D);
       bool ok = true;
       for (int it = 0; it < seq.n_iter && ok; ++it) {
         const int s = it % kVStages, r = it / kVStages;
@@ -440,9 +441,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int64_t grow = bh * a.q_len + row;
     RowState st;
     row_state_init(st);
-    uint64_t O2[64];
+    uint64_t O2[D / 2];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) O2[i] = 0ull;
+    for (int i = 0; i < D / 2; ++i) O2[i] = 0ull;
     bool ok = true;
     // Software-pipelined by one tile: the statistics of tile `it` (running maximum, denominator,
     // weights) are consumed as soon as its probabilities exist, while the accumulator that is
@@ -497,14 +498,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         uint32_t acc[16];
         tmem_load16(tmem_o + lane_base, acc);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < D / 16; ++c) {
           tmem_load_wait();
           uint64_t f2[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
                                static_cast<float>(int(acc[2 * i + 1])));
-          if (c < 7) {
+          if (c < D / 16 - 1) {
             tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
           } else {
             tc_fence_before();
@@ -521,9 +522,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
     }
-    float O[128];
+    float O[D];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
+    for (int i = 0; i < D / 2; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {
       if constexpr (CAPTURE) {
@@ -532,12 +533,12 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
       const float inv = rcp_approx(denom);
       const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
-      const float* vs = a.v_scale + kvh * 128;
-      const float* vc = a.v_center + kvh * 128;
+      const float* vs = a.v_scale + kvh * D;
+      const float* vc = a.v_center + kvh * D;
       char* o_row = static_cast<char*>(a.o) +
                     2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
 #pragma unroll
-      for (int ch = 0; ch < 128; ch += 8) {
+      for (int ch = 0; ch < D; ch += 8) {
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -588,23 +589,25 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// 3-D byte tensor {inner, rows, slabs} with a {128, box_rows, 1} box and the 128-byte swizzle.
+// 3-D byte tensor {inner, rows, slabs} with a {box_inner, box_rows, 1} box; rows of 128 bytes use the
+// 128-byte swizzle, rows of 64 bytes the 64-byte one (what the MMA descriptors expect).
 bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs,
-              uint32_t box_rows) {
+              uint32_t box_inner, uint32_t box_rows) {
   const cuuint64_t dims[3] = {inner, rows, slabs};
   const cuuint64_t strides[2] = {inner, inner * rows};
-  const cuuint32_t box[3] = {128, box_rows, 1};
+  const cuuint32_t box[3] = {box_inner, box_rows, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides,
-                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool CAPTURE, int CTA_K>
+template <bool CAPTURE, int CTA_K, int D>
 int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
               const CUtensorMap& map_v, cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<CAPTURE, CTA_K>;
+  auto kernel = attention_tc_kernel<CAPTURE, CTA_K, D>;
   static thread_local int configured = -1;  // per instantiation, thread and device
   int device = -1;
   cudaGetDevice(&device);
@@ -623,28 +626,35 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
 
 }  // namespace
 
-// head_dim 128 with 64- or 128-key tiles, every mask form, causal, tile lists, capture.  The packed V
-// row must hold at least one 128-key slab (the V box is always 128 keys wide).
+// head_dim 128 with 64- or 128-key tiles and head_dim 64 with 64-key tiles (the only width the
+// packed formats define for it); every mask form, causal, tile lists, capture.  The packed V row
+// must hold at least one 128-key slab (the V box is always 128 keys wide).
 bool attention_tc_supported(const AttentionArgs& a) {
   const int64_t padded = int64_t((a.k_len + a.cta_k - 1) / a.cta_k) * a.cta_k;
-  return a.head_dim == 128 && (a.cta_k == 128 || a.cta_k == 64) && padded >= 128 &&
-         encode_fn() != nullptr && reinterpret_cast<uintptr_t>(a.o) % 16 == 0 &&
-         a.o_stride_b % 8 == 0 && a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
+  const bool shape = (a.head_dim == 128 && (a.cta_k == 128 || a.cta_k == 64)) ||
+                     (a.head_dim == 64 && a.cta_k == 64);
+  return shape && padded >= 128 && encode_fn() != nullptr &&
+         reinterpret_cast<uintptr_t>(a.o) % 16 == 0 && a.o_stride_b % 8 == 0 &&
+         a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
 }
 
 int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
   const int n_k = (a.k_len + a.cta_k - 1) / a.cta_k;
+  const uint32_t d = uint32_t(a.head_dim);
   CUtensorMap map_q, map_k, map_v;
-  if (!make_map(&map_q, a.q, 128, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads, 128) ||
-      !make_map(&map_k, a.k, 128, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads, a.cta_k) ||
-      !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, 128, uint64_t(a.batch) * a.kv_heads, 128))
+  if (!make_map(&map_q, a.q, d, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads, d, 128) ||
+      !make_map(&map_k, a.k, d, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads, d, a.cta_k) ||
+      !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, d, uint64_t(a.batch) * a.kv_heads, 128, d))
     return fail(RISA_B200_CUDA, "attention: tensor map creation failed");
   const bool capture = a.block_mass != nullptr;
+  if (a.head_dim == 64)
+    return capture ? launch_tc<true, 64, 64>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<false, 64, 64>(a, map_q, map_k, map_v, stream);
   if (a.cta_k == 64)
-    return capture ? launch_tc<true, 64>(a, map_q, map_k, map_v, stream)
-                   : launch_tc<false, 64>(a, map_q, map_k, map_v, stream);
-  return capture ? launch_tc<true, 128>(a, map_q, map_k, map_v, stream)
-                 : launch_tc<false, 128>(a, map_q, map_k, map_v, stream);
+    return capture ? launch_tc<true, 64, 128>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<false, 64, 128>(a, map_q, map_k, map_v, stream);
+  return capture ? launch_tc<true, 128, 128>(a, map_q, map_k, map_v, stream)
+                 : launch_tc<false, 128, 128>(a, map_q, map_k, map_v, stream);
 }
 
 }  // namespace risa_b200

@@ -69,8 +69,20 @@ __device__ __forceinline__ uint32_t to_s8(float x) {
   asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
   return static_cast<uint32_t>(q) & 0xffu;
 }
+// Four codes in one word, a in the lowest byte.  Round to nearest even to a 32-bit integer, then the
+// saturating pack (two values per instruction, the third operand supplies the upper half): the
+// same bytes as four cvt.rni.sat.s8.f32 (both clamp to [-128, 127] after the same rounding; NaN
+// gives 0 either way) with fewer than half the instructions.
 __device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
-  return to_s8(a) | (to_s8(b) << 8) | (to_s8(c) << 16) | (to_s8(d) << 24);
+  int32_t ia, ib, ic, id;
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ia) : "f"(a));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ib) : "f"(b));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ic) : "f"(c));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(id) : "f"(d));
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(id), "r"(ic), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(ib), "r"(ia), "r"(hi));
+  return w;
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

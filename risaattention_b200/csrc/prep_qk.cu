@@ -60,11 +60,12 @@ __device__ __forceinline__ void rotate16(float* v, int chunk) {
 #pragma unroll
   for (int s = 0; s < kLaneStages; ++s) {
     const int bit = 1 << s;
-    const bool upper = (chunk & bit) != 0;
+    // other - v in the upper lane of a pair, v + other in the lower one: one FMA with a lane sign
+    const float sign = (chunk & bit) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float other = __shfl_xor_sync(0xffffffffu, v[i], bit);
-      v[i] = upper ? other - v[i] : v[i] + other;
+      v[i] = fmaf(v[i], sign, other);
     }
   }
   constexpr float kNorm = ROT == kRotH64 ? 0.25f : 0.1767766952966369f;

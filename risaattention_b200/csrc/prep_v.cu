@@ -230,30 +230,46 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
   // with k_len a multiple of 16 the window is two aligned 16-token storage groups.
   const int first_hi = k_len - 1 - blockIdx.x * kTiledSlots;
   int buffer = 0;
-  for (int hi = first_hi; hi >= 0; hi -= slots, buffer ^= 1) {
-    const int lo = hi - (kTiledSlots - 1);
-    const int src = hi - sl;
-    if (src >= 0) {
-      float t[4];
-      const int64_t row = row_map ? __ldg(row_map + src) : src;
-      Load4<T>::load(in + row * stride_n, t);
-      const int position = storage_position(src) - lo;
+  // The loads of kBatch consecutive windows are issued together (a token's row is only read once,
+  // so nothing but the number of loads in flight hides the memory latency), then the windows are
+  // converted and written one after the other.
+  constexpr int kBatch = 8;
+  for (int batch_hi = first_hi; batch_hi >= 0; batch_hi -= kBatch * slots) {
+    float t[kBatch][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float normalized = (t[i] - center[i]) * inv[i];
-        const uint32_t code = to_s8(normalized);
-        s_tile[buffer][4 * quad + i][position] = static_cast<unsigned char>(code);
-        if constexpr (AFFINE)
-          residual[i] += normalized - static_cast<float>(static_cast<int8_t>(code));
+    for (int u = 0; u < kBatch; ++u) {
+      const int src = batch_hi - u * slots - sl;
+      if (src >= 0) {
+        const int64_t row = row_map ? __ldg(row_map + src) : src;
+        Load4<T>::load(in + row * stride_n, t[u]);
       }
     }
-    __syncthreads();  // the other buffer was read before the previous barrier: safe to refill next
-    if (threadIdx.x < 2 * kTiledChannels) {
-      const int channel = threadIdx.x >> 1, group = threadIdx.x & 1;
-      const int base = lo + 16 * group;
-      if (base >= 0)
-        *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + base) =
-            *reinterpret_cast<const uint4*>(&s_tile[buffer][channel][16 * group]);
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int hi = batch_hi - u * slots;
+      if (hi < 0) break;  // uniform over the CTA
+      const int lo = hi - (kTiledSlots - 1);
+      const int src = hi - sl;
+      if (src >= 0) {
+        const int position = storage_position(src) - lo;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float normalized = (t[u][i] - center[i]) * inv[i];
+          const uint32_t code = to_s8(normalized);
+          s_tile[buffer][4 * quad + i][position] = static_cast<unsigned char>(code);
+          if constexpr (AFFINE)
+            residual[i] += normalized - static_cast<float>(static_cast<int8_t>(code));
+        }
+      }
+      __syncthreads();  // the other buffer was read before the previous barrier: safe to refill
+      if (threadIdx.x < 2 * kTiledChannels) {
+        const int channel = threadIdx.x >> 1, group = threadIdx.x & 1;
+        const int base = lo + 16 * group;
+        if (base >= 0)
+          *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + base) =
+              *reinterpret_cast<const uint4*>(&s_tile[buffer][channel][16 * group]);
+      }
+      buffer ^= 1;
     }
   }
   if constexpr (AFFINE) {

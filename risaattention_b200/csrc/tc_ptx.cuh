@@ -199,6 +199,21 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_address) {
   return desc;
 }
 
+// Same for tiles whose rows are ROW_BYTES wide: 128 -> 128-byte swizzle (8-row groups 1024 bytes
+// apart), 64 -> 64-byte swizzle (layout type 4, 8-row groups 512 bytes apart), which is what a TMA
+// box of that inner width with the matching swizzle mode produces.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t smem_address) {
+  static_assert(ROW_BYTES == 64 || ROW_BYTES == 128, "row width");
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4);
+  desc |= static_cast<uint64_t>(1) << 16;
+  desc |= static_cast<uint64_t>((8 * ROW_BYTES) >> 4) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(ROW_BYTES == 128 ? 2 : 4) << 61;
+  return desc;
+}
+
 // Instruction descriptor of kind::i8: S32 accumulator, A and B K-major, M = 128.
 __host__ __device__ constexpr uint32_t idesc_i8(bool a_signed, bool b_signed, int n) {
   return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) |

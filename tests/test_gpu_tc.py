@@ -178,3 +178,53 @@ def test_tc_key_mask_tile_list(ref, cta_k):
     assert torch.isneginf(got["lse"][0, 1]).all()
     fin = torch.isfinite(want["lse"])
     torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0, atol=5e-4)
+
+
+D64_SHAPES = [
+    # lq, lk, hq, hkv
+    (137, 263, 2, 1),
+    (300, 1153, 4, 2),
+    (128, 2048, 2, 2),
+]
+
+
+@pytest.mark.parametrize("shape", D64_SHAPES)
+@pytest.mark.parametrize("mask_kind", ["none", "key_bias", "bias_4d"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_head_dim_64(ref, shape, mask_kind, causal):
+    """head_dim 64 (64-byte operand rows, 64-byte swizzle) on the tensor-core path."""
+    from tests.test_gpu_attention import _masks
+
+    lq, lk, hq, hkv = shape
+    _, _, _, pk = _packed(ref, 64, lq, lk, hq, hkv, 64, affine=True, seed=lq + lk)
+    mask = _masks(mask_kind, 1, hq, lq, lk)
+    for scale in (64 ** -0.5, -0.125):
+        want = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, want_lse=True)
+        rows = _ours(pk, sm_scale=scale, path=1, mask=mask, is_causal=causal, want_lse=True)
+        got = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, want_lse=True)
+        _status()
+        assert_outputs_match(got["out"], want["out"], TOL)
+        assert_outputs_match(got["out"], rows["out"], TOL)
+        fin = torch.isfinite(want["lse"])
+        torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0,
+                                   atol=2e-4 if mask_kind == "none" else 5e-4)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_head_dim_64_capture_bit_exact(ref, causal):
+    from risaattention_b200.sparse import select_retained_mass_csr
+
+    lq, lk, hq, hkv = 300, 1153, 4, 2
+    _, _, _, pk = _packed(ref, 64, lq, lk, hq, hkv, 64, seed=21)
+    want = ref.attention(pk, sm_scale=0.125, is_causal=causal, capture=True)
+    got = _ours(pk, sm_scale=0.125, path=0, is_causal=causal, capture=True)
+    _status()
+    assert torch.equal(got["workspace"].view(torch.int32), want["workspace"].view(torch.int32))
+    assert torch.equal(got["out"], want["out"])
+    n_q, n_k = -(-lq // 128), -(-lk // 64)
+    masses = got["workspace"][: hq * n_q * n_k].view(-1, n_k)
+    ro, bi, _ = select_retained_mass_csr(masses, 0.9)
+    want_s = ref.attention(pk, sm_scale=0.125, is_causal=causal, row_offsets=ro, block_indices=bi)
+    got_s = _ours(pk, sm_scale=0.125, path=0, is_causal=causal, row_offsets=ro, block_indices=bi)
+    _status()
+    assert_outputs_match(got_s["out"], want_s["out"], TOL)
