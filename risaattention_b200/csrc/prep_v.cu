@@ -183,7 +183,9 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
     int chunks, int slots, int64_t stride_b, int64_t stride_h, int64_t stride_n,
     const int32_t* __restrict__ perm) {
   __shared__ float s_inv[kTiledChannels], s_center[kTiledChannels];
-  __shared__ __align__(16) unsigned char s_tile[2][kTiledChannels][48];  // 32 positions + padding
+  // 32 positions per channel; a row pitch of 36 bytes (9 words) spreads the 16 channel quads of a
+  // half-warp over 8 banks (any pitch that is a multiple of 16 bytes would put them on 2)
+  __shared__ __align__(4) unsigned char s_tile[2][kTiledChannels][36];
   const int d_tiles = head_dim / kTiledChannels;
   const int d_tile = blockIdx.y % d_tiles, bh = blockIdx.y / d_tiles;
   const int h = bh % kv_heads, b = bh / kv_heads;
@@ -194,13 +196,29 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
   const int32_t* row_map = perm ? perm + static_cast<int64_t>(bh) * k_len : nullptr;
   const int64_t out_row = static_cast<int64_t>(bh) * head_dim + d0;
 
-  if (threadIdx.x < kTiledChannels) {
+  // channel range = min / max over the per-chunk partials: spread over the whole CTA (eight chunk
+  // subsets per channel) so that the loads overlap instead of forming one long dependent loop
+  __shared__ float s_lo[kTiledThreads / kTiledChannels][kTiledChannels];
+  __shared__ float s_hi[kTiledThreads / kTiledChannels][kTiledChannels];
+  {
+    const int channel = threadIdx.x % kTiledChannels, part = threadIdx.x / kTiledChannels;
     float lo = FLT_MAX, hi = -FLT_MAX;
-    const float2* r = ranges + static_cast<int64_t>(bh) * chunks * head_dim + d0 + threadIdx.x;
-    for (int c = 0; c < chunks; ++c) {
+    const float2* r = ranges + static_cast<int64_t>(bh) * chunks * head_dim + d0 + channel;
+    for (int c = part; c < chunks; c += kTiledThreads / kTiledChannels) {
       const float2 x = __ldg(r + static_cast<int64_t>(c) * head_dim);
       lo = fminf(lo, x.x);
       hi = fmaxf(hi, x.y);
+    }
+    s_lo[part][channel] = lo;
+    s_hi[part][channel] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x < kTiledChannels) {
+    float lo = FLT_MAX, hi = -FLT_MAX;
+#pragma unroll
+    for (int part = 0; part < kTiledThreads / kTiledChannels; ++part) {
+      lo = fminf(lo, s_lo[part][threadIdx.x]);
+      hi = fmaxf(hi, s_hi[part][threadIdx.x]);
     }
     float center, radius;
     if constexpr (AFFINE) {
@@ -265,9 +283,11 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
       if (threadIdx.x < 2 * kTiledChannels) {
         const int channel = threadIdx.x >> 1, group = threadIdx.x & 1;
         const int base = lo + 16 * group;
-        if (base >= 0)
+        if (base >= 0) {
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(&s_tile[buffer][channel][16 * group]);
           *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + base) =
-              *reinterpret_cast<const uint4*>(&s_tile[buffer][channel][16 * group]);
+              make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
       buffer ^= 1;
     }
