@@ -116,9 +116,13 @@ struct Bars {
 };
 
 // ---- softmax of one tile by the thread that owns the row -----------------------------------------
-// Common case: exact integer scores, not the last visited tile.  Pass 1 takes the maxima on the
-// raw integers (no conversion), pass 2 converts, scales, exponentiates and packs.
-template <bool CAPTURE, int CTA_K>
+// Common case: every score of the tile is visible and it is not the last visited tile.  Pass 1
+// takes the maxima on the raw integers (no conversion), pass 2 converts, scales, exponentiates and
+// packs.  KIND selects the reference's arithmetic: kScoresInt fuses the scale into one FMA per
+// score (unmasked, non-causal calls); kScoresScaled multiplies first and subtracts the maximum
+// afterwards (causal calls, for their tiles below the diagonal) -- the positive scale keeps the
+// maximum of the products equal to the product of the integer maximum.
+template <bool CAPTURE, int CTA_K, int KIND>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
                                                  uint16_t* sums, uint32_t s_free_bar) {
@@ -144,7 +148,10 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   }
   float gm[4];
 #pragma unroll
-  for (int g = 0; g < 4; ++g) gm[g] = fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset);
+  for (int g = 0; g < 4; ++g)
+    gm[g] = KIND == kScoresInt
+                ? fmaf(static_cast<float>(imax[g]), sc[g], -kU8Offset)
+                : fmaxf(static_cast<float>(imax[g]) * sc[g], -50000.0f) - kU8Offset;
   const float tile_m = fmaxf(fmaxf(gm[0], gm[1]), fmaxf(gm[2], gm[3]));
   const float neg_m = -tile_m;
   uint32_t numer = 0;
@@ -156,6 +163,13 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[i]));
+    if constexpr (KIND == kScoresScaled) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float s = sc[(i & 7) >> 1];
+        unpack_f32x2(mul_f32x2(pack_f32x2(x[i], x[i + 1]), pack_f32x2(s, s)), x[i], x[i + 1]);
+      }
+    }
     if (c > 0) {
       tmem_load32(tmem_row + 32 * (c - 1), raw);
     } else {
@@ -164,7 +178,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
       mbar_arrive(s_free_bar);
     }
     uint32_t P[8], s4[8];
-    tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, neg_m, P, numer, s4);
+    tile_exp_chunk<KIND, CAPTURE>(x, sc, neg_m, P, numer, s4);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
@@ -382,6 +396,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int row = bx * 128 + row_in;
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
     const bool int_scores = !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const bool causal_fast = a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
     const bool row_ok = row < a.q_len;
     const float scale2 = a.sm_scale * kLog2e;
     const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
@@ -416,9 +431,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
                       ((it >> 2) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
+      // causal: tiles that end at or before the CTA's first query are fully visible
+      const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       if (int_scores && !last)
-        softmax_tile_int<CAPTURE, CTA_K>(tmem_row, sc, p_row, row_in & 7, stat, my_sums,
-                                         bar(Bars::SFREE + sb));
+        softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
+                                                     my_sums, bar(Bars::SFREE + sb));
+      else if (below_diagonal && !last)
+        softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
+                                                        my_sums, bar(Bars::SFREE + sb));
       else {
         softmax_tile_general<CAPTURE, CTA_K>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                              row_in & 7, stat, my_sums, int_scores, last, row,
