@@ -51,19 +51,35 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
 
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
 
+// Per head_dim: what one CTA holds and how deep its rings are.  head_dim 256 is run as two CTAs per
+// (query block, head), each contracting Q.K^T over all 256 channels (two 128-byte column panels of
+// the Q and K tiles) but producing 128 of the output channels, so that the accumulator, the output
+// registers of the correction group and tensor memory stay exactly as for head_dim 128; the price
+// is that both CTAs do the softmax.  Its larger Q / K tiles are paid for with shallower rings.
+template <int D>
 struct SmemLayout {
+  static constexpr int kOut = D == 256 ? 128 : D;          // output channels per CTA
+  static constexpr int kHalves = D == 256 ? 2 : 1;         // CTAs per (query block, head)
+  static constexpr int kPanels = D == 256 ? 2 : 1;         // column panels of a Q / K tile
+  static constexpr int kPanelBytes = D == 64 ? 64 : 128;   // bytes per row of a panel
+  static constexpr int kKSt = D == 256 ? 2 : kKStages;     // K ring depth
+  static constexpr int kVSt = D == 256 ? 2 : kVStages;     // V ring depth
+  static constexpr int kSlots = D == 256 ? 3 : 4;          // P tiles and per-row statistics
+  static constexpr int kQKBytes = kPanels * kTile;         // one Q tile / one K stage
   static constexpr int q = 0;
-  static constexpr int k = q + kTile;
-  static constexpr int v = k + kKStages * kTile;
-  static constexpr int p = v + kVStages * kTile;
-  static constexpr int stats = p + 4 * kTile;             // float2 [4][128]: tile max, U8 sum
-  static constexpr int sums = stats + 4 * 128 * 8;        // uint16 [4][128][32] (capture only)
-  static constexpr int bars = sums + 4 * 128 * 64;        // 8-byte mbarriers
+  static constexpr int k = q + kQKBytes;
+  static constexpr int v = k + kKSt * kQKBytes;
+  static constexpr int p = v + kVSt * kTile;
+  static constexpr int stats = p + kSlots * kTile;         // float2 [slots][128]: tile max, U8 sum
+  static constexpr int sums = stats + 4 * 128 * 8;         // uint16 [slots][128][32] (capture only)
+  static constexpr int bars = sums + 4 * 128 * 64;         // 8-byte mbarriers
   static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int total = tmem_slot + 16;
+  static constexpr size_t bytes = total + 1024;            // room to align the base to 1024
 };
-constexpr size_t kSmemBytes = SmemLayout::total + 1024;  // room to align the base to 1024
+static_assert(SmemLayout<256>::bytes <= 232448 && SmemLayout<128>::bytes <= 232448,
+              "shared memory per CTA");
 
 struct TileSeq {
   int n_iter;
@@ -111,7 +127,7 @@ struct Bars {
   // S has three buffers (tile it uses it % 3), so the scores of a group's next tile are computed
   // while it is still busy with the current one; the P.V accumulator has one buffer, handed back
   // as soon as the correction group has it in registers; the probability tiles and the per-row
-  // statistics have four slots (it & 3).
+  // statistics have four slots (it % L::kSlots).
   __device__ __forceinline__ uint32_t operator()(int i) const { return base + 8u * i; }
 };
 
@@ -253,19 +269,21 @@ template <bool CAPTURE, int CTA_K, int D>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
+  using L = SmemLayout<D>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2;
-  const int bx = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int bx = blockIdx.x, head = blockIdx.y / L::kHalves, half = blockIdx.y % L::kHalves;
+  const int batch = blockIdx.z;
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const int n_k = (a.k_len + CTA_K - 1) / CTA_K, n_q = gridDim.x;
   const int64_t bh = int64_t(batch) * a.q_heads + head;
   const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
   unsigned int* error = &g_tc_status;
-  Bars bar{sbase + SmemLayout::bars};
+  Bars bar{sbase + L::bars};
 
   if (threadIdx.x == 0) {
     mbar_init(bar(Bars::QFULL), 1);
@@ -290,16 +308,16 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     }
     mbar_init_fence();
   }
-  if (warp == 17) tmem_alloc(sbase + SmemLayout::tmem_slot, 512);
+  if (warp == 17) tmem_alloc(sbase + L::tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::tmem_slot);
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + L::tmem_slot);
   const uint32_t tmem_o = tmem + 384;  // S buffers at columns 0, 128, 256
 
   const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE);
-  float2* stats = reinterpret_cast<float2*>(smem + SmemLayout::stats);
-  uint16_t* sums = reinterpret_cast<uint16_t*>(smem + SmemLayout::sums);
+  float2* stats = reinterpret_cast<float2*>(smem + L::stats);
+  uint16_t* sums = reinterpret_cast<uint16_t*>(smem + L::sums);
 
   if (wg == 4) {
     regs_dec<kRegsIssue>();
@@ -309,40 +327,45 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       tma_prefetch_descriptor(&map_k);
       tma_prefetch_descriptor(&map_v);
       mbar_expect_tx(bar(Bars::QFULL), 128 * D);
-      tma_load_3d(sbase + SmemLayout::q, &map_q, bar(Bars::QFULL), 0, bx * 128, int(bh));
+#pragma unroll
+      for (int panel = 0; panel < L::kPanels; ++panel)
+        tma_load_3d(sbase + L::q + panel * kTile, &map_q, bar(Bars::QFULL), 128 * panel, bx * 128,
+                    int(bh));
       bool ok = true;
       int k_issued = 0, v_issued = 0;
       // K runs two tiles ahead of V, matching the order in which the MMA warp consumes them.
       for (int step = 0; step < seq.n_iter + 2 && ok; ++step) {
         if (step < seq.n_iter) {
-          const int s = step % kKStages, r = step / kKStages;
+          const int s = step % L::kKSt, r = step / L::kKSt;
           ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
           if (!ok) break;
           mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * D);
-          tma_load_3d(sbase + SmemLayout::k + s * kTile, &map_k, bar(Bars::KFULL + s), 0,
-                      seq.tile(step) * CTA_K, int(kvh));
+#pragma unroll
+          for (int panel = 0; panel < L::kPanels; ++panel)
+            tma_load_3d(sbase + L::k + s * L::kQKBytes + panel * kTile, &map_k,
+                        bar(Bars::KFULL + s), 128 * panel, seq.tile(step) * CTA_K, int(kvh));
           k_issued = step + 1;
         }
         const int it = step - 2;
         if (it >= 0) {
-          const int s = it % kVStages, r = it / kVStages;
+          const int s = it % L::kVSt, r = it / L::kVSt;
           ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
           if (!ok) break;
           // V always arrives as the 128-key slab that holds the tile (64-key tiles use half of it):
           // rows stay 128 bytes wide, so one swizzle mode and one descriptor form serve both widths
-          mbar_expect_tx(bar(Bars::VFULL + s), D * 128);
-          tma_load_3d(sbase + SmemLayout::v + s * kTile, &map_v, bar(Bars::VFULL + s),
-                      (seq.tile(it) * CTA_K) & ~127, 0, int(kvh));
+          mbar_expect_tx(bar(Bars::VFULL + s), L::kOut * 128);
+          tma_load_3d(sbase + L::v + s * kTile, &map_v, bar(Bars::VFULL + s),
+                      (seq.tile(it) * CTA_K) & ~127, L::kOut * half, int(kvh));
           v_issued = it + 1;
         }
       }
       if (!ok) {
         // drain: every issued load must land before shared memory can be released
         mbar_wait(bar(Bars::QFULL), 0, error, 104);
-        for (int it = max(0, k_issued - kKStages); it < k_issued; ++it)
-          mbar_wait(bar(Bars::KFULL + it % kKStages), (it / kKStages) & 1, error, 105);
-        for (int it = max(0, v_issued - kVStages); it < v_issued; ++it)
-          mbar_wait(bar(Bars::VFULL + it % kVStages), (it / kVStages) & 1, error, 106);
+        for (int it = max(0, k_issued - L::kKSt); it < k_issued; ++it)
+          mbar_wait(bar(Bars::KFULL + it % L::kKSt), (it / L::kKSt) & 1, error, 105);
+        for (int it = max(0, v_issued - L::kVSt); it < v_issued; ++it)
+          mbar_wait(bar(Bars::VFULL + it % L::kVSt), (it / L::kVSt) & 1, error, 106);
       }
     } else if (warp == 17 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: S = Q.K^T
@@ -350,34 +373,38 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
       // round-trips on each.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, CTA_K);
-      const uint64_t desc_q = smem_desc_kmajor<D>(sbase + SmemLayout::q);
       bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
-        const int b = it % 3, u = it / 3, s = it % kKStages, r = it / kKStages;
+        const int b = it % 3, u = it / 3, s = it % L::kKSt, r = it / L::kKSt;
         ok = mbar_wait2<true>(bar(Bars::KFULL + s), r & 1, bar(Bars::SFREE + b), (u & 1) ^ 1,
                               error, 202);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t desc_k = smem_desc_kmajor<D>(sbase + SmemLayout::k + s * kTile);
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk)
-          mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, kk > 0);
+        for (int panel = 0; panel < L::kPanels; ++panel) {
+          const uint64_t desc_q = smem_desc_kmajor<L::kPanelBytes>(sbase + L::q + panel * kTile);
+          const uint64_t desc_k = smem_desc_kmajor<L::kPanelBytes>(
+              sbase + L::k + s * L::kQKBytes + panel * kTile);
+#pragma unroll
+          for (int kk = 0; kk < L::kPanelBytes / 32; ++kk)
+            mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, (panel | kk) > 0);
+        }
         mma_commit(bar(Bars::SFULL + b));
         mma_commit(bar(Bars::KEMPTY + s));
       }
     } else if (warp == 18 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: P.V
-      constexpr uint32_t idesc_pv = idesc_i8(false, true, D);
+      constexpr uint32_t idesc_pv = idesc_i8(false, true, L::kOut);
       bool ok = true;
       for (int it = 0; it < seq.n_iter && ok; ++it) {
-        const int s = it % kVStages, r = it / kVStages;
-        const int slot = it & 3, j = it >> 2;
+        const int s = it % L::kVSt, r = it / L::kVSt;
+        const int slot = it % L::kSlots, j = it / L::kSlots;
         ok = mbar_wait3<true>(bar(Bars::PFULL + slot), j & 1, bar(Bars::VFULL + s), r & 1,
                               bar(Bars::OFREE), (it & 1) ^ 1, error, 204);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t desc_p = smem_desc_k128(sbase + SmemLayout::p + slot * kTile);
-        const uint64_t desc_v = smem_desc_k128(sbase + SmemLayout::v + s * kTile);
+        const uint64_t desc_p = smem_desc_k128(sbase + L::p + slot * kTile);
+        const uint64_t desc_v = smem_desc_k128(sbase + L::v + s * kTile);
         // a 64-key tile is the first or second half (64 bytes per row) of its 128-key V slab
         const uint32_t v_k0 = CTA_K == 64 ? 4u * (seq.tile(it) & 1) : 0u;
 #pragma unroll
@@ -399,7 +426,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const bool causal_fast = a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
     const bool row_ok = row < a.q_len;
     const float scale2 = a.sm_scale * kLog2e;
-    const float q_scale = __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
+    const float q_scale =
+        D == 256 ? __ldg(a.q_scale + bh * (n_q * 64) + (row / 16) * 8 + (row & 7))
+                 : __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
     const float* k_scale = a.k_scale + kvh * (n_k * 4);
     bool ok = true;
     float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
@@ -423,12 +452,12 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
       // The P buffer is free once P.V of this group's previous tile is done, the statistics slot
       // once the correction group has read the tile four back; S is ready when the MMA warp says so.
-      const int slot = it & 3;
+      const int slot = it % L::kSlots;
       float2* stat = stats + slot * 128 + row_in;
       uint16_t* my_sums = sums + (slot * 128 + row_in) * 32;
-      unsigned char* p_row = smem + SmemLayout::p + slot * kTile + row_in * 128;
-      ok = mbar_wait3(bar(Bars::PFREE + slot), ((it >> 2) & 1) ^ 1, bar(Bars::STATFREE + slot),
-                      ((it >> 2) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
+      unsigned char* p_row = smem + L::p + slot * kTile + row_in * 128;
+      ok = mbar_wait3(bar(Bars::PFREE + slot), ((it / L::kSlots) & 1) ^ 1, bar(Bars::STATFREE + slot),
+                      ((it / L::kSlots) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
       if (!ok) break;
       tc_fence_after();
       // causal: tiles that end at or before the CTA's first query are fully visible
@@ -461,9 +490,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int64_t grow = bh * a.q_len + row;
     RowState st;
     row_state_init(st);
-    uint64_t O2[D / 2];
+    constexpr int kOut = L::kOut;
+    uint64_t O2[kOut / 2];
 #pragma unroll
-    for (int i = 0; i < D / 2; ++i) O2[i] = 0ull;
+    for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = true;
     // Software-pipelined by one tile: the statistics of tile `it` (running maximum, denominator,
     // weights) are consumed as soon as its probabilities exist, while the accumulator that is
@@ -475,9 +505,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (it < seq.n_iter) {
         const bool last_iter = it == seq.n_iter - 1;
         const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
-        ok = mbar_wait(bar(Bars::PFULL + (it & 3)), (it >> 2) & 1, error, 401);
+        ok = mbar_wait(bar(Bars::PFULL + (it % L::kSlots)), (it / L::kSlots) & 1, error, 401);
         if (!ok) break;
-        const int slot = it & 3;
+        const int slot = it % L::kSlots;
         const float2 stat = stats[slot * 128 + row_in];
         const uint32_t numer = __float_as_uint(stat.y);
         const TileScales ts = tile_begin(st, stat.x);
@@ -492,7 +522,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
             if (last) denominator_chunk<true>(st, ts, c == 0, s4);
             else denominator_chunk<false>(st, ts, c == 0, s4);
           }
-          if (row_ok) {
+          if (row_ok && half == 0) {
             if (last_iter) {
               float* out = cap.last + grow * 2;
               out[0] = static_cast<float>(numer);
@@ -518,14 +548,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         uint32_t acc[16];
         tmem_load16(tmem_o + lane_base, acc);
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
+        for (int c = 0; c < kOut / 16; ++c) {
           tmem_load_wait();
           uint64_t f2[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
                                static_cast<float>(int(acc[2 * i + 1])));
-          if (c < D / 16 - 1) {
+          if (c < kOut / 16 - 1) {
             tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
           } else {
             tc_fence_before();
@@ -542,23 +572,23 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
     }
-    float O[D];
+    float O[kOut];
 #pragma unroll
-    for (int i = 0; i < D / 2; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
+    for (int i = 0; i < kOut / 2; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {
-      if constexpr (CAPTURE) {
+      if (CAPTURE && half == 0) {
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
       const float inv = rcp_approx(denom);
       const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
-      const float* vs = a.v_scale + kvh * D;
-      const float* vc = a.v_center + kvh * D;
-      char* o_row = static_cast<char*>(a.o) +
+      const float* vs = a.v_scale + kvh * D + kOut * half;
+      const float* vc = a.v_center + kvh * D + kOut * half;
+      char* o_row = static_cast<char*>(a.o) + 2 * kOut * half +
                     2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
 #pragma unroll
-      for (int ch = 0; ch < D; ch += 8) {
+      for (int ch = 0; ch < kOut; ch += 8) {
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -577,7 +607,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         *reinterpret_cast<uint4*>(o_row + 2 * ch) =
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      if (a.lse) a.lse[grow] = row_lse(denom, st.m);
+      if (a.lse && half == 0) a.lse[grow] = row_lse(denom, st.m);
     }
   }
 
@@ -633,25 +663,26 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
   cudaGetDevice(&device);
   if (configured != device) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(kSmemBytes));
+                                         int(SmemLayout<D>::bytes));
     if (e != cudaSuccess)
       return fail(RISA_B200_CUDA, "attention: cannot reserve %zu bytes of shared memory: %s",
-                  kSmemBytes, cudaGetErrorString(e));
+                  SmemLayout<D>::bytes, cudaGetErrorString(e));
     configured = device;
   }
-  const dim3 grid((a.q_len + 127) / 128, a.q_heads, a.batch);
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, a);
+  const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D>::kHalves, a.batch);
+  kernel<<<grid, kThreads, SmemLayout<D>::bytes, stream>>>(map_q, map_k, map_v, a);
   return check_launch("attention (tensor-core kernel)");
 }
 
 }  // namespace
 
-// head_dim 128 with 64- or 128-key tiles and head_dim 64 with 64-key tiles (the only width the
-// packed formats define for it); every mask form, causal, tile lists, capture.  The packed V row
+// head_dim 128 and 256 with 64- or 128-key tiles and head_dim 64 with 64-key tiles (the only width
+// the packed formats define for it); every mask form, causal, tile lists, capture.  The packed V row
 // must hold at least one 128-key slab (the V box is always 128 keys wide).
 bool attention_tc_supported(const AttentionArgs& a) {
   const int64_t padded = int64_t((a.k_len + a.cta_k - 1) / a.cta_k) * a.cta_k;
-  const bool shape = (a.head_dim == 128 && (a.cta_k == 128 || a.cta_k == 64)) ||
+  const bool shape = ((a.head_dim == 128 || a.head_dim == 256) &&
+                      (a.cta_k == 128 || a.cta_k == 64)) ||
                      (a.head_dim == 64 && a.cta_k == 64);
   return shape && padded >= 128 && encode_fn() != nullptr &&
          reinterpret_cast<uintptr_t>(a.o) % 16 == 0 && a.o_stride_b % 8 == 0 &&
@@ -662,11 +693,22 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
   const int n_k = (a.k_len + a.cta_k - 1) / a.cta_k;
   const uint32_t d = uint32_t(a.head_dim);
   CUtensorMap map_q, map_k, map_v;
-  if (!make_map(&map_q, a.q, d, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads, d, 128) ||
-      !make_map(&map_k, a.k, d, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads, d, a.cta_k) ||
-      !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, d, uint64_t(a.batch) * a.kv_heads, 128, d))
+  const uint32_t panel = d < 128 ? d : 128;      // bytes per row of a Q / K box
+  const uint32_t v_rows = d == 256 ? 128 : d;    // output channels (V rows) per CTA
+  if (!make_map(&map_q, a.q, d, uint64_t(a.q_len), uint64_t(a.batch) * a.q_heads, panel, 128) ||
+      !make_map(&map_k, a.k, d, uint64_t(a.k_len), uint64_t(a.batch) * a.kv_heads, panel,
+                a.cta_k) ||
+      !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, d, uint64_t(a.batch) * a.kv_heads, 128,
+                v_rows))
     return fail(RISA_B200_CUDA, "attention: tensor map creation failed");
   const bool capture = a.block_mass != nullptr;
+  if (a.head_dim == 256) {
+    if (a.cta_k == 64)
+      return capture ? launch_tc<true, 64, 256>(a, map_q, map_k, map_v, stream)
+                     : launch_tc<false, 64, 256>(a, map_q, map_k, map_v, stream);
+    return capture ? launch_tc<true, 128, 256>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<false, 128, 256>(a, map_q, map_k, map_v, stream);
+  }
   if (a.head_dim == 64)
     return capture ? launch_tc<true, 64, 64>(a, map_q, map_k, map_v, stream)
                    : launch_tc<false, 64, 64>(a, map_q, map_k, map_v, stream);

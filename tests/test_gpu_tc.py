@@ -228,3 +228,40 @@ def test_tc_head_dim_64_capture_bit_exact(ref, causal):
     got_s = _ours(pk, sm_scale=0.125, path=0, is_causal=causal, row_offsets=ro, block_indices=bi)
     _status()
     assert_outputs_match(got_s["out"], want_s["out"], TOL)
+
+
+@pytest.mark.parametrize("cta_k", [64, 128])
+@pytest.mark.parametrize("mask_kind", ["none", "key_bias", "bias_4d"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_head_dim_256(ref, cta_k, mask_kind, causal):
+    """head_dim 256: two CTAs per (query block, head), each contracting over all 256 channels
+    (two column panels) and producing 128 output channels."""
+    from tests.test_gpu_attention import _masks
+
+    if mask_kind == "bias_4d" and cta_k == 128:
+        pytest.skip("per-query masks always use 64-key tiles")
+    lq, lk, hq, hkv = 300, 1153, 4, 2
+    _, _, _, pk = _packed(ref, 256, lq, lk, hq, hkv, cta_k, affine=True, seed=cta_k)
+    mask = _masks(mask_kind, 1, hq, lq, lk)
+    for scale in (256 ** -0.5, -0.125):
+        want = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, want_lse=True)
+        rows = _ours(pk, sm_scale=scale, path=1, mask=mask, is_causal=causal, want_lse=True)
+        got = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, want_lse=True)
+        _status()
+        assert_outputs_match(got["out"], want["out"], TOL)
+        assert_outputs_match(got["out"], rows["out"], TOL)
+        fin = torch.isfinite(want["lse"])
+        torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0,
+                                   atol=2e-4 if mask_kind == "none" else 5e-4)
+
+
+@pytest.mark.parametrize("cta_k", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_head_dim_256_capture_bit_exact(ref, cta_k, causal):
+    lq, lk, hq, hkv = 300, 1153, 4, 2
+    _, _, _, pk = _packed(ref, 256, lq, lk, hq, hkv, cta_k, seed=31)
+    want = ref.attention(pk, sm_scale=0.0625, is_causal=causal, capture=True)
+    got = _ours(pk, sm_scale=0.0625, path=0, is_causal=causal, capture=True)
+    _status()
+    assert torch.equal(got["workspace"].view(torch.int32), want["workspace"].view(torch.int32))
+    assert torch.equal(got["out"], want["out"])
