@@ -47,7 +47,7 @@ B, HQ, HKV, D = 1, 16, 4, 128
 METRIC = "dense_equiv_int8_tops_32k_full_call"
 # DRAM bytes (read + written) of one attention_tc_kernel launch from an ncu capture of this script,
 # keyed by (sequence length, query heads on the GPU); other shapes report null.
-NCU_DRAM_BYTES_PER_LAUNCH = {(32768, 16): 101876224 + 84157184}
+NCU_DRAM_BYTES_PER_LAUNCH = {(32768, 16): 101399808 + 83646976}
 
 
 def dense_ops(batch, heads, lq, lk, d):
@@ -108,15 +108,54 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
+    # NVML reason bits (nvml.h): sw_power_cap 0x4, hw_slowdown 0x8, sw_thermal 0x20, hw_thermal 0x40
+    NVML_REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                    0x40: "hw_thermal_slowdown"}
+
     def __init__(self, index):
         self.index = index
         self.proc = None
+        self.thread = None
+        self.samples = []
+
+    def _poll_nvml(self, pynvml, handle):
+        while not self.stop:
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                mx = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                try:
+                    bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except AttributeError:
+                    bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((float(sm), float(mx), int(bits)))
+            except Exception:
+                break
+            time.sleep(0.005)
 
     def __enter__(self):
+        # read-only NVML polling every 5 ms (several samples inside a 100 ms timed region);
+        # nvidia-smi in a loop is the fallback
+        try:
+            import pynvml
+            import threading
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.index
+            if visible:
+                entry = visible.split(",")[self.index]
+                index = int(entry) if entry.isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.stop = False
+            self.thread = threading.Thread(target=self._poll_nvml, args=(pynvml, handle),
+                                           daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                 "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -124,6 +163,18 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread is not None:
+            self.stop = True
+            self.thread.join(timeout=2)
+            if self.samples:
+                reasons = set()
+                for _, _, bits in self.samples:
+                    reasons.update(name for bit, name in self.NVML_REASONS.items() if bits & bit)
+                self.result = {"sm_mhz": statistics.median(s[0] for s in self.samples),
+                               "sm_max_mhz": max(s[1] for s in self.samples),
+                               "reasons": sorted(reasons), "samples": len(self.samples),
+                               "source": "nvml, 5 ms period"}
+            return
         if self.proc is None:
             return
         self.proc.terminate()
@@ -148,7 +199,8 @@ class ClockSampler:
                     reasons.add(name)
         if sm:
             self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx),
-                           "reasons": sorted(reasons), "samples": len(sm)}
+                           "reasons": sorted(reasons), "samples": len(sm),
+                           "source": "nvidia-smi -lms 50"}
 
 
 def event_time_ms(fn, steps, warmup, barrier=None):
