@@ -678,14 +678,16 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
 
 // head_dim 128 and 256 with 64- or 128-key tiles and head_dim 64 with 64-key tiles (the only width
 // the packed formats define for it); every mask form, causal, tile lists, capture.  The packed V row
-// must hold at least one 128-key slab (the V box is always 128 keys wide).
+// must hold at least one 128-key slab (the V box is always 128 keys wide) and TMA needs 16-byte
+// aligned operand bases; anything else goes to the row-per-thread kernel.
 bool attention_tc_supported(const AttentionArgs& a) {
   const int64_t padded = int64_t((a.k_len + a.cta_k - 1) / a.cta_k) * a.cta_k;
   const bool shape = ((a.head_dim == 128 || a.head_dim == 256) &&
                       (a.cta_k == 128 || a.cta_k == 64)) ||
                      (a.head_dim == 64 && a.cta_k == 64);
-  return shape && padded >= 128 && encode_fn() != nullptr &&
-         reinterpret_cast<uintptr_t>(a.o) % 16 == 0 && a.o_stride_b % 8 == 0 &&
+  auto aligned16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  return shape && padded >= 128 && encode_fn() != nullptr && aligned16(a.q) && aligned16(a.k) &&
+         aligned16(a.v) && aligned16(a.o) && a.o_stride_b % 8 == 0 &&
          a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
 }
 
