@@ -2,7 +2,7 @@
 # Test infrastructure, not product code.
 #
 # Compiles the reference project's own CUDA kernel sources, unmodified and from
-# where they lie (REF_ROOT, default /root/reference), into
+# where they lie (the checkout named by REF_ROOT), into
 # oracle/_ref/librisa_ref.so together with ref_shim.cpp (exception-catching
 # C wrappers around the reference's extern "C" launchers, csrc/launchers.h:8-64).
 # Flags follow the reference's csrc/CMakeLists.txt:30-44 because --use_fast_math
