@@ -500,6 +500,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     // folded into O in the same iteration is the one of tile it - 1, whose P.V had the whole
     // softmax time of tile `it` to finish.  The group therefore never idles on a P.V in flight.
     float prev_o_scale = 1.0f, prev_w = 0.0f;
+    float m_o = -INFINITY;  // maximum the FP32 output rows are scaled to (dense path only)
     for (int it = 0; it <= seq.n_iter && ok; ++it) {
       float cur_o_scale = 1.0f, cur_w = 0.0f;
       if (it < seq.n_iter) {
@@ -535,6 +536,15 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           }
         } else {
           denominator_single(st, ts, numer);
+          // the output rows follow a stale maximum that is only moved when the true one has run
+          // ahead by 2^8: almost no tile then needs the accumulated row rescaled
+          float factor = 1.0f;
+          if (st.m > m_o + 8.0f) {
+            factor = ex2_approx(m_o - st.m);
+            m_o = st.m;
+          }
+          cur_o_scale = factor;
+          cur_w = ex2_approx(stat.x - m_o);
         }
         mbar_arrive(bar(Bars::STATFREE + slot));
       }
@@ -581,7 +591,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
-      const float inv = rcp_approx(denom);
+      // dense path: bring the rows from the stale maximum to the final one together with 1 / d
+      const float inv = CAPTURE ? rcp_approx(denom) : rcp_approx(denom) * ex2_approx(m_o - st.m);
       const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
       const float* vs = a.v_scale + kvh * D + kOut * half;
       const float* vc = a.v_center + kvh * D + kOut * half;

@@ -144,15 +144,18 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
       P[4 * j + g] = __byte_perm(lo, hi, 0x5410);
     }
   }
+  uint32_t odd = 0;  // second partial sum: two short dependent chains instead of one
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     if constexpr (WANT_SUMS) {
       s4[w] = __dp4a(P[w], 0x01010101u, 0u);
       numer += s4[w];
     } else {
-      numer = __dp4a(P[w], 0x01010101u, numer);
+      if (w & 1) odd = __dp4a(P[w], 0x01010101u, odd);
+      else numer = __dp4a(P[w], 0x01010101u, numer);
     }
   }
+  numer += odd;
 }
 
 // Advances the four denominator partials over one chunk in the reference's order: one FMA per
