@@ -495,14 +495,45 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = true;
-    // Software-pipelined by one tile: the statistics of tile `it` (running maximum, denominator,
-    // weights) are consumed as soon as its probabilities exist, while the accumulator that is
-    // folded into O in the same iteration is the one of tile it - 1, whose P.V had the whole
-    // softmax time of tile `it` to finish.  The group therefore never idles on a P.V in flight.
+    // Software-pipelined by one tile.  Each iteration first folds the accumulator of tile it - 1
+    // (whose weights were computed in the previous iteration) and hands it back, so that the P.V
+    // of tile `it` can start the moment its probabilities exist; then it consumes the statistics
+    // of tile `it` (running maximum, denominator, weights).
     float prev_o_scale = 1.0f, prev_w = 0.0f;
     float m_o = -INFINITY;  // maximum the FP32 output rows are scaled to (dense path only)
     for (int it = 0; it <= seq.n_iter && ok; ++it) {
       float cur_o_scale = 1.0f, cur_w = 0.0f;
+      if (it >= 1) {
+        const int j = it - 1;
+        ok = mbar_wait(bar(Bars::OFULL), j & 1, error, 402);
+        if (!ok) break;
+        tc_fence_after();
+        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
+        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
+        uint32_t acc[16];
+        tmem_load16(tmem_o + lane_base, acc);
+#pragma unroll
+        for (int c = 0; c < kOut / 16; ++c) {
+          tmem_load_wait();
+          uint64_t f2[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
+                               static_cast<float>(int(acc[2 * i + 1])));
+          if (c < kOut / 16 - 1) {
+            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
+          } else {
+            tc_fence_before();
+            mbar_arrive(bar(Bars::OFREE));
+          }
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
+        }
+      }
       if (it < seq.n_iter) {
         const bool last_iter = it == seq.n_iter - 1;
         const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
@@ -547,37 +578,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           cur_w = ex2_approx(stat.x - m_o);
         }
         mbar_arrive(bar(Bars::STATFREE + slot));
-      }
-      if (it >= 1) {
-        const int j = it - 1;
-        ok = mbar_wait(bar(Bars::OFULL), j & 1, error, 402);
-        if (!ok) break;
-        tc_fence_after();
-        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
-        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
-        uint32_t acc[16];
-        tmem_load16(tmem_o + lane_base, acc);
-#pragma unroll
-        for (int c = 0; c < kOut / 16; ++c) {
-          tmem_load_wait();
-          uint64_t f2[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
-                               static_cast<float>(int(acc[2 * i + 1])));
-          if (c < kOut / 16 - 1) {
-            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
-          } else {
-            tc_fence_before();
-            mbar_arrive(bar(Bars::OFREE));
-          }
-          if (rescale) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
-        }
       }
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
