@@ -2,8 +2,8 @@
 
 A caller whose Q/K/V live in (pinned) host memory pays two PCIe transfers around the kernels.  The
 path is independent per (batch, KV head) -- the same property the multi-GPU sharding uses -- so the
-call is cut into one stage per KV head and its query heads, and the stages are pipelined over three
-streams: host-to-device copies of stage g+1 and the device-to-host copy of stage g-1 run while
+call is cut into stages of one KV head and (some of) its query heads, and the stages are pipelined over
+three streams: host-to-device copies of stage g+1 and the device-to-host copy of stage g-1 run while
 stage g computes.  Results are identical to a single device-resident call (every stage runs the
 same kernels on the same per-head data).  The reference has no counterpart: its API takes CUDA
 tensors only.
@@ -49,27 +49,43 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     start.record(compute)
     copy_in.wait_event(start)  # inputs written by earlier work on the caller's stream are visible
     copy_out.wait_event(start)
-    keep = []
+    # Stages: one per (batch, KV head) with all of its query heads, except that the very first and
+    # the very last stage of the call carry a single query head, because the upload of the first
+    # stage and the download of the last one are the only transfers nothing can hide (their K/V
+    # head is quantised once more for the split-off heads, which costs far less than it saves).
+    stages = []
     for b in range(batch):
         for h in range(kv_heads):
-            qs = slice(h * group, (h + 1) * group)
-            with torch.cuda.stream(copy_in):
-                dq = query[b:b + 1, qs].to(device, non_blocking=True)
-                dk = key[b:b + 1, h:h + 1].to(device, non_blocking=True)
-                dv = value[b:b + 1, h:h + 1].to(device, non_blocking=True)
-                ready = torch.cuda.Event()
-                ready.record(copy_in)
-            compute.wait_event(ready)
-            for t in (dq, dk, dv):
-                t.record_stream(compute)
-            result = int8_attention(dq, dk, dv, **kwargs)
-            done = torch.cuda.Event()
-            done.record(compute)
-            copy_out.wait_event(done)
-            result.record_stream(copy_out)
-            with torch.cuda.stream(copy_out):
-                out[b:b + 1, qs].copy_(result, non_blocking=True)
-            keep.append((dq, dk, dv, result))
+            stages.append((b, h, h * group, (h + 1) * group))
+    b, h, lo, hi = stages[0]
+    if hi - lo > 1:
+        stages[0:1] = [(b, h, lo, lo + 1), (b, h, lo + 1, hi)]
+    b, h, lo, hi = stages[-1]
+    if hi - lo > 1:
+        stages[-1:] = [(b, h, lo, hi - 1), (b, h, hi - 1, hi)]
+    keep = []
+    resident = (None, None, None)  # (batch, KV head) whose K and V are on the device, and the tensors
+    for b, h, lo, hi in stages:
+        qs = slice(lo, hi)
+        with torch.cuda.stream(copy_in):
+            dq = query[b:b + 1, qs].to(device, non_blocking=True)
+            if resident[0] != (b, h):  # K / V travel once per KV head, also when its stage is split
+                resident = ((b, h), key[b:b + 1, h:h + 1].to(device, non_blocking=True),
+                            value[b:b + 1, h:h + 1].to(device, non_blocking=True))
+            dk, dv = resident[1], resident[2]
+            ready = torch.cuda.Event()
+            ready.record(copy_in)
+        compute.wait_event(ready)
+        for t in (dq, dk, dv):
+            t.record_stream(compute)
+        result = int8_attention(dq, dk, dv, **kwargs)
+        done = torch.cuda.Event()
+        done.record(compute)
+        copy_out.wait_event(done)
+        result.record_stream(copy_out)
+        with torch.cuda.stream(copy_out):
+            out[b:b + 1, qs].copy_(result, non_blocking=True)
+        keep.append((dq, dk, dv, result))
     finished = torch.cuda.Event()
     finished.record(copy_out)
     compute.wait_event(finished)  # the caller's stream sees the output once this event has passed
