@@ -43,12 +43,15 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     elif out.shape != query.shape or out.device.type != "cpu" or not out.is_contiguous():
         raise ValueError("out must be a contiguous CPU tensor of q's shape")
 
-    compute = torch.cuda.current_stream(device)
+    caller = torch.cuda.current_stream(device)
+    # Two compute streams taken in turn: the last, partly filled wave of CTAs of one stage then
+    # overlaps the first wave of the next stage instead of leaving SMs idle at every stage boundary.
+    computes = (torch.cuda.Stream(device), torch.cuda.Stream(device))
     copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     start = torch.cuda.Event()
-    start.record(compute)
-    copy_in.wait_event(start)  # inputs written by earlier work on the caller's stream are visible
-    copy_out.wait_event(start)
+    start.record(caller)
+    for stream in (*computes, copy_in, copy_out):
+        stream.wait_event(start)  # work queued earlier on the caller's stream comes first
     # Stages: one per (batch, KV head) with all of its query heads, except that the very first and
     # the very last stage of the call carry a single query head, because the upload of the first
     # stage and the download of the last one are the only transfers nothing can hide (their K/V
@@ -65,8 +68,9 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
         stages[-1:] = [(b, h, lo, hi - 1), (b, h, hi - 1, hi)]
     keep = []
     resident = (None, None, None)  # (batch, KV head) whose K and V are on the device, and the tensors
-    for b, h, lo, hi in stages:
+    for index, (b, h, lo, hi) in enumerate(stages):
         qs = slice(lo, hi)
+        compute = computes[index % 2]
         with torch.cuda.stream(copy_in):
             dq = query[b:b + 1, qs].to(device, non_blocking=True)
             if resident[0] != (b, h):  # K / V travel once per KV head, also when its stage is split
@@ -78,9 +82,10 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
         compute.wait_event(ready)
         for t in (dq, dk, dv):
             t.record_stream(compute)
-        result = int8_attention(dq, dk, dv, **kwargs)
-        done = torch.cuda.Event()
-        done.record(compute)
+        with torch.cuda.stream(compute):
+            result = int8_attention(dq, dk, dv, **kwargs)
+            done = torch.cuda.Event()
+            done.record(compute)
         copy_out.wait_event(done)
         result.record_stream(copy_out)
         with torch.cuda.stream(copy_out):
@@ -88,5 +93,5 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
         keep.append((dq, dk, dv, result))
     finished = torch.cuda.Event()
     finished.record(copy_out)
-    compute.wait_event(finished)  # the caller's stream sees the output once this event has passed
+    caller.wait_event(finished)  # the caller's stream sees the output once this event has passed
     return out
