@@ -49,6 +49,11 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
                   kThreads * kRegsLaunch,
               "register budget exceeds the launch pool");
 
+// Unroll factor of the exponent pass over a tile's 32-column chunks: two copies of the chunk body
+// measured fastest (one copy leaves the loads too little to hide behind, four copies fall out of the
+// instruction cache next to the other roles' code).
+constexpr int kExpUnroll = 2;
+
 __device__ unsigned int g_tc_status;  // first failing wait site since the last status query
 
 // Per head_dim: what one CTA holds and how deep its rings are.  head_dim 256 is run as two CTAs per
@@ -152,6 +157,8 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     tmem_load32(tmem_row + 64 * h, raw_a);
     tmem_load32(tmem_row + 64 * h + 32, raw);
     tmem_load_wait();
+    tmem_regs_ready<32>(raw_a);
+    tmem_regs_ready<32>(raw);
     // columns of K scale group g inside a chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -171,20 +178,21 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   const float tile_m = fmaxf(fmaxf(gm[0], gm[1]), fmaxf(gm[2], gm[3]));
   const float neg_m = -tile_m;
   uint32_t numer = 0;
-  // One copy of the chunk body (rolled loop): the chunk is converted to floats as soon as it
-  // lands, which frees the landing registers for the next chunk's load to overlap the exponentials.
-#pragma unroll 1
+  // The chunk is converted to floats as soon as it lands, which frees the landing registers for
+  // the next chunk's load to overlap the exponentials.
+#pragma unroll kExpUnroll
   for (int c = CTA_K / 32 - 1; c >= 0; --c) {
     tmem_load_wait();
+    tmem_regs_ready<32>(raw);
     float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = static_cast<float>(int(raw[i]));
     if constexpr (KIND == kScoresScaled) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float s = sc[(i & 7) >> 1];
-        unpack_f32x2(mul_f32x2(pack_f32x2(x[i], x[i + 1]), pack_f32x2(s, s)), x[i], x[i + 1]);
-      }
+      // one rounding for the product, a second one when the maximum is subtracted (the reference's
+      // pre-scaled arithmetic); scalar multiplies with an explicit rounding mode on purpose: a packed
+      // multiply followed by the packed add was observed to be merged into one fused operation
+      for (int i = 0; i < 32; ++i) x[i] = __fmul_rn(x[i], sc[(i & 7) >> 1]);
     }
     if (c > 0) {
       tmem_load32(tmem_row + 32 * (c - 1), raw);
@@ -220,6 +228,7 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
     uint32_t raw[32];
     tmem_load32(tmem_row + 32 * c, raw);
     tmem_load_wait();
+    tmem_regs_ready<32>(raw);
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int kv = c0 + 32 * c + i;
@@ -228,7 +237,7 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
         if (last && kv >= k_len) s = -1.0e30f;
       } else {
         if (masked) s = apply_mask(a, batch, head, row, kv, row_ok, s, sc[(i & 7) >> 1]);
-        else s *= sc[(i & 7) >> 1];
+        else s = __fmul_rn(s, sc[(i & 7) >> 1]);
         if (causal && kv > row) s = -INFINITY;
         if (last && kv >= k_len) s = -INFINITY;
       }
@@ -515,6 +524,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
         for (int c = 0; c < kOut / 16; ++c) {
           tmem_load_wait();
+          tmem_regs_ready<16>(acc);
           uint64_t f2[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i)

@@ -175,6 +175,21 @@ __device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t* r) {
 __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The registers a tcgen05.ld names are undefined until the wait above, but the wait does not
+// mention them, so the compiler sees no dependency and may schedule their readers in front of it.
+// This empty volatile statement, placed right after the wait (volatile statements keep their
+// order), takes the registers in and out: every later reader now depends on it.  No instruction.
+template <int N>
+__device__ __forceinline__ void tmem_regs_ready(uint32_t* r) {
+  static_assert(N % 16 == 0, "register block");
+#pragma unroll
+  for (int i = 0; i < N; i += 16)
+    asm volatile(""
+                 : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]),
+                   "+r"(r[i + 5]), "+r"(r[i + 6]), "+r"(r[i + 7]), "+r"(r[i + 8]), "+r"(r[i + 9]),
+                   "+r"(r[i + 10]), "+r"(r[i + 11]), "+r"(r[i + 12]), "+r"(r[i + 13]),
+                   "+r"(r[i + 14]), "+r"(r[i + 15]));
+}
 
 // ---- register budget per warpgroup (all four warps of an aligned group of 128 threads) ----------
 template <int N> __device__ __forceinline__ void regs_dec() {
