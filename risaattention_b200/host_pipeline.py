@@ -14,6 +14,8 @@ import torch
 
 from .dense import int8_attention
 
+_STREAMS: dict = {}
+
 
 def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                              out: torch.Tensor | None = None, *, device=None, **kwargs):
@@ -46,8 +48,12 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     caller = torch.cuda.current_stream(device)
     # Two compute streams taken in turn: the last, partly filled wave of CTAs of one stage then
     # overlaps the first wave of the next stage instead of leaving SMs idle at every stage boundary.
-    computes = (torch.cuda.Stream(device), torch.cuda.Stream(device))
-    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    # The four side streams are created once per device and reused: the caching allocator keeps its
+    # free blocks per stream, so fresh streams on every call would send every stage to cudaMalloc.
+    streams = _STREAMS.get(device)
+    if streams is None:
+        streams = _STREAMS[device] = tuple(torch.cuda.Stream(device) for _ in range(4))
+    computes, copy_in, copy_out = streams[:2], streams[2], streams[3]
     start = torch.cuda.Event()
     start.record(caller)
     for stream in (*computes, copy_in, copy_out):
