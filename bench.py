@@ -2,25 +2,33 @@
 """Benchmark of the quantised-attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--seq-len 32768] [--scaling weak|strong]
+                    [--seq-len 32768] [--scaling strong|weak] [--no-extras]
 
-Workload (N = 1): the reference's dense sweep at 32K -- ``int8_attention`` on B=1, Hq=16, Hkv=4,
-D=128, bf16, Lq=Lk=32768, HND contiguous, q/k/v i.i.d. N(0,1) from ``torch.Generator(seed 0)`` in
-the reference's generator order (benchmarks/common.py:105-131).  A step is one full call (K anchor,
+Workload: the reference's dense sweep at 32K -- ``int8_attention`` on B=1, Hq=16, Hkv=4, D=128,
+bf16, Lq=Lk=32768, HND contiguous, q/k/v i.i.d. N(0,1) from ``torch.Generator(seed 0)`` in the
+reference's generator order (benchmarks/common.py:105-131).  A step is one full call (K anchor,
 Q/K/V quantisation, fused attention).  ``value`` is dense-equivalent INT8 TOPS,
 4*B*Hq*Lq*Lk*D / time (benchmarks/plot_scaling.py:66-74), with inputs resident in HBM;
-``ms_per_step`` is the full-call latency.  ``e2e`` is the same metric through the public API with
-the inputs in pinned host memory: the timed region copies q, k, v to the device and the output back
-every step.  ``roofline`` is for the dominant kernel (the fused attention kernel, tensor bound)
-timed alone with CUDA events; ``prep_roofline`` gives the HBM-bound preparation kernels.
-``cpu_baseline`` times the CPU restatement of the path (oracle/) on a bounded sample;
-``reference_kernels_on_this_gpu`` times the reference project's own CUDA kernels (oracle/_ref)
-on the same inputs when that library is present.  Extra keys report sparse reuse.
+``ms_per_step`` is the full-call latency.  ``e2e`` is the same metric through the public
+host-operand call with the inputs in pinned host memory: the timed region copies q, k, v to the
+device and the output back every step.  ``roofline`` is for the dominant kernel (the fused
+attention kernel, tensor bound) timed alone with CUDA events; ``prep_roofline`` gives the HBM-bound
+preparation kernels.  ``cpu_baseline`` times the CPU restatement of the path (oracle/) on a bounded
+sample; ``reference_kernels_on_this_gpu`` times the reference project's own CUDA kernels
+(oracle/_ref) on the same inputs when that library is present.  Further keys (N = 1 only, skipped by
+``--no-extras``): ``dense_sweep`` (every length x V mode of the sweep under the reference's timing
+protocol: 200 warm-up calls, 10 samples of 20 calls, median per seed, median over seeds 0/1/2),
+``sparse_reuse`` on both sparse workloads, ``video_dit`` (one GPU's 5 heads at L=32760) and
+``edge_sweep`` (Hq32 Hkv8 Lq4096 Lk16384, D 64 / 256).
 
-N > 1 (launched by torchrun, one rank per GPU): the path has no exchange step.  ``--scaling weak``
-(default) gives every rank its own 32K call (global batch N); ``--scaling strong`` splits the 16
-query heads of one call over the ranks with KV heads co-located (risaattention_b200/sharding.py).
-Timing: max over ranks of CUDA-event time, bracketed by barriers.
+N > 1 (launched by torchrun, one rank per GPU).  The path has no exchange step.  Default
+(``--scaling strong``): ONE 32K call whose 16 query heads are split over the ranks with KV heads
+co-located, or replicated when there are more ranks than KV heads (risaattention_b200/sharding.py);
+``value`` = ops of the whole call / max-over-ranks time.  Extra keys: CTA waves per rank,
+``gather_ms`` (NCCL all-gather of the per-rank outputs, for callers that want the result on one
+device; not part of the timed step) and ``sharding_check`` (gathered output and merged sparse
+pattern compared bit for bit with a single-GPU run on rank 0).  ``--scaling weak`` gives every rank
+its own full 32K call instead.  Timing: max over ranks of CUDA-event time, bracketed by barriers.
 
 ``--impl reference`` times the reference's CPU path.  The reference ships no CPU implementation of
 this path (its Python refuses non-CUDA tensors), so this arm runs the CPU restatement in oracle/ on
@@ -48,6 +56,8 @@ METRIC = "dense_equiv_int8_tops_32k_full_call"
 # DRAM bytes (read + written) of one attention_tc_kernel launch from an ncu capture of this script,
 # keyed by (sequence length, query heads on the GPU); other shapes report null.
 NCU_DRAM_BYTES_PER_LAUNCH = {(32768, 16): 101529856 + 81629696}
+# kernels the library launches for one unmasked dense call: K anchor, Q, K, V range, V codes, attention
+KERNELS_PER_DENSE_CALL = 6
 
 
 def dense_ops(batch, heads, lq, lk, d):
@@ -63,42 +73,10 @@ def measured_peaks():
 
 
 def make_inputs(seq_len, device, seed=0, heads=HQ, kv_heads=HKV, batch=B):
-    g = torch.Generator(device=device).manual_seed(seed)
-    q = torch.randn(batch, heads, seq_len, D, device=device, generator=g).bfloat16()
-    k = torch.randn(batch, kv_heads, seq_len, D, device=device, generator=g).bfloat16()
-    v = torch.randn(batch, kv_heads, seq_len, D, device=device, generator=g).bfloat16()
-    return q, k, v
+    from risaattention_b200 import synthetic
 
-
-def block_structured_inputs(seq_len, device, seed=0):
-    """Sparse-reuse generator of the benchmark spec: one centroid per 128-token block and head,
-    tokens = centroid + 0.5 N(0,1); V ~ N(0,1)."""
-    g = torch.Generator(device=device).manual_seed(seed)
-
-    def blocks(heads):
-        cent = torch.randn(B, heads, seq_len // 128, 1, D, device=device, generator=g)
-        noise = torch.randn(B, heads, seq_len // 128, 128, D, device=device, generator=g)
-        return (cent + 0.5 * noise).reshape(B, heads, seq_len, D).bfloat16()
-
-    q, k = blocks(HQ), blocks(HKV)
-    v = torch.randn(B, HKV, seq_len, D, device=device, generator=g).bfloat16()
-    return q, k, v, g
-
-
-def video_blocks_inputs(seq_len, device, seed=0, clusters=2, prototype_norm=8.0):
-    """The reference's own sparse-benchmark generator (benchmarks/sparse.py:33-52): N(0,1) q/k/v
-    plus, per KV head, `clusters` unit-direction prototypes of norm 8 added to Q and K by
-    128-token block (block index modulo clusters)."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    q = torch.randn(B, HQ, seq_len, D, device=device, generator=g).bfloat16()
-    k = torch.randn(B, HKV, seq_len, D, device=device, generator=g).bfloat16()
-    v = torch.randn(B, HKV, seq_len, D, device=device, generator=g).bfloat16()
-    proto = torch.randn(B, HKV, clusters, D, device=device, generator=g)
-    proto *= prototype_norm / proto.norm(dim=-1, keepdim=True)
-    cluster = torch.arange(seq_len, device=device).div(128, rounding_mode="floor") % clusters
-    q = q + proto.repeat_interleave(HQ // HKV, dim=1)[:, :, cluster].to(q.dtype)
-    k = k + proto[:, :, cluster].to(k.dtype)
-    return q, k, v, g
+    return synthetic.dense_inputs(seq_len, device, seed=seed, q_heads=heads, kv_heads=kv_heads,
+                                  head_dim=D, batch=batch)
 
 
 class ClockSampler:
@@ -263,8 +241,9 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
-        "data": "synthetic",
+        "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 and args.scaling == "strong" else "weak",
+        "vs_baseline": None, "dtype": "s8", "data": "synthetic",
         "config": {"workload": f"dense int8_attention B{B} Hq{HQ} Hkv{HKV} D{D} L{args.seq_len} bf16",
                    "note": "reference has no CPU path; CPU restatement timed; ms_per_step is the "
                            "sample time scaled to the full workload"},
@@ -341,36 +320,198 @@ def accuracy_leg(q, k, v, out_ours, seq_len):
     return result
 
 
-def sparse_leg(seq_len, device, steps, generator="video_blocks"):
+def sparse_leg(seq_len, device, steps, workload="video_blocks"):
     import risaattention_b200 as risa
+    from risaattention_b200 import synthetic
 
-    if generator == "video_blocks":
-        q, k, v, g = video_blocks_inputs(seq_len, device)
+    if workload == "video_blocks":
+        q, k, v, g = synthetic.video_block_inputs(seq_len, device)
     else:
-        q, k, v, g = block_structured_inputs(seq_len, device)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
+        q, k, v, g = synthetic.block_centroid_inputs(seq_len, device)
     _, pattern = risa.construct_sparse_int8_attention(q, k, v, theta=0.99)
-    torch.cuda.synchronize()
-    construct_ms = (time.perf_counter() - t0) * 1e3
-    construct_ms = min(construct_ms, event_time_ms(
-        lambda: risa.construct_sparse_int8_attention(q, k, v, theta=0.99), 2, 1))
-
-    def drift(x):
-        noise = torch.randn(x.shape, device=device, generator=g)
-        if generator == "video_blocks":  # additive drift, as the reference benchmark
-            return (x.float() + 0.05 * noise).bfloat16()
-        return (0.95 * x.float() + 0.05 * noise).bfloat16()
-
-    q2, k2, v2 = drift(q), drift(k), drift(v)
+    construct_ms = event_time_ms(
+        lambda: risa.construct_sparse_int8_attention(q, k, v, theta=0.99), max(2, steps // 2), 2)
+    kind = "additive" if workload == "video_blocks" else "blend"
+    q2, k2, v2 = (synthetic.drift(t, g, kind) for t in (q, k, v))
     sparse_ms = event_time_ms(lambda: risa.sparse_int8_attention(q2, k2, v2, pattern), steps, 3)
     dense_ms = event_time_ms(lambda: risa.int8_attention(q2, k2, v2), steps, 3)
     return {"seq_len": seq_len, "theta": 0.99, "coverage": pattern.coverage,
             "construct_ms": construct_ms, "sparse_ms": sparse_ms, "dense_ms": dense_ms,
+            "construct_over_dense": construct_ms / dense_ms,
             "speedup_vs_dense": dense_ms / sparse_ms,
             "inputs": ("reference generator: 2 alternating prototypes of norm 8 per KV head added to "
-                       "N(0,1) Q/K, additive drift 0.05" if generator == "video_blocks" else
+                       "N(0,1) Q/K, additive drift 0.05" if workload == "video_blocks" else
                        "per-128-token-block centroids + 0.5 N(0,1); reuse on 0.95 x + 0.05 N(0,1)")}
+
+
+def reference_protocol_ms(fn, warmup=200, samples=10, calls=20):
+    """The reference's timing protocol (benchmarks/common.py:184-220): warm-up calls, then
+    `samples` timings of `calls` back-to-back calls between CUDA events; returns the median."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(samples):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(calls):
+            fn()
+        stop.record()
+        stop.synchronize()
+        times.append(start.elapsed_time(stop) / calls)
+    return statistics.median(times)
+
+
+def dense_sweep_leg(device, lengths=(512, 1024, 2048, 4096, 8192, 16384, 32768), seeds=(0, 1, 2)):
+    """Full-call latency of every (length, V mode) of the dense sweep, median over seeds of the
+    per-seed median, next to the reference's own CUDA kernels on the same inputs (shorter
+    protocol for those: 20 warm-ups, 5 samples of 10 calls)."""
+    import risaattention_b200 as risa
+
+    try:
+        from oracle import ref_gpu
+        have_ref = ref_gpu.available()
+    except Exception:
+        have_ref = False
+    rows = []
+    for length in lengths:
+        for mode in ("absmax", "midpoint_affine"):
+            ours, theirs = [], []
+            for seed in seeds:
+                q, k, v = make_inputs(length, device, seed=seed)
+                # long sequences need fewer warm-ups to reach steady clocks than 200 x 7 ms
+                warm = 200 if length <= 8192 else 50
+                ours.append(reference_protocol_ms(
+                    lambda: risa.int8_attention(q, k, v, v_quantization=mode), warmup=warm))
+                if have_ref and seed == seeds[0]:
+                    cta_k = 128 if length > 1024 else 64
+                    out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+
+                    def ref_call():
+                        pk = ref_gpu.prequantize(q, k, v, cta_k=cta_k,
+                                                 midpoint_affine=mode == "midpoint_affine")
+                        ref_gpu.attention(pk, sm_scale=D ** -0.5, out=out)
+
+                    theirs.append(reference_protocol_ms(ref_call, warmup=20, samples=5, calls=10))
+            ms = statistics.median(ours)
+            row = {"seq_len": length, "v_quantization": mode, "ms": ms,
+                   "tops": dense_ops(B, HQ, length, length, D) / ms / 1e9}
+            if theirs:
+                row["reference_kernels_ms"] = theirs[0]
+            rows.append(row)
+    return {"protocol": "200 warm-up calls (50 above 8K), 10 samples x 20 calls, median per seed, "
+                        "median over seeds 0/1/2; reference kernels driven by ctypes, seed 0, 20 "
+                        "warm-ups, 5 x 10 calls",
+            "rows": rows}
+
+
+def video_dit_leg(device, steps):
+    """One GPU's share of the video-DiT configuration (5 of 40 heads, Hq = Hkv, L = 32760):
+    dense call, pattern construction and sparse reuse at theta = 0.99."""
+    import risaattention_b200 as risa
+    from risaattention_b200 import synthetic
+
+    heads, length = 5, 32760
+    q, k, v = synthetic.video_dit_inputs(heads, device, seq_len=length)
+    dense_ms = event_time_ms(lambda: risa.int8_attention(q, k, v), steps, 3)
+    _, pattern = risa.construct_sparse_int8_attention(q, k, v, theta=0.99)
+    construct_ms = event_time_ms(
+        lambda: risa.construct_sparse_int8_attention(q, k, v, theta=0.99), max(2, steps // 2), 2)
+    sparse_ms = event_time_ms(lambda: risa.sparse_int8_attention(q, k, v, pattern), steps, 3)
+    result = {"heads_per_gpu": heads, "seq_len": length, "dense_ms": dense_ms,
+              "dense_tops": dense_ops(1, heads, length, length, D) / dense_ms / 1e9,
+              "construct_ms": construct_ms, "coverage": pattern.coverage, "sparse_ms": sparse_ms}
+    try:
+        from oracle import ref_gpu
+        if ref_gpu.available():
+            out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+
+            def ref_call():
+                ref_gpu.attention(ref_gpu.prequantize(q, k, v, cta_k=128), sm_scale=D ** -0.5,
+                                  out=out)
+
+            result["reference_kernels_dense_ms"] = event_time_ms(ref_call, max(2, steps // 2), 2)
+    except Exception as error:  # comparison only
+        result["reference_error"] = str(error)[:200]
+    return result
+
+
+def edge_sweep_leg(device, steps):
+    """Edge / feature sweep timings at Hq32 Hkv8 Lq4096 Lk16384 for head_dim 64 and 256."""
+    import risaattention_b200 as risa
+    from risaattention_b200 import synthetic
+
+    rows = []
+    for dim in (64, 256):
+        for feature in ("dense_b2_lse", "causal", "bias_mask", "bool_mask_rows"):
+            batch = 2 if feature in ("dense_b2_lse", "bool_mask_rows") else 1
+            q, k, v = synthetic.dense_inputs(4096, device, seed=dim, q_heads=32, kv_heads=8,
+                                             head_dim=dim, batch=batch, kv_len=16384)
+            g = torch.Generator(device=device).manual_seed(dim + 1)
+            kwargs = {}
+            if feature == "causal":
+                kwargs["is_causal"] = True
+            elif feature == "bias_mask":
+                kwargs["attn_mask"] = torch.randn(batch, 32, 4096, 16384, device=device, generator=g)
+            elif feature == "bool_mask_rows":
+                mask = torch.ones(batch, 32, 4096, 16384, device=device, dtype=torch.bool)
+                mask[:, :, torch.randperm(4096, device=device, generator=g)[:409]] = False
+                kwargs["attn_mask"] = mask
+            else:
+                kwargs["return_lse"] = True
+            ms = event_time_ms(lambda: risa.int8_attention(q, k, v, **kwargs), max(3, steps // 2), 3)
+            ops = dense_ops(batch, 32, 4096, 16384, dim) * (0.5 if feature == "causal" else 1.0)
+            row = {"head_dim": dim, "feature": feature, "batch": batch, "ms": ms,
+                   "tops_executed": ops / ms / 1e9}
+            try:
+                from oracle import ref_gpu
+                if ref_gpu.available():
+                    cta_k = 64 if ("attn_mask" in kwargs or dim == 64) else 128
+                    mask = kwargs.get("attn_mask")
+                    out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
+
+                    def ref_call():
+                        pk = ref_gpu.prequantize(q, k, v, cta_k=cta_k)
+                        ref_gpu.attention(pk, sm_scale=dim ** -0.5, mask=mask, out=out,
+                                          is_causal=kwargs.get("is_causal", False),
+                                          want_lse=feature == "dense_b2_lse")
+
+                    row["reference_kernels_ms"] = event_time_ms(ref_call, 3, 2)
+            except Exception as error:  # comparison only
+                row["reference_error"] = str(error)[:120]
+            rows.append(row)
+            del kwargs
+    return rows
+
+
+def mma_issue_loop_tops(device):
+    """INT8 tensor-pipe ceiling of this GPU at its current clocks, from the probe library (built
+    beside the product library; see include/risa_b200_probe.h): back-to-back kind::i8 128x256x32
+    MMAs on every SM, no loads."""
+    import ctypes
+
+    path = ROOT / "risaattention_b200" / "librisa_b200_probe.so"
+    if not path.exists():
+        return None
+    lib = ctypes.CDLL(str(path))
+    fn = lib.risa_b200_mma_i8_issue_loop
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    ctas, ops = ctypes.c_int(0), ctypes.c_double(0.0)
+    stream = torch.cuda.current_stream(device).cuda_stream
+
+    def launch():
+        if fn(8192, ctypes.byref(ctas), ctypes.byref(ops), stream) != 0:
+            raise RuntimeError("INT8 issue-loop probe failed to launch")
+
+    ms = event_time_ms(launch, 10, 3)
+    return ops.value / ms / 1e9
+
+
+def cta_waves(q_heads_local, seq_len, sms=148):
+    ctas = q_heads_local * ((seq_len + 127) // 128)
+    return {"ctas": ctas, "sms": sms, "waves": ctas / sms,
+            "wave_efficiency": (ctas / sms) / -(-ctas // sms)}
 
 
 def run_ours(args):
@@ -390,21 +531,27 @@ def run_ours(args):
 
     import risaattention_b200 as risa
     from risaattention_b200 import _backend
-    from risaattention_b200.sharding import plan_head_shard
+    from risaattention_b200.sharding import gather_heads, merge_patterns, plan_head_shard
 
     L = args.seq_len
-    if args.scaling == "strong" and world > 1:
+    sharded = args.scaling == "strong" and world > 1
+    shard = None
+    if sharded:
         shard = plan_head_shard(HQ, HKV, rank, world)
-        q, k, v = make_inputs(L, device, seed=0)
-        q = q[:, shard.q_start:shard.q_stop].contiguous()
-        k = k[:, shard.kv_start:shard.kv_stop].contiguous()
-        v = v[:, shard.kv_start:shard.kv_stop].contiguous()
+        full_q, full_k, full_v = make_inputs(L, device, seed=0)
+        q = full_q[:, shard.q_start:shard.q_stop].contiguous()
+        k = full_k[:, shard.kv_start:shard.kv_stop].contiguous()
+        v = full_v[:, shard.kv_start:shard.kv_stop].contiguous()
+        if rank != 0:
+            del full_q, full_k, full_v
         total_ops = dense_ops(B, HQ, L, L, D)
-        parallelism = f"heads sharded {HQ // world} q-heads/GPU, KV co-located, no collective"
+        parallelism = (f"one call, {HQ // world} query heads per GPU, KV heads co-located"
+                       f"{' (replicated across GPU pairs)' if world > HKV else ''}, no collective")
     else:
         q, k, v = make_inputs(L, device, seed=rank)
         total_ops = dense_ops(B, HQ, L, L, D) * world
-        parallelism = f"dp{world}: one {L}-token call per GPU, no collective"
+        parallelism = f"{world} independent calls, one {L}-token call per GPU, no collective" \
+            if world > 1 else "single GPU"
     local_ops = dense_ops(q.shape[0], q.shape[1], L, L, D)
 
     def step():
@@ -419,20 +566,57 @@ def run_ours(args):
         ms = float(t)
 
     # ---- end to end: pinned host inputs, output read back, every step -------------------------
+    # (each rank moves only the heads it owns)
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     host_out = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step():
-        # public host-operand entry point: one stage per KV head, PCIe copies overlapped with compute
-        risa.int8_attention_from_host(hq, hk, hv, out=host_out, device=device)
+        # public host-operand entry point: one stage per KV head, PCIe copies overlapped with
+        # compute; the timed region ends with a device synchronisation, so the output is complete
+        risa.int8_attention_from_host(hq, hk, hv, out=host_out, device=device, wait=False)
 
-    e2e_ms = event_time_ms(e2e_step, max(2, args.steps // 2), 2, barrier)
+    e2e_ms = event_time_ms(e2e_step, max(2, args.steps // 2), 3, barrier)
     if world > 1:
         t = torch.tensor([e2e_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t)
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
     d2h = host_out.numel() * host_out.element_size()
+    if world > 1:
+        moved = torch.tensor([h2d, d2h], device=device, dtype=torch.int64)
+        dist.all_reduce(moved)
+        h2d, d2h = int(moved[0]), int(moved[1])
+
+    extra = {}
+    if sharded:
+        # output reassembly for callers that want one device to hold the result: NCCL all-gather
+        local_out = step()
+        gather_ms = event_time_ms(lambda: gather_heads(local_out), 5, 2, barrier)
+        t = torch.tensor([gather_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gathered = gather_heads(local_out)
+        # sparse supports: construct on the shard, merge in global row order
+        ls, kl = min(L, 8192), None
+        sq = q[:, :, :ls].contiguous()
+        sk, sv = k[:, :, :ls].contiguous(), v[:, :, :ls].contiguous()
+        _, local_pattern = risa.construct_sparse_int8_attention(sq, sk, sv, theta=0.9)
+        merged_offsets, merged_indices = merge_patterns(local_pattern.row_offsets,
+                                                        local_pattern.block_indices, B)
+        check = None
+        if rank == 0:
+            want = risa.int8_attention(full_q, full_k, full_v)
+            _, full_pattern = risa.construct_sparse_int8_attention(
+                full_q[:, :, :ls].contiguous(), full_k[:, :, :ls].contiguous(),
+                full_v[:, :, :ls].contiguous(), theta=0.9)
+            check = {"gathered_output_bit_identical_to_single_gpu": bool(torch.equal(gathered, want)),
+                     "merged_pattern_bit_identical_to_single_gpu":
+                         bool(torch.equal(merged_offsets, full_pattern.row_offsets)
+                              and torch.equal(merged_indices, full_pattern.block_indices)),
+                     "pattern_seq_len": ls}
+        extra = {"gather_ms": float(t),
+                 "gather_bytes_per_rank": local_out.numel() * local_out.element_size(),
+                 "cta_waves_per_rank": cta_waves(q.shape[1], L),
+                 "sharding_check": check}
 
     if rank != 0:
         if world > 1:
@@ -448,17 +632,13 @@ def run_ours(args):
     prep_ms = event_time_ms(lambda: risa.prequantize_int8_attention(q, k, v), args.steps,
                             args.warmup)
     int8_peak = 2.0 * peaks["bf16_tflops"]  # no INT8 entry in MEASURED_PEAKS: 2 x measured bf16
-    # measured INT8 issue-loop throughput of this GPU (kind::i8 128x256x32 back to back, all SMs)
-    stream_ptr = torch.cuda.current_stream(device).cuda_stream
-    _, loop_ops = _backend._C.mma_i8_issue_loop(8192, stream_ptr)
-    loop_ms = event_time_ms(lambda: _backend._C.mma_i8_issue_loop(8192, stream_ptr), 10, 3)
-    mma_loop_tops = loop_ops / loop_ms / 1e9
+    mma_loop_tops = mma_issue_loop_tops(device)
     achieved = local_ops / att_ms / 1e9
     prep_bytes = sum(t.numel() * 3 for t in (q, k, v))  # 2 B in + 1 B out per element
     line = {
         "metric": METRIC, "value": total_ops / ms / 1e9, "unit": "TOPS", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": args.scaling if world > 1 else "weak", "vs_baseline": None, "dtype": "s8",
+        "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "s8",
         "data": "synthetic",
         "config": {"workload": f"dense int8_attention B{B} Hq{HQ} Hkv{HKV} D{D} L{L} bf16, "
                                "full call incl. Q/K/V quantisation",
@@ -467,32 +647,46 @@ def run_ours(args):
         "clocks": clocks.result,
         "e2e": {"value": total_ops / e2e_ms / 1e9, "unit": "TOPS", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": KERNELS_PER_DENSE_CALL * args.steps * world,
         "roofline": {"bound": "tensor", "kernel": "attention_tc_kernel", "achieved": achieved,
                      "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
                      "kernel_ms": att_ms,
-                     "mma_i8_issue_loop_tops": mma_loop_tops,
-                     "frac_of_issue_loop": achieved / mma_loop_tops,
                      "peak_source": f"2 x {peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s "
                                     "(no INT8 figure in MEASURED_PEAKS.json)",
+                     "peak_int8_issue_loop": mma_loop_tops,
+                     "frac_of_issue_loop": None if not mma_loop_tops else achieved / mma_loop_tops,
+                     "peak_int8_issue_loop_source": "measured in this run by this repository's own "
+                                                    "probe kernel: back-to-back tcgen05.mma kind::i8 "
+                                                    "128x256x32 on every SM, no loads",
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((L, q.shape[1])),
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
-                                       "profiles/attention_tc_kernel_dense32k_dram_traffic.md"},
+                     "traffic_source": "constant: dram__bytes_read.sum + dram__bytes_write.sum of one "
+                                       "launch of this workload from an ncu capture, not measured in "
+                                       "this run"},
         "prep_roofline": {"bound": "hbm", "achieved": prep_bytes / prep_ms / 1e6,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s",
                           "frac": prep_bytes / prep_ms / 1e6 / peaks["hbm_gbs"],
-                          "kernel_ms": prep_ms, "note": "5 kernels incl. host launch gaps"},
+                          "kernel_ms": prep_ms,
+                          "note": f"{KERNELS_PER_DENSE_CALL - 1} kernels incl. host launch gaps"},
     }
+    line.update(extra)
     if world == 1:
         line["accuracy"] = accuracy_leg(q, k, v, step(), L)
         line["reference_kernels_on_this_gpu"] = reference_kernels_leg(q, k, v, L, args.steps)
-        if not args.no_sparse:
-            try:
-                line["sparse_reuse"] = sparse_leg(L, device, max(3, args.steps // 2))
-                line["sparse_reuse_block_centroids"] = sparse_leg(L, device, max(3, args.steps // 2),
-                                                                  "block_centroids")
-            except Exception as error:
-                line["sparse_reuse"] = {"error": str(error)[:200]}
+        line["cta_waves"] = cta_waves(q.shape[1], L)
+        del packed
+        if not args.no_extras:
+            half = max(3, args.steps // 2)
+            for key, leg in (("sparse_reuse", lambda: sparse_leg(L, device, half)),
+                             ("sparse_reuse_block_centroids",
+                              lambda: sparse_leg(L, device, half, "block_centroids")),
+                             ("dense_sweep", lambda: dense_sweep_leg(device)),
+                             ("video_dit", lambda: video_dit_leg(device, half)),
+                             ("edge_sweep", lambda: edge_sweep_leg(device, half))):
+                try:
+                    line[key] = leg()
+                except Exception as error:  # an extra must never cost the headline line
+                    line[key] = {"error": str(error)[:200]}
+                torch.cuda.empty_cache()
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(L)
     print(json.dumps(line))
@@ -508,9 +702,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--seq-len", type=int, default=32768)
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="N > 1: split one call's heads over the ranks (strong, default) or run "
+                         "one full call per rank (weak)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-sparse", action="store_true", help="skip the sparse-reuse leg")
+    ap.add_argument("--no-extras", "--no-sparse", dest="no_extras", action="store_true",
+                    help="skip the sparse-reuse, dense-sweep, video-DiT and edge-sweep legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -116,24 +116,26 @@ int risa_b200_dense_attention(const void* q, const void* k, const void* v, void*
                               int out_dtype_code, int64_t o_stride_b, int64_t o_stride_n,
                               int64_t o_stride_h, int is_causal, void* stream);
 
-/* Measurement aid, no counterpart in the reference: launches one CTA per SM that issues
- * `mma_per_cta` back-to-back tcgen05.mma kind::i8 128x256x32 instructions on shared-memory
- * operands.  Timed by the caller (events on `stream`), ops_per_launch / time is the INT8 tensor
- * issue-loop throughput of this GPU at its current clocks: the measured ceiling the attention
- * kernel's roofline fraction can be read against.  Writes the CTA count and the operation count
- * (2*M*N*K per MMA) of one launch. */
-int risa_b200_mma_i8_issue_loop(int mma_per_cta, int* ctas, double* ops_per_launch, void* stream);
-
-/* Selects which attention kernel family the library may use: 0 = automatic (tensor-core kernel
- * where it applies), 1 = force the row-per-thread integer kernel (used by parity tests to compare
- * the two).  Process-wide; returns the previous value. */
+/* Selects which attention kernel family calls made BY THE CALLING THREAD may use: 0 = automatic
+ * (tensor-core kernel where it applies), 1 = force the row-per-thread integer kernel, whose FP32
+ * operation order equals the reference's (the on-device cross-check of the tensor-core kernel).
+ * Thread-local: other threads of the process are not affected.  Returns the previous value. */
 int risa_b200_set_attention_path(int path);
 
 /* Reads (and clears) the device status word of the tensor-core attention kernel.  Every wait inside
- * that kernel is bounded; if one expires the kernel records where, drains and exits, and this call
- * returns RISA_B200_DEVICE with the site in risa_b200_last_error().  Synchronises the device.  No
- * counterpart in the reference, whose kernels have no waits that can expire. */
+ * that kernel is bounded; if one expires the CTA records where, writes NaN into the output rows
+ * (and LSE entries) it owns, drains and exits, and this call returns RISA_B200_DEVICE with the site
+ * in risa_b200_last_error().  The record is per process and only reports: later launches are not
+ * affected by an earlier expiry.  Synchronises the device.  No counterpart in the reference, whose
+ * kernels have no waits that can expire. */
 int risa_b200_device_status(void);
+
+/* Health check of the bounded-wait machinery on this GPU and driver: one warp waits, for at most
+ * limit_ns nanoseconds (0 < limit_ns <= 1e9), on a barrier that nothing ever completes, then
+ * returns.  Afterwards risa_b200_device_status() reports RISA_B200_DEVICE with site 900 and the
+ * context stays usable.  Nothing faults, traps or spins past the limit.  No counterpart in the
+ * reference. */
+int risa_b200_bounded_wait_self_test(uint64_t limit_ns, void* stream);
 
 /* Retained-mass prefix selection over descending-sorted block masses and CSR packing.  Replaces
  * launch_select_retained_mass + retained_mass_selector_workspace_size (csrc/launchers.h:61-67;

@@ -2,9 +2,12 @@
 
 The reference binds its kernels through a nanobind module ``_C`` that receives DLPack capsules
 (src/risa_attention/_backend.py:6-54, csrc/bindings.cpp:642-673).  Here ``_C`` is a thin object
-over ``librisa_b200.so`` (see include/risa_b200.h): tensors are passed as device pointers plus
-element strides, the stream as the raw ``cudaStream_t``.  There is no CPU fallback: when the
-library or a capable GPU is missing every entry point raises ``RuntimeError``.
+over ``librisa_b200.so`` (see include/risa_b200.h) with the same entry-point names, argument
+order, keyword names and defaults, so the reference's own Python runtime can call it unchanged:
+tensor arguments may be ``torch.Tensor`` objects or DLPack capsules, scratch pointers
+(``anchor_indices_ptr``, ``permutation_ptr``) may be tensors or raw integer addresses, the stream is
+the raw ``cudaStream_t``.  There is no CPU fallback: when the library or a capable GPU is missing
+every entry point raises ``RuntimeError``.
 """
 from __future__ import annotations
 
@@ -13,7 +16,7 @@ from pathlib import Path
 
 import torch
 
-MINIMUM_COMPUTE_CAPABILITY = (10, 0)
+REQUIRED_COMPUTE_CAPABILITY_MAJOR = 10  # the library holds sm_100a code only
 _LIB_PATH = Path(__file__).resolve().parent / "librisa_b200.so"
 _EXTENSION_ERROR: Exception | None = None
 
@@ -39,7 +42,7 @@ _SIGNATURES = {
     "risa_b200_dense_attention": (
         c_i32, [c_vp] * 5 + [c_sz] + [c_i32] * 7 + [c_i64] * 9 + [c_i32, c_i32, c_f32, c_i32] +
         [c_i64] * 3 + [c_i32, c_vp]),
-    "risa_b200_mma_i8_issue_loop": (c_i32, [c_i32, c_vp, c_vp, c_vp]),
+    "risa_b200_bounded_wait_self_test": (c_i32, [ctypes.c_uint64, c_vp]),
     "risa_b200_set_attention_path": (c_i32, [c_i32]),
     "risa_b200_device_status": (c_i32, []),
     "risa_b200_selector_workspace_size": (c_sz, [c_i32]),
@@ -53,13 +56,26 @@ _SIGNATURES = {
 DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.bool: 3}
 
 
-def _ptr(tensor):
-    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+def _t(x):
+    """Tensor view of a native-call argument: tensors pass through, DLPack capsules (what the
+    reference's runtime hands to its native module) are imported without a copy."""
+    if x is None or isinstance(x, torch.Tensor):
+        return x
+    return torch.utils.dlpack.from_dlpack(x)
 
 
-def _stride(tensor, dim):
-    # An extent of one never contributes to an address; report 0 so alignment checks ignore it.
-    return tensor.stride(dim)
+def _ptr(x):
+    """Device address of a tensor, or a raw integer address (0 / None = null)."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x) if x else None
+    return ctypes.c_void_p(x.data_ptr())
+
+
+def _default_cta_k(head_dim, key_length, has_mask):
+    # csrc/bindings.cpp:549-551
+    return 128 if (not has_mask and head_dim >= 128 and key_length > 1024) else 64
 
 
 class _Native:
@@ -80,18 +96,55 @@ class _Native:
     # -- risa_sdpa_quantize (csrc/bindings.cpp:195-272) ---------------------------------------
     def risa_sdpa_quantize(self, q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale,
                            v_center, cta_k, input_dtype_code, use_midpoint_affine, stream_ptr,
-                           anchors, q_perm=None, k_perm=None, v_perm=None, workspace=None):
+                           anchor_indices_ptr, permutation_ptr=0, *, q_permutation_ptr=0,
+                           workspace=None):
+        """``permutation_ptr``: int32 [B,Hkv,Lk] gather table applied to K and V (the reference's
+        fused gather); ``q_permutation_ptr`` (extension) the same for Q.  ``workspace``
+        (extension): scratch for the V quantiser; allocated on the call's stream when omitted."""
+        q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale, v_center = map(
+            _t, (q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale, v_center))
         b, hq, lq, d = q.shape
         hkv, lk = k.shape[1], k.shape[2]
+        if workspace is None:
+            with torch.cuda.device(q.device), torch.cuda.stream(
+                    torch.cuda.ExternalStream(stream_ptr, device=q.device) if stream_ptr
+                    else torch.cuda.default_stream(q.device)):
+                workspace = torch.empty(self.quantize_v_workspace_size(b, hkv, lk, d),
+                                        dtype=torch.uint8, device=q.device)
         self._check(self.lib.risa_b200_quantize_qk(
             _ptr(q), _ptr(q_int8), _ptr(q_scale), _ptr(k), _ptr(k_int8), _ptr(k_scale), b, hq, lq,
             hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
-            k.stride(2), input_dtype_code, _ptr(anchors), _ptr(q_perm), _ptr(k_perm), stream_ptr))
+            k.stride(2), input_dtype_code, _ptr(anchor_indices_ptr), _ptr(q_permutation_ptr),
+            _ptr(permutation_ptr), stream_ptr))
         self._check(self.lib.risa_b200_quantize_v(
             _ptr(v), _ptr(v_int8), _ptr(v_scale), _ptr(v_center), b, hkv, lk, d, v_int8.shape[1],
             v.stride(0), v.stride(1), v.stride(2), input_dtype_code, int(use_midpoint_affine),
-            _ptr(v_perm), _ptr(workspace), workspace.numel() * workspace.element_size(),
+            _ptr(permutation_ptr), _ptr(workspace), workspace.numel() * workspace.element_size(),
             stream_ptr))
+
+    # -- risa_sdpa (csrc/bindings.cpp:497-616) ----------------------------------------------------
+    def risa_sdpa(self, q, k, v, o, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale, v_center,
+                  sm_scale, input_dtype_code, output_dtype_code, use_midpoint_affine, stream_ptr,
+                  anchor_indices_ptr, attn_mask=None, cta_k=0, is_causal=False,
+                  key_mask_tiles=None):
+        """Quantise Q, K and V into the caller's packed buffers and attend, on one stream."""
+        q, k, v, o = map(_t, (q, k, v, o))
+        if q.ndim != 4 or k.ndim != 4 or v.ndim != 4 or o.ndim != 4:
+            raise RuntimeError("risa_sdpa: q, k, v, o must be 4D [batch_size,num_heads,L,head_dim]")
+        if not 0 <= input_dtype_code <= 2:
+            raise RuntimeError(
+                "risa_sdpa: input_dtype_code must be 0 (fp32), 1 (fp16), or 2 (bf16)")
+        if not anchor_indices_ptr and not isinstance(anchor_indices_ptr, torch.Tensor):
+            raise RuntimeError("risa_sdpa: anchor_indices scratch is required")
+        if cta_k == 0:
+            cta_k = _default_cta_k(q.shape[3], k.shape[2], attn_mask is not None)
+        self.risa_sdpa_quantize(q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale,
+                                v_center, cta_k, input_dtype_code, use_midpoint_affine,
+                                stream_ptr, anchor_indices_ptr)
+        self.risa_sdpa_prequantized(q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale,
+                                    v_center, cta_k, sm_scale, output_dtype_code, stream_ptr,
+                                    attn_mask=attn_mask, is_causal=is_causal,
+                                    key_mask_tiles=key_mask_tiles)
 
     # -- fused unmasked dense call (no counterpart in the reference's native module) ------------
     def dense_scratch_size(self, batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k) -> int:
@@ -110,13 +163,6 @@ class _Native:
             input_dtype_code, int(use_midpoint_affine), sm_scale, output_dtype_code, o.stride(0),
             o.stride(2), o.stride(1), int(is_causal), stream_ptr))
 
-    def mma_i8_issue_loop(self, mma_per_cta, stream_ptr) -> tuple[int, float]:
-        """Launches the INT8 tensor-pipe issue loop once; returns (CTAs, operations in the launch)."""
-        ctas, ops = ctypes.c_int(0), ctypes.c_double(0.0)
-        self._check(self.lib.risa_b200_mma_i8_issue_loop(mma_per_cta, ctypes.byref(ctas),
-                                                         ctypes.byref(ops), stream_ptr))
-        return ctas.value, ops.value
-
     def quantize_v_workspace_size(self, batch, kv_heads, k_len, head_dim) -> int:
         return int(self.lib.risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim))
 
@@ -125,6 +171,10 @@ class _Native:
                                v_center, cta_k, sm_scale, output_dtype_code, stream_ptr,
                                attn_mask=None, sparse_row_offsets=None, sparse_block_indices=None,
                                block_mass=None, is_causal=False, lse=None, key_mask_tiles=None):
+        (q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale, v_center, attn_mask,
+         sparse_row_offsets, sparse_block_indices, block_mass, lse, key_mask_tiles) = map(
+            _t, (q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale, v_center, attn_mask,
+                 sparse_row_offsets, sparse_block_indices, block_mass, lse, key_mask_tiles))
         b, hq, lq, d = q_int8.shape
         hkv, lk = k_int8.shape[1], k_int8.shape[2]
         padded = (lk + cta_k - 1) // cta_k * cta_k
@@ -169,6 +219,10 @@ class _Native:
     def select_retained_mass_csr(self, sorted_mass, descending_indices, counts, support,
                                  row_totals, row_offsets, block_indices, summary, scan_workspace,
                                  theta, stream_ptr):
+        (sorted_mass, descending_indices, counts, support, row_totals, row_offsets, block_indices,
+         summary, scan_workspace) = map(
+            _t, (sorted_mass, descending_indices, counts, support, row_totals, row_offsets,
+                 block_indices, summary, scan_workspace))
         rows, blocks = sorted_mass.shape
         self._check(self.lib.risa_b200_select_retained_mass(
             _ptr(sorted_mass), _ptr(descending_indices), _ptr(counts), _ptr(support),
@@ -176,6 +230,7 @@ class _Native:
             _ptr(scan_workspace), scan_workspace.numel(), rows, blocks, float(theta), stream_ptr))
 
     def prepare_key_mask_tiles(self, mask, tiles, tile_size, stream_ptr):
+        mask, tiles = _t(mask), _t(tiles)
         if mask.ndim != 4 or mask.stride(2) != 0 or tile_size not in (64, 128):
             raise RuntimeError("prepare_key_mask_tiles requires an expanded broadcast key mask")
         b, h, _, lk = mask.shape
@@ -184,6 +239,7 @@ class _Native:
             mask.stride(3), DTYPE_CODES[mask.dtype], stream_ptr))
 
     def risa_lse_shift(self, q, k, anchors, out, scale, stream_ptr):
+        q, k, anchors, out = map(_t, (q, k, anchors, out))
         b, hq, lq, d = q.shape
         self._check(self.lib.risa_b200_correct_lse(
             _ptr(q), _ptr(k), _ptr(anchors), _ptr(out), b, hq, k.shape[1], lq, d, q.stride(0),
@@ -195,7 +251,11 @@ class _Native:
         self._check(self.lib.risa_b200_device_status())
 
     def set_attention_path(self, path: int) -> int:
+        """Kernel family for calls made by the calling thread (0 automatic, 1 row-per-thread)."""
         return int(self.lib.risa_b200_set_attention_path(path))
+
+    def bounded_wait_self_test(self, limit_ns: int, stream_ptr) -> None:
+        self._check(self.lib.risa_b200_bounded_wait_self_test(limit_ns, stream_ptr))
 
 
 try:
@@ -211,7 +271,8 @@ _AVAILABLE: dict = {}
 
 
 def is_available(device: torch.device | int | str | None = None) -> bool:
-    """True when the library is loaded and ``device`` is a Blackwell datacenter GPU (sm_100)."""
+    """True when the library is loaded and ``device`` is a Blackwell datacenter GPU (compute
+    capability 10.x; the library holds sm_100a code, which no other family can load)."""
     if _C is None:
         return False
     if isinstance(device, torch.device) and device.type == "cuda" and device.index is not None:
@@ -231,7 +292,7 @@ def _probe(device) -> bool:
             resolved = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
             if resolved.type != "cuda":
                 return False
-        return torch.cuda.get_device_capability(resolved) >= MINIMUM_COMPUTE_CAPABILITY
+        return torch.cuda.get_device_capability(resolved)[0] == REQUIRED_COMPUTE_CAPABILITY_MAJOR
     except (AssertionError, RuntimeError, ValueError):
         return False
 

@@ -53,12 +53,13 @@ def resolve_scale(scale, original_head_dim):
     return value
 
 
-def quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine, permutations=(None,) * 3):
+def quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine, kv_table=None):
+    """``kv_table``: optional int32 [B,Hkv,Lk] gather table the K and V quantisers read through."""
     _backend._C.risa_sdpa_quantize(
         q, k, v, buffers.q_codes, buffers.q_scales, buffers.k_codes, buffers.k_scales,
         buffers.v_codes, buffers.v_scales, buffers.v_centers, key_block_size,
         DTYPE_CODES[q.dtype], use_midpoint_affine,
-        torch.cuda.current_stream(q.device).cuda_stream, buffers.anchors, *permutations,
+        torch.cuda.current_stream(q.device).cuda_stream, buffers.anchors, kv_table,
         workspace=buffers.workspace)
 
 
@@ -70,13 +71,13 @@ def prequantize_int8_attention(q, k, v, *, scale=None, attn_mask=None, v_quantiz
     The result keeps no floating-point input, so callers may free Q/K/V before
     :func:`int8_attention_from_prequantized`.  No host synchronisation is introduced."""
     attn_mask = validate_inputs(q, k, v, attn_mask)
-    permutations = (None, None, None)
+    kv_table = None
     if kv_permutation is not None:
         from .permutation import prepare_inputs
 
-        q, k, v, permutations = prepare_inputs(q, k, v, permutation=kv_permutation, mask=attn_mask,
-                                               causal=is_causal, return_lse=return_lse,
-                                               fuse=fuse_gather)
+        q, k, v, kv_table = prepare_inputs(q, k, v, permutation=kv_permutation, mask=attn_mask,
+                                           causal=is_causal, return_lse=return_lse,
+                                           fuse=fuse_gather)
     use_midpoint_affine = uses_centered_values(v_quantization)
     input_dtype = q.dtype
     q, k, v, original_head_dim, _ = pad_head_dim(q, k, v)
@@ -84,7 +85,7 @@ def prequantize_int8_attention(q, k, v, *, scale=None, attn_mask=None, v_quantiz
     key_block_size = select_key_block_size(
         q.shape[-1], k.shape[2], has_mask=attn_mask is not None and attn_mask.stride(-2) != 0)
     buffers = PackedBuffers(q, k, key_block_size)
-    quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine, permutations)
+    quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine, kv_table)
     lse_shift = None
     if return_lse:
         # K was translated by its anchor row before quantisation; this restores the row-wise logit

@@ -15,7 +15,10 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = CSRC / "_obj"
 LIB = PKG / "librisa_b200.so"
-UNITS = ["prep_qk", "prep_v", "misc", "attention_api", "attention_rows", "attention_tc", "mma_peak"]
+UNITS = ["prep_qk", "prep_v", "misc", "attention_api", "attention_rows", "attention_tc"]
+# measurement probe (INT8 issue-loop ceiling used by bench.py), its own library
+PROBE_LIB = PKG / "librisa_b200_probe.so"
+PROBE_UNITS = ["mma_peak"]
 # --use_fast_math is part of the numeric contract shared with the reference's kernels
 # (approximate division / reciprocal, flush-to-zero, contracted multiply-adds).
 NVCC_FLAGS = [
@@ -44,16 +47,17 @@ def _compile(unit: str, force: bool, verbose: bool) -> str | None:
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
+    units = UNITS + PROBE_UNITS
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        logs = list(pool.map(lambda u: _compile(u, force, verbose), UNITS))
-    rebuilt = any(log is not None for log in logs)
+        logs = dict(zip(units, pool.map(lambda u: _compile(u, force, verbose), units)))
     if verbose:
-        for unit, log in zip(UNITS, logs):
+        for unit, log in logs.items():
             if log:
                 (OBJ / f"{unit}.ptxas.log").write_text(log)
-    if rebuilt or not LIB.exists():
-        objs = [str(OBJ / f"{u}.o") for u in UNITS]
-        subprocess.run(["nvcc", "-shared", "-o", str(LIB), *objs, "-lcudart"], check=True)
+    for lib, members in ((LIB, UNITS), (PROBE_LIB, PROBE_UNITS)):
+        if any(logs[u] is not None for u in members) or not lib.exists():
+            objs = [str(OBJ / f"{u}.o") for u in members]
+            subprocess.run(["nvcc", "-shared", "-o", str(lib), *objs, "-lcudart"], check=True)
     return LIB
 
 

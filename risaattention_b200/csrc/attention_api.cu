@@ -1,12 +1,13 @@
 // C-ABI entry of the fused INT8 attention call: validation, kernel-family selection and the
 // block-mass reduction that follows a capture pass.
 #include "attention_common.cuh"
-#include <atomic>
 
 namespace risa_b200 {
 namespace {
 
-std::atomic<int> g_attention_path{0};
+// Kernel family the calling thread asked for (0 = automatic); per thread, so that a parity check
+// forcing the row-per-thread kernel cannot change what other threads of the process run.
+thread_local int g_attention_path = 0;
 
 // Block mass of (query block, key tile): sum over the block's queries of
 // numerator * 2^(tile_max - m_final) / d_final.  One CTA per (query block, head, batch), thread =
@@ -60,7 +61,9 @@ __global__ __launch_bounds__(128) void block_mass_kernel(const AttentionArgs a, 
 using namespace risa_b200;
 
 extern "C" int risa_b200_set_attention_path(int path) {
-  return g_attention_path.exchange(path == 1 ? 1 : 0);
+  const int previous = g_attention_path;
+  g_attention_path = path == 1 ? 1 : 0;
+  return previous;
 }
 
 extern "C" int risa_b200_attention(
@@ -132,7 +135,7 @@ extern "C" int risa_b200_attention(
                          : nullptr;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   int status;
-  if (g_attention_path.load() == 0 && attention_tc_supported(a))
+  if (g_attention_path == 0 && attention_tc_supported(a))
     status = attention_tc(a, stream);
   else
     status = attention_rows(a, stream);

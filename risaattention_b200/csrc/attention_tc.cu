@@ -22,8 +22,9 @@
 // Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh.  The integer
 // products are exact, so probabilities, capture statistics and block masses are bit-identical to
 // the row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
-// Every mbarrier wait is bounded (tc_ptx.cuh): a protocol error sets a device status word and the
-// CTA drains and exits instead of spinning.
+// Every mbarrier wait is bounded (tc_ptx.cuh): when one expires the CTA's waiters leave, the producer
+// waits for its loads in flight, the rows of the CTA are written as NaN and a device status word
+// records the site; the CTA then exits instead of spinning.
 #include "attention_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -53,8 +54,7 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
 // measured fastest (one copy leaves the loads too little to hide behind, four copies fall out of the
 // instruction cache next to the other roles' code).
 constexpr int kExpUnroll = 2;
-
-__device__ unsigned int g_tc_status;  // first failing wait site since the last status query
+constexpr unsigned int kSelfTestSite = 900;  // site number reported by the bounded-wait self test
 
 // Per head_dim: what one CTA holds and how deep its rings are.  head_dim 256 is run as two CTAs per
 // (query block, head), each contracting Q.K^T over all 256 channels (two 128-byte column panels of
@@ -80,6 +80,7 @@ struct SmemLayout {
   static constexpr int bars = sums + 4 * 128 * 64;         // 8-byte mbarriers
   static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
+  static constexpr int gave_up = tmem_slot + 8;            // site of the first expired wait, or 0
   static constexpr int total = tmem_slot + 16;
   static constexpr size_t bytes = total + 1024;            // room to align the base to 1024
 };
@@ -291,10 +292,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   const int n_k = (a.k_len + CTA_K - 1) / CTA_K, n_q = gridDim.x;
   const int64_t bh = int64_t(batch) * a.q_heads + head;
   const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
-  unsigned int* error = &g_tc_status;
+  const uint32_t gave_up = sbase + L::gave_up;  // set by the first wait of this CTA that expires
   Bars bar{sbase + L::bars};
 
   if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile uint32_t*>(smem + L::gave_up) = 0u;
     mbar_init(bar(Bars::QFULL), 1);
     for (int s = 0; s < kKStages; ++s) {
       mbar_init(bar(Bars::KFULL + s), 1);
@@ -346,7 +348,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       for (int step = 0; step < seq.n_iter + 2 && ok; ++step) {
         if (step < seq.n_iter) {
           const int s = step % L::kKSt, r = step / L::kKSt;
-          ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, error, 101);
+          ok = mbar_wait<true>(bar(Bars::KEMPTY + s), (r & 1) ^ 1, gave_up, 101);
           if (!ok) break;
           mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * D);
 #pragma unroll
@@ -358,7 +360,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         const int it = step - 2;
         if (it >= 0) {
           const int s = it % L::kVSt, r = it / L::kVSt;
-          ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, error, 102);
+          ok = mbar_wait<true>(bar(Bars::VEMPTY + s), (r & 1) ^ 1, gave_up, 102);
           if (!ok) break;
           // V always arrives as the 128-key slab that holds the tile (64-key tiles use half of it):
           // rows stay 128 bytes wide, so one swizzle mode and one descriptor form serve both widths
@@ -370,11 +372,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
       if (!ok) {
         // drain: every issued load must land before shared memory can be released
-        mbar_wait(bar(Bars::QFULL), 0, error, 104);
+        mbar_drain(bar(Bars::QFULL), 0);
         for (int it = max(0, k_issued - L::kKSt); it < k_issued; ++it)
-          mbar_wait(bar(Bars::KFULL + it % L::kKSt), (it / L::kKSt) & 1, error, 105);
+          mbar_drain(bar(Bars::KFULL + it % L::kKSt), (it / L::kKSt) & 1);
         for (int it = max(0, v_issued - L::kVSt); it < v_issued; ++it)
-          mbar_wait(bar(Bars::VFULL + it % L::kVSt), (it / L::kVSt) & 1, error, 106);
+          mbar_drain(bar(Bars::VFULL + it % L::kVSt), (it / L::kVSt) & 1);
       }
     } else if (warp == 17 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: S = Q.K^T
@@ -382,11 +384,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
       // round-trips on each.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, CTA_K);
-      bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, error, 201);
+      bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, gave_up, 201);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
         const int b = it % 3, u = it / 3, s = it % L::kKSt, r = it / L::kKSt;
         ok = mbar_wait2<true>(bar(Bars::KFULL + s), r & 1, bar(Bars::SFREE + b), (u & 1) ^ 1,
-                              error, 202);
+                              gave_up, 202);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -409,7 +411,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         const int s = it % L::kVSt, r = it / L::kVSt;
         const int slot = it % L::kSlots, j = it / L::kSlots;
         ok = mbar_wait3<true>(bar(Bars::PFULL + slot), j & 1, bar(Bars::VFULL + s), r & 1,
-                              bar(Bars::OFREE), (it & 1) ^ 1, error, 204);
+                              bar(Bars::OFREE), (it & 1) ^ 1, gave_up, 204);
         if (!ok) break;
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + L::p + slot * kTile);
@@ -466,7 +468,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       uint16_t* my_sums = sums + (slot * 128 + row_in) * 32;
       unsigned char* p_row = smem + L::p + slot * kTile + row_in * 128;
       ok = mbar_wait3(bar(Bars::PFREE + slot), ((it / L::kSlots) & 1) ^ 1, bar(Bars::STATFREE + slot),
-                      ((it / L::kSlots) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, error, 301);
+                      ((it / L::kSlots) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, gave_up, 301);
       if (!ok) break;
       tc_fence_after();
       // causal: tiles that end at or before the CTA's first query are fully visible
@@ -514,7 +516,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       float cur_o_scale = 1.0f, cur_w = 0.0f;
       if (it >= 1) {
         const int j = it - 1;
-        ok = mbar_wait(bar(Bars::OFULL), j & 1, error, 402);
+        ok = mbar_wait(bar(Bars::OFULL), j & 1, gave_up, 402);
         if (!ok) break;
         tc_fence_after();
         const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
@@ -547,7 +549,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (it < seq.n_iter) {
         const bool last_iter = it == seq.n_iter - 1;
         const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
-        ok = mbar_wait(bar(Bars::PFULL + (it % L::kSlots)), (it / L::kSlots) & 1, error, 401);
+        ok = mbar_wait(bar(Bars::PFULL + (it % L::kSlots)), (it / L::kSlots) & 1, gave_up, 401);
         if (!ok) break;
         const int slot = it % L::kSlots;
         const float2 stat = stats[slot * 128 + row_in];
@@ -629,6 +631,16 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       if (a.lse && half == 0) a.lse[grow] = row_lse(denom, st.m);
+    } else if (row_ok) {
+      // a wait of this CTA expired: mark the rows it owns, so that a failed launch cannot be taken
+      // for a result (NaN in both 16-bit output formats, NaN LSE)
+      char* o_row = static_cast<char*>(a.o) + 2 * kOut * half +
+                    2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
+#pragma unroll
+      for (int ch = 0; ch < kOut; ch += 8)
+        *reinterpret_cast<uint4*>(o_row + 2 * ch) =
+            make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+      if (a.lse && half == 0) a.lse[grow] = __int_as_float(0x7fffffff);
     }
   }
 
@@ -638,6 +650,20 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+}
+
+// One warp waits on a barrier that nobody arrives at, with a caller-chosen limit: the bounded-wait
+// machinery (expiry, site record, orderly return) exercised without any faulty launch.
+__global__ void bounded_wait_self_test_kernel(uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t barrier;
+  __shared__ uint32_t gave_up_word;
+  if (threadIdx.x == 0) {
+    gave_up_word = 0u;
+    mbar_init(smem_u32(&barrier), 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  mbar_wait(smem_u32(&barrier), 0, smem_u32(&gave_up_word), kSelfTestSite, limit_ns);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -688,6 +714,19 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
     if (e != cudaSuccess)
       return fail(RISA_B200_CUDA, "attention: cannot reserve %zu bytes of shared memory: %s",
                   SmemLayout<D>::bytes, cudaGetErrorString(e));
+    // setmaxnreg hands out the registers the CTA is launched with; if the compiler ever gave this
+    // kernel fewer than the roles ask for, the increase could never be granted (it blocks, beyond
+    // the reach of the bounded waits), so such a build must not run
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess)
+      return fail(RISA_B200_CUDA, "attention: cudaFuncGetAttributes: %s", cudaGetErrorString(e));
+    if (attr.numRegs * kThreads <
+        128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue))
+      return fail(RISA_B200_CUDA,
+                  "attention: kernel was compiled with %d registers per thread, the warp roles "
+                  "need a pool of %d", attr.numRegs,
+                  128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue) / kThreads);
     configured = device;
   }
   const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D>::kHalves, a.batch);
@@ -746,11 +785,11 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
 
 extern "C" int risa_b200_device_status(void) {
   unsigned int status = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&status, risa_b200::g_tc_status, sizeof(status)) != cudaSuccess)
+  if (cudaMemcpyFromSymbol(&status, risa_b200::tc::g_wait_status, sizeof(status)) != cudaSuccess)
     return risa_b200::fail(RISA_B200_CUDA, "device status: %s",
                            cudaGetErrorString(cudaGetLastError()));
   if (status != 0) {
-    cudaMemcpyToSymbol(risa_b200::g_tc_status, &zero, sizeof(zero));
+    cudaMemcpyToSymbol(risa_b200::tc::g_wait_status, &zero, sizeof(zero));
     return risa_b200::fail(RISA_B200_DEVICE,
                            "attention kernel gave up waiting at site %u (bounded wait expired)",
                            status);
@@ -758,4 +797,11 @@ extern "C" int risa_b200_device_status(void) {
   return RISA_B200_OK;
 }
 
-
+extern "C" int risa_b200_bounded_wait_self_test(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull)
+    return risa_b200::fail(RISA_B200_INVALID,
+                           "bounded_wait_self_test: limit must be in (0, 1e9] nanoseconds");
+  risa_b200::bounded_wait_self_test_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      limit_ns);
+  return risa_b200::check_launch("bounded-wait self test");
+}

@@ -3,7 +3,8 @@
 // issues back-to-back tcgen05.mma kind::i8 128 x 256 x 32 instructions on operands that stay in
 // shared memory, alternating between two tensor-memory accumulators, and waits (bounded) for the
 // last one.  Operand values are whatever shared memory holds: integer MMAs have no slow inputs.
-#include "common.cuh"
+// Built into its own library (librisa_b200_probe.so): a measurement aid, not part of the product.
+#include "../../include/risa_b200_probe.h"
 #include "tc_ptx.cuh"
 
 namespace risa_b200 {
@@ -14,19 +15,18 @@ using namespace tc;
 constexpr int kPeakThreads = 128;
 constexpr int kPeakSmem = 16384 + 32768 + 1024 + 64;  // A 128 x 128 B, B 256 x 128 B, alignment, barrier
 
-__device__ unsigned int g_peak_status;
-
 __global__ void __launch_bounds__(kPeakThreads, 1) mma_i8_issue_loop_kernel(int mma_count) {
   extern __shared__ unsigned char peak_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(peak_smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bar = sbase + 16384 + 32768, slot = bar + 16;
+  const uint32_t bar = sbase + 16384 + 32768, slot = bar + 16, gave_up = bar + 32;
   const int warp = threadIdx.x >> 5;
   // defined operand bytes (any integers do)
   for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += kPeakThreads)
     reinterpret_cast<uint32_t*>(smem)[i] = 0x01020304u * (i + 1);
   if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile uint32_t*>(smem + 16384 + 32768 + 32) = 0u;
     mbar_init(bar, 1);
     mbar_init_fence();
   }
@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_i8_issue_loop_kernel(int 
       mma_i8(tmem + 256 * ((i >> 2) & 1), desc_a + 2 * (i & 3), desc_b + 2 * (i & 3), idesc,
              (i & 3) != 0);
     mma_commit(bar);
-    mbar_wait(bar, 0, &g_peak_status, 901);
+    mbar_wait(bar, 0, gave_up, 901);
   }
   tc_fence_before();
   __syncthreads();
@@ -60,22 +60,22 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_i8_issue_loop_kernel(int 
 extern "C" int risa_b200_mma_i8_issue_loop(int mma_per_cta, int* ctas, double* ops_per_launch,
                                            void* stream) {
   using namespace risa_b200;
-  RISA_REQUIRE(mma_per_cta > 0 && mma_per_cta <= (1 << 20) && ctas && ops_per_launch,
-               "mma_i8_issue_loop: 1..2^20 MMAs per CTA and non-null outputs");
+  if (mma_per_cta <= 0 || mma_per_cta > (1 << 20) || !ctas || !ops_per_launch)
+    return int(cudaErrorInvalidValue);
   int device = 0, sms = 0;
-  cudaGetDevice(&device);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-    return fail(RISA_B200_CUDA, "mma_i8_issue_loop: cannot read the SM count");
+  cudaError_t e = cudaGetDevice(&device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) return int(e);
   static thread_local int configured = -1;
   if (configured != device) {
-    if (cudaFuncSetAttribute(mma_i8_issue_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kPeakSmem) != cudaSuccess)
-      return fail(RISA_B200_CUDA, "mma_i8_issue_loop: cannot reserve shared memory");
+    e = cudaFuncSetAttribute(mma_i8_issue_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kPeakSmem);
+    if (e != cudaSuccess) return int(e);
     configured = device;
   }
   mma_i8_issue_loop_kernel<<<sms, kPeakThreads, kPeakSmem, static_cast<cudaStream_t>(stream)>>>(
       mma_per_cta);
   *ctas = sms;
   *ops_per_launch = 2.0 * 128 * 256 * 32 * double(mma_per_cta) * sms;
-  return check_launch("mma_i8_issue_loop");
+  return int(cudaGetLastError());
 }

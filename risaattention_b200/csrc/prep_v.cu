@@ -404,8 +404,10 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
         stride_n, perm);
     const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
     const dim3 tiled_grid(p.slots / kTiledSlots, channels / kTiledChannels);
-    // 16-byte code stores need whole storage groups and an aligned destination
-    const bool tiled = k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0;
+    // 16-byte code stores need whole storage groups and an aligned destination; a CTA of the tiled
+    // kernel owns kTiledChannels channels of one head, so the head must split into whole groups
+    const bool tiled = k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0 &&
+                       head_dim % kTiledChannels == 0;
     if (tiled && midpoint_affine) {
       v_quantize_tiled_kernel<T, true><<<tiled_grid, kTiledThreads, 0, stream>>>(
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,

@@ -66,24 +66,49 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in the kernel is bounded: after kWaitLimitNs without progress the waiter records the
-// site in *error and reports failure, so a protocol bug ends the kernel instead of hanging the GPU.
+// Every wait in the kernel is bounded: after the limit without progress the waiter records the
+// site and reports failure, so a protocol bug ends the kernel instead of hanging the GPU.  Two
+// words take the record.  `gave_up` is a word in the CTA's own shared memory (zeroed before the
+// first wait): the other waiters of the same CTA poll it and leave as soon as one of them has given
+// up; it dies with the CTA, so one expired wait never poisons a later launch.  g_wait_status is the
+// process-wide report the host reads (first failing site since the last query).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ unsigned int g_wait_status;
+
+__device__ __forceinline__ uint32_t gave_up_read(uint32_t gave_up) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(gave_up) : "memory");
+  return v;
+}
 
 template <bool SPIN = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* error,
-                                          unsigned int site) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t gave_up,
+                                          unsigned int site, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_test(bar, parity)) return true;
   const uint64_t start = global_timer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < (SPIN ? 256 : 16); ++i)
       if (SPIN ? mbar_test(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    if (*reinterpret_cast<volatile unsigned int*>(error) != 0) return false;  // someone gave up
-    if (global_timer_ns() - start > kWaitLimitNs) {
-      atomicCAS(error, 0u, site);
+    if (gave_up_read(gave_up) != 0) return false;  // another waiter of this CTA gave up
+    if (global_timer_ns() - start > limit_ns) {
+      atomicCAS(&g_wait_status, 0u, site);
+      asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(gave_up), "r"(site) : "memory");
       return false;
     }
+  }
+}
+
+// Wait used while draining after a failure: ignores the give-up word (it is set by then) and only
+// stops on completion or on the limit.
+__device__ __forceinline__ bool mbar_drain(uint32_t bar, uint32_t parity,
+                                           uint64_t limit_ns = kWaitLimitNs) {
+  const uint64_t start = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - start > limit_ns) return false;
   }
 }
 
@@ -91,21 +116,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
 // (in steady state all of them are already complete), then any that failed is waited for in turn.
 template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
-                                           unsigned int* error, unsigned int site) {
+                                           uint32_t gave_up, unsigned int site) {
   const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1);
   if (r0 & r1) return true;
-  return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
-         (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1));
+  return (r0 || mbar_wait<SPIN>(b0, p0, gave_up, site)) &&
+         (r1 || mbar_wait<SPIN>(b1, p1, gave_up, site + 1));
 }
 template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1,
-                                           uint32_t b2, uint32_t p2, unsigned int* error,
+                                           uint32_t b2, uint32_t p2, uint32_t gave_up,
                                            unsigned int site) {
   const bool r0 = mbar_test(b0, p0), r1 = mbar_test(b1, p1), r2 = mbar_test(b2, p2);
   if (r0 & r1 & r2) return true;
-  return (r0 || mbar_wait<SPIN>(b0, p0, error, site)) &&
-         (r1 || mbar_wait<SPIN>(b1, p1, error, site + 1)) &&
-         (r2 || mbar_wait<SPIN>(b2, p2, error, site + 2));
+  return (r0 || mbar_wait<SPIN>(b0, p0, gave_up, site)) &&
+         (r1 || mbar_wait<SPIN>(b1, p1, gave_up, site + 1)) &&
+         (r2 || mbar_wait<SPIN>(b2, p2, gave_up, site + 2));
 }
 
 // ---- proxies / fences --------------------------------------------------------------------------

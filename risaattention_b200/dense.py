@@ -10,19 +10,16 @@ from ._quantization import prequantize_int8_attention
 from ._validation import uses_centered_values
 
 
-@torch.library.custom_op("risa_attention::int8_attention", mutates_args=())
 def _op_int8_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None,
                        use_midpoint_affine: bool, is_causal: bool) -> torch.Tensor:
     return execute_dense_attention(q, k, v, scale=scale, attn_mask=None,
                                    use_midpoint_affine=use_midpoint_affine, is_causal=is_causal)
 
 
-@_op_int8_attention.register_fake
-def _(q, k, v, scale, use_midpoint_affine, is_causal):
+def _fake_int8_attention(q, k, v, scale, use_midpoint_affine, is_causal):
     return q.new_empty(q.shape)
 
 
-@torch.library.custom_op("risa_attention::int8_attention_masked", mutates_args=())
 def _op_int8_attention_masked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                               attn_mask: torch.Tensor, scale: float | None,
                               use_midpoint_affine: bool, is_causal: bool) -> torch.Tensor:
@@ -30,9 +27,27 @@ def _op_int8_attention_masked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                    use_midpoint_affine=use_midpoint_affine, is_causal=is_causal)
 
 
-@_op_int8_attention_masked.register_fake
-def _(q, k, v, attn_mask, scale, use_midpoint_affine, is_causal):
+def _fake_int8_attention_masked(q, k, v, attn_mask, scale, use_midpoint_affine, is_causal):
     return q.new_empty(q.shape)
+
+
+def _register(name, implementation, fake) -> bool:
+    """Defines ``risa_attention::<name>`` with the reference's schema unless the process already
+    has it (the reference package imported side by side registers the same names; a second
+    definition is an error, and its operators then stay in charge of compiled graphs)."""
+    try:
+        operator = torch.library.custom_op(f"risa_attention::{name}", mutates_args=())(
+            implementation)
+    except RuntimeError:
+        return False
+    operator.register_fake(fake)
+    return True
+
+
+OPERATORS_REGISTERED = (
+    _register("int8_attention", _op_int8_attention, _fake_int8_attention),
+    _register("int8_attention_masked", _op_int8_attention_masked, _fake_int8_attention_masked),
+)
 
 
 def int8_attention(q, k, v, *, scale=None, attn_mask=None, v_quantization="absmax",

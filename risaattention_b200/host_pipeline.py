@@ -10,20 +10,29 @@ tensors only.
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from .dense import int8_attention
 
 _STREAMS: dict = {}
+_STREAMS_LOCK = threading.Lock()
 
 
 def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
-                             out: torch.Tensor | None = None, *, device=None, **kwargs):
+                             out: torch.Tensor | None = None, *, device=None,
+                             wait: bool = True, **kwargs):
     """``int8_attention`` for CPU tensors in ``[B, H, L, D]`` layout; returns a pinned CPU tensor.
 
     ``kwargs`` are passed to :func:`int8_attention` (``scale``, ``is_causal``, ``v_quantization``).
     Masks, LSE and KV permutations are not supported here.  Pinned inputs make the copies
     asynchronous; pageable inputs work but serialise.
+
+    With ``wait=True`` (default) the call returns once the last device-to-host copy has finished,
+    so the returned tensor can be read on the host at once.  With ``wait=False`` it returns
+    ``(out, event)`` while copies may still be in flight: the host must ``event.synchronize()``
+    before it reads ``out`` (work queued afterwards on the caller's stream is ordered already).
     """
     for name in ("attn_mask", "return_lse", "kv_permutation"):
         option = kwargs.get(name)
@@ -50,9 +59,10 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     # overlaps the first wave of the next stage instead of leaving SMs idle at every stage boundary.
     # The four side streams are created once per device and reused: the caching allocator keeps its
     # free blocks per stream, so fresh streams on every call would send every stage to cudaMalloc.
-    streams = _STREAMS.get(device)
-    if streams is None:
-        streams = _STREAMS[device] = tuple(torch.cuda.Stream(device) for _ in range(4))
+    with _STREAMS_LOCK:
+        streams = _STREAMS.get(device)
+        if streams is None:
+            streams = _STREAMS[device] = tuple(torch.cuda.Stream(device) for _ in range(4))
     computes, copy_in, copy_out = streams[:2], streams[2], streams[3]
     start = torch.cuda.Event()
     start.record(caller)
@@ -100,4 +110,7 @@ def int8_attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torc
     finished = torch.cuda.Event()
     finished.record(copy_out)
     caller.wait_event(finished)  # the caller's stream sees the output once this event has passed
+    if not wait:
+        return out, finished
+    finished.synchronize()
     return out

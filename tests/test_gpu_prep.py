@@ -138,3 +138,46 @@ def test_lse_shift(ref, dtype, dim):
     expect = (q.float() * sel.repeat_interleave(2, 1)).sum(-1) * dim ** -0.5
     torch.testing.assert_close(out, expect, rtol=2e-5, atol=5e-6)
     assert torch.count_nonzero(out[0, :2]) == 0
+
+
+@pytest.mark.parametrize("dim", [32, 96, 8])
+@pytest.mark.parametrize("lk", [64, 1040, 333])
+@pytest.mark.parametrize("affine", [False, True])
+def test_quantize_v_c_abi_head_dims_outside_the_kernel_set(ref, dim, lk, affine):
+    """The C-ABI accepts any head_dim that is a multiple of 8 (the Python runtime only ever passes
+    64 / 128 / 256): such sizes must take the channel-generic kernels, also when the key length is
+    a multiple of 16, and match the reference's kernel bit for bit."""
+    import ctypes
+
+    from oracle import ref_gpu
+    from risaattention_b200 import _backend
+
+    b, hkv = 2, 3
+    g = torch.Generator(device="cuda").manual_seed(dim + lk)
+    v = (torch.randn(b, hkv, lk, dim, device="cuda", generator=g) + 0.7).bfloat16()
+    padded = -(-lk // 64) * 64
+    channels = b * hkv * dim
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def buffers():
+        return (torch.full((channels, padded), 77, dtype=torch.int8, device="cuda"),
+                torch.empty(channels, device="cuda"), torch.empty(channels, device="cuda"))
+
+    codes, scale, center = buffers()
+    C = _backend._C
+    ws = torch.empty(C.quantize_v_workspace_size(b, hkv, lk, dim), dtype=torch.uint8, device="cuda")
+    guard = torch.zeros(4096, dtype=torch.uint8, device="cuda")  # allocated right after the outputs
+    C._check(C.lib.risa_b200_quantize_v(
+        ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(codes.data_ptr()),
+        ctypes.c_void_p(scale.data_ptr()), ctypes.c_void_p(center.data_ptr()), b, hkv, lk, dim,
+        padded, v.stride(0), v.stride(1), v.stride(2), 2, int(affine), None,
+        ctypes.c_void_p(ws.data_ptr()), ws.numel(), stream))
+    rc, rs, rcen = buffers()
+    ref_gpu._ok(ref_gpu.lib().ref_quantize_v(
+        ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(rc.data_ptr()),
+        ctypes.c_void_p(rs.data_ptr()), ctypes.c_void_p(rcen.data_ptr()), b, hkv, lk, dim, padded,
+        v.stride(0), v.stride(1), v.stride(2), 2, int(affine), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(codes, rc) and torch.equal(scale, rs)
+    _centers_match(center, rcen)
+    assert int(guard.sum()) == 0
