@@ -1,13 +1,19 @@
-"""Loads the C-ABI library and exposes it as the native module the runtime calls.
+"""The native module the runtime calls, and a ctypes view of the C-ABI beneath it.
 
 The reference binds its kernels through a nanobind module ``_C`` that receives DLPack capsules
-(src/risa_attention/_backend.py:6-54, csrc/bindings.cpp:642-673).  Here ``_C`` is a thin object
-over ``librisa_b200.so`` (see include/risa_b200.h) with the same entry-point names, argument
-order, keyword names and defaults, so the reference's own Python runtime can call it unchanged:
-tensor arguments may be ``torch.Tensor`` objects or DLPack capsules, scratch pointers
-(``anchor_indices_ptr``, ``permutation_ptr``) may be tensors or raw integer addresses, the stream is
-the raw ``cudaStream_t``.  There is no CPU fallback: when the library or a capable GPU is missing
-every entry point raises ``RuntimeError``.
+(src/risa_attention/_backend.py:6-54, csrc/bindings.cpp:642-673).  Here ``_C`` is the PyTorch C++
+extension built from csrc/torch_binding.cpp: the same entry-point names, argument order, keyword
+names and defaults over the C-ABI library ``librisa_b200.so`` (include/risa_b200.h), so the
+reference's own Python runtime can call it unchanged: tensor arguments may be ``torch.Tensor``
+objects or DLPack capsules, scratch pointers (``anchor_indices_ptr``, ``permutation_ptr``) may be
+tensors or raw integer addresses, the stream is the raw ``cudaStream_t``.
+
+``_Native`` is the same surface written against the shared library with ctypes alone, for hosts
+that have no C++ toolchain or no torch headers at build time and for tests that drive the C-ABI
+symbol by symbol (``_ABI.lib``); it calls exactly the same library functions.
+
+There is no CPU fallback: when the extension or a capable GPU is missing every entry point raises
+``RuntimeError``.
 """
 from __future__ import annotations
 
@@ -128,7 +134,10 @@ class _Native:
                   anchor_indices_ptr, attn_mask=None, cta_k=0, is_causal=False,
                   key_mask_tiles=None):
         """Quantise Q, K and V into the caller's packed buffers and attend, on one stream."""
-        q, k, v, o = map(_t, (q, k, v, o))
+        # a DLPack capsule can be imported once: resolve every operand here, before the two stages
+        (q, k, v, o, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale, v_center, attn_mask,
+         key_mask_tiles) = map(_t, (q, k, v, o, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale,
+                                    v_center, attn_mask, key_mask_tiles))
         if q.ndim != 4 or k.ndim != 4 or v.ndim != 4 or o.ndim != 4:
             raise RuntimeError("risa_sdpa: q, k, v, o must be 4D [batch_size,num_heads,L,head_dim]")
         if not 0 <= input_dtype_code <= 2:
@@ -261,9 +270,11 @@ class _Native:
 try:
     if getattr(torch.version, "hip", None) or not getattr(torch.version, "cuda", None):
         raise ImportError("RISA Attention requires an NVIDIA CUDA build of PyTorch")
-    _C = _Native(_LIB_PATH)
+    _ABI = _Native(_LIB_PATH)
+    from . import _C  # noqa: E402  (the PyTorch C++ extension; links librisa_b200.so)
 except (ImportError, OSError, AttributeError) as error:
     _C = None
+    _ABI = None
     _EXTENSION_ERROR = error
 
 

@@ -1,4 +1,5 @@
-"""Builds librisa_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
+"""Builds librisa_b200.so (the C-ABI library, nvcc for sm_100a) and the PyTorch C++ extension
+``_C`` over it, both in-tree.
 
 Usage: ``python -m risaattention_b200.build [--force]``.  Objects are cached under
 ``risaattention_b200/csrc/_obj`` and rebuilt when a source or header is newer.
@@ -45,6 +46,36 @@ def _compile(unit: str, force: bool, verbose: bool) -> str | None:
     return proc.stderr
 
 
+def build_torch_extension(force: bool = False) -> Path:
+    """Compiles csrc/torch_binding.cpp into the in-tree module ``risaattention_b200/_C*.so``: the
+    PyTorch C++ extension through which the Python runtime reaches the C-ABI library (linked by
+    relative run path, so the pair can be moved together)."""
+    import sysconfig
+
+    import pybind11
+    import torch
+    from torch.utils import cpp_extension
+
+    target = PKG / f"_C{sysconfig.get_config_var('EXT_SUFFIX')}"
+    src = CSRC / "torch_binding.cpp"
+    newest = max(src.stat().st_mtime, (PKG.parent / "include" / "risa_b200.h").stat().st_mtime)
+    if not force and target.exists() and target.stat().st_mtime > newest:
+        return target
+    includes = [*cpp_extension.include_paths(), pybind11.get_include(),
+                sysconfig.get_paths()["include"], "/usr/local/cuda/include"]
+    torch_lib = str(Path(torch.__file__).resolve().parent / "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           *[f"-I{path}" for path in includes], str(src), "-o", str(target),
+           f"-L{PKG}", "-lrisa_b200", f"-L{torch_lib}", "-ltorch_python", "-ltorch", "-ltorch_cpu",
+           "-lc10", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"g++ failed for torch_binding.cpp:\n{proc.stdout}\n{proc.stderr}")
+    return target
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
     units = UNITS + PROBE_UNITS
@@ -58,6 +89,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if any(logs[u] is not None for u in members) or not lib.exists():
             objs = [str(OBJ / f"{u}.o") for u in members]
             subprocess.run(["nvcc", "-shared", "-o", str(lib), *objs, "-lcudart"], check=True)
+    build_torch_extension(force)
     return LIB
 
 

@@ -14,11 +14,13 @@
 //              and everything that is sequential over tiles: running maximum, denominator, per-tile
 //              weights, O = O * o_scale + float(P.V) * w, capture statistics, epilogue and store.
 //   WG4        warp 16: TMA producer (Q, K ring, V ring); warp 17: one thread issues the QK^T MMAs,
-//              up to three tiles ahead of the softmax; warp 18: one thread issues the P.V MMAs.
-// Tensor memory (512 columns): three S buffers of 128 columns (tile it in buffer it % 3) and one
-// P.V accumulator of 128 columns.  Probabilities are scaled to the tile maximum (full 8-bit
-// resolution in every tile), so each tile's integer P.V has its own weight and is folded into FP32
-// by the correction group; nothing accumulates across tiles inside tensor memory.
+//              up to four tiles ahead of the read-back; warp 18: one thread issues the P.V MMAs.
+// Tensor memory (512 columns) is four accumulator buffers of 128 columns.  Tile it owns buffer
+// it % 4 from its Q.K^T until its P.V result has been read back: the scores are written there, the
+// softmax group reads them, P.V overwrites the same columns and the correction group takes the
+// result into registers.  Probabilities are scaled to the tile maximum (full 8-bit resolution in
+// every tile), so each tile's integer P.V has its own weight and is folded into FP32 by the
+// correction group; nothing accumulates across tiles inside tensor memory.
 // Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh.  The integer
 // products are exact, so probabilities, capture statistics and block masses are bit-identical to
 // the row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
@@ -42,6 +44,7 @@ constexpr int kVStages = 3;           // V ring depth
 constexpr int kTile = 128 * 128;      // bytes of one 128 x 128 INT8 tile
 constexpr int kThreads = 640;
 constexpr int kSoftmaxGroups = 3;     // softmax warpgroups; tile it is handled by group it % 3
+constexpr int kBuffers = 4;           // tensor-memory accumulator buffers; tile it uses it % 4
 constexpr int kRegsLaunch = 96;        // what ptxas gives 640 threads (65536 / 640, multiple of 8)
 constexpr int kRegsSoftmax = 96, kRegsCorrection = 168, kRegsIssue = 24;
 // setmaxnreg redistributes the registers the CTA was launched with (threads x launch count); a
@@ -56,12 +59,15 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
 constexpr int kExpUnroll = 2;
 constexpr unsigned int kSelfTestSite = 900;  // site number reported by the bounded-wait self test
 
-// Per head_dim: what one CTA holds and how deep its rings are.  head_dim 256 is run as two CTAs per
-// (query block, head), each contracting Q.K^T over all 256 channels (two 128-byte column panels of
-// the Q and K tiles) but producing 128 of the output channels, so that the accumulator, the output
-// registers of the correction group and tensor memory stay exactly as for head_dim 128; the price
-// is that both CTAs do the softmax.  Its larger Q / K tiles are paid for with shallower rings.
-template <int D>
+// Per head_dim and key-tile width: what one CTA holds and how deep its rings are.  head_dim 256 is
+// run as two CTAs per (query block, head), each contracting Q.K^T over all 256 channels (two
+// 128-byte column panels of the Q and K tiles) but producing 128 of the output channels, so that
+// the accumulator, the output registers of the correction group and tensor memory stay exactly as
+// for head_dim 128; the price is that both CTAs do the softmax.  Its larger Q / K tiles are paid
+// for with shallower rings.  Kernels with 64-key tiles (per-query masks, short sequences,
+// head_dim 64) have smaller K stages and spend the difference on a per-warp staging area through
+// which mask values are loaded with coalesced accesses and handed to the row-owning threads.
+template <int D, int CTA_K>
 struct SmemLayout {
   static constexpr int kOut = D == 256 ? 128 : D;          // output channels per CTA
   static constexpr int kHalves = D == 256 ? 2 : 1;         // CTAs per (query block, head)
@@ -70,21 +76,29 @@ struct SmemLayout {
   static constexpr int kKSt = D == 256 ? 2 : kKStages;     // K ring depth
   static constexpr int kVSt = D == 256 ? 2 : kVStages;     // V ring depth
   static constexpr int kSlots = D == 256 ? 3 : 4;          // P tiles and per-row statistics
-  static constexpr int kQKBytes = kPanels * kTile;         // one Q tile / one K stage
+  static constexpr int kQBytes = kPanels * kTile;          // the Q tile
+  static constexpr int kKPanel = CTA_K * 128;              // one column panel of a K stage
+  static constexpr int kKStage = kPanels * kKPanel;        // one K stage
+  static constexpr int kMaskStageWords = 32 * 33;          // 32 x 32 values, rows padded to 33
+  static constexpr int kMaskStageBytes =
+      CTA_K == 64 ? kSoftmaxGroups * 4 * kMaskStageWords * 4 : 0;  // one area per softmax warp
   static constexpr int q = 0;
-  static constexpr int k = q + kQKBytes;
-  static constexpr int v = k + kKSt * kQKBytes;
+  static constexpr int k = q + kQBytes;
+  static constexpr int v = k + kKSt * kKStage;
   static constexpr int p = v + kVSt * kTile;
   static constexpr int stats = p + kSlots * kTile;         // float2 [slots][128]: tile max, U8 sum
-  static constexpr int sums = stats + 4 * 128 * 8;         // uint16 [slots][128][32] (capture only)
-  static constexpr int bars = sums + 4 * 128 * 64;         // 8-byte mbarriers
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 20;  // a few spare
+  static constexpr int sums = stats + 4 * 128 * 8;         // uint16 [slots][128][CTA_K / 4] (capture)
+  static constexpr int mask_stage = sums + 4 * 128 * (CTA_K / 2);
+  static constexpr int bars = mask_stage + kMaskStageBytes;  // 8-byte mbarriers
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 6 * 4 + 3;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int gave_up = tmem_slot + 8;            // site of the first expired wait, or 0
   static constexpr int total = tmem_slot + 16;
   static constexpr size_t bytes = total + 1024;            // room to align the base to 1024
 };
-static_assert(SmemLayout<256>::bytes <= 232448 && SmemLayout<128>::bytes <= 232448,
+static_assert(SmemLayout<256, 128>::bytes <= 232448 && SmemLayout<128, 128>::bytes <= 232448 &&
+                  SmemLayout<256, 64>::bytes <= 232448 && SmemLayout<128, 64>::bytes <= 232448 &&
+                  SmemLayout<64, 64>::bytes <= 232448,
               "shared memory per CTA");
 
 struct TileSeq {
@@ -127,13 +141,16 @@ __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t
 struct Bars {
   uint32_t base;
   static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
-                       VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages, SFREE = SFULL + 3,
-                       PFULL = SFREE + 3, PFREE = PFULL + 4, OFULL = PFREE + 4, OFREE = OFULL + 1,
-                       STATFREE = OFREE + 1;
-  // S has three buffers (tile it uses it % 3), so the scores of a group's next tile are computed
-  // while it is still busy with the current one; the P.V accumulator has one buffer, handed back
-  // as soon as the correction group has it in registers; the probability tiles and the per-row
-  // statistics have four slots (it % L::kSlots).
+                       VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages,
+                       BUFFREE = SFULL + kBuffers, PFULL = BUFFREE + kBuffers, PFREE = PFULL + 4,
+                       OFULL = PFREE + 4, STATFREE = OFULL + kBuffers;
+  // Tensor memory is four accumulator buffers of 128 columns; tile it owns buffer it % 4 for its
+  // whole life: Q.K^T writes the scores there (SFULL), the softmax group reads them, P.V then
+  // overwrites the same columns with the tile's integer output (OFULL) and the correction group
+  // hands the buffer back once it has it in registers (BUFFREE).  Three tiles can be in the
+  // softmax stage while a fourth is in P.V / read-back, so no stage waits for another tile's
+  // accumulator.  The probability tiles and the per-row statistics have four slots
+  // (it % L::kSlots).
   __device__ __forceinline__ uint32_t operator()(int i) const { return base + 8u * i; }
 };
 
@@ -147,7 +164,7 @@ struct Bars {
 template <bool CAPTURE, int CTA_K, int KIND>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
-                                                 uint16_t* sums, uint32_t s_free_bar) {
+                                                 uint16_t* sums) {
   // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
   // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
   // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
@@ -195,13 +212,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
       // multiply followed by the packed add was observed to be merged into one fused operation
       for (int i = 0; i < 32; ++i) x[i] = __fmul_rn(x[i], sc[(i & 7) >> 1]);
     }
-    if (c > 0) {
-      tmem_load32(tmem_row + 32 * (c - 1), raw);
-    } else {
-      // all scores of the tile are in registers: the MMA warp may overwrite S with the next tile
-      tc_fence_before();
-      mbar_arrive(s_free_bar);
-    }
+    if (c > 0) tmem_load32(tmem_row + 32 * (c - 1), raw);
     uint32_t P[8], s4[8];
     tile_exp_chunk<KIND, CAPTURE>(x, sc, neg_m, P, numer, s4);
     if constexpr (CAPTURE) {
@@ -216,51 +227,142 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
-// Every other case (last visited tile, causal, scale <= 0): float scores with the masks applied.
+// Mask values of a block of 32 query rows x 32 keys, fetched by the warp that owns the rows: for
+// every row the 32 lanes read 32 consecutive keys (one coalesced request per row instead of one
+// strided request per lane), the block is turned around through the warp's shared staging area
+// (rows padded to 33 words: conflict-free both ways) and lane r leaves with row r's values as FP32
+// bit patterns: the additive bias, 0 for a kept boolean entry, NaN for anything masked (boolean
+// false, non-finite bias, rows or keys past the end).
+__device__ __forceinline__ void mask_block_rows(const AttentionArgs& a, int batch, int head,
+                                                int row0, int kv0, uint32_t* stage, int lane,
+                                                uint32_t (&vals)[32]) {
+  constexpr uint32_t kMasked = 0x7fc00000u;
+  const int kv = kv0 + lane;
+  const bool kv_ok = kv < a.k_len;
+  const int64_t base = int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
+                       int64_t(kv) * a.mask_stride_k;
+  const int code = a.mask_dtype_code;
+#pragma unroll 8
+  for (int r = 0; r < 32; ++r) {
+    const int row = row0 + r;
+    uint32_t bits = kMasked;
+    if (kv_ok && row < a.q_len) {
+      const int64_t off = base + int64_t(row) * a.mask_stride_q;
+      if (code == 3)
+        bits = static_cast<const uint8_t*>(a.mask)[off] != 0 ? 0u : kMasked;
+      else if (code == 0)
+        bits = static_cast<const uint32_t*>(a.mask)[off];
+      else if (code == 1)
+        bits = __float_as_uint(__half2float(static_cast<const __half*>(a.mask)[off]));
+      else
+        bits = uint32_t(static_cast<const uint16_t*>(a.mask)[off]) << 16;
+    }
+    stage[r * 33 + lane] = bits;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) vals[i] = stage[lane * 33 + i];
+  __syncwarp();
+}
+
+// A per-query mask is one long row per query: a CTA's tile touches 128 rows that lie far apart in
+// memory and takes only CTA_K elements of each, which on its own makes every access open a new
+// DRAM page.  Every kMaskRunKeys keys the warp that owns the rows therefore asks L2 for the next
+// run of each of its rows in one piece (lane r = row r); the tile loads that follow hit L2.
+constexpr int kMaskRunKeys = 512;
+
+__device__ __forceinline__ void mask_prefetch_runs(const AttentionArgs& a, int batch, int head,
+                                                   int row, int first_key) {
+  if (row >= a.q_len || first_key >= a.k_len || a.mask_stride_k != 1) return;
+  const int esize = a.mask_dtype_code == 3 ? 1 : a.mask_dtype_code == 0 ? 4 : 2;
+  const int64_t off = int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
+                      int64_t(row) * a.mask_stride_q + first_key;
+  const uintptr_t begin = (reinterpret_cast<uintptr_t>(a.mask) + off * esize) & ~uintptr_t(15);
+  const uintptr_t row_end = reinterpret_cast<uintptr_t>(a.mask) +
+                            (off - first_key + a.k_len) * esize;
+  uintptr_t end = begin + kMaskRunKeys * esize + 16;
+  if (end > row_end) end = row_end & ~uintptr_t(15);
+  if (end > begin) l2_prefetch_run(reinterpret_cast<const void*>(begin), uint32_t(end - begin));
+}
+
+// Every other case (last visited tile, masks, causal diagonal, scale <= 0).  Pass 1 turns the raw
+// integers into the scores the reference's generic path works on -- scaled, mask and causal rule
+// applied, keys past the end removed -- takes their maxima and writes them back over the raw
+// scores in tensor memory; pass 2 reads those floats, so masks are fetched once per tile.
+// mask_stage: the warp's staging area (64-key-tile kernels), or nullptr.
 template <bool CAPTURE, int CTA_K>
 __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int batch, int head,
                                                      bool row_ok, uint32_t tmem_row,
                                                      const float (&sc)[4], unsigned char* p_row,
                                                      int swz, float2* stat, uint16_t* sums,
-                                                     bool int_scores, bool last, int row, int c0) {
+                                                     bool int_scores, bool last, int row, int c0,
+                                                     uint32_t* mask_stage) {
   const bool causal = a.is_causal != 0, masked = a.mask != nullptr;
   const int k_len = a.k_len;
-  auto load_chunk = [&](int c, float* x) {
-    uint32_t raw[32];
-    tmem_load32(tmem_row + 32 * c, raw);
-    tmem_load_wait();
-    tmem_regs_ready<32>(raw);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int kv = c0 + 32 * c + i;
-      float s = static_cast<float>(int(raw[i]));
-      if (int_scores) {
-        if (last && kv >= k_len) s = -1.0e30f;
-      } else {
-        if (masked) s = apply_mask(a, batch, head, row, kv, row_ok, s, sc[(i & 7) >> 1]);
-        else s = __fmul_rn(s, sc[(i & 7) >> 1]);
-        if (causal && kv > row) s = -INFINITY;
-        if (last && kv >= k_len) s = -INFINITY;
-      }
-      x[i] = s;
-    }
-  };
+  // per-query masks go through the staging area; masks broadcast over queries are read directly
+  // (all lanes of a warp then ask for the same address)
+  const bool staged = masked && mask_stage != nullptr && a.mask_stride_q != 0;
+  const int lane = threadIdx.x & 31;
+  if (staged && c0 % kMaskRunKeys == 0) mask_prefetch_runs(a, batch, head, row, c0 + kMaskRunKeys);
   TileMax tm;
   tile_max_init<kScoresScaled, true>(tm);  // maxima start at -50000 in all of these cases
 #pragma unroll 1
   for (int c = 0; c < CTA_K / 32; ++c) {
+    uint32_t raw[32];
     float x[32];
-    load_chunk(c, x);
+    tmem_load32(tmem_row + 32 * c, raw);
+    if (staged) {
+      uint32_t bias_bits[32];
+      mask_block_rows(a, batch, head, row - lane, c0 + 32 * c, mask_stage, lane, bias_bits);
+      tmem_load_wait();
+      tmem_regs_ready<32>(raw);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float bias = __uint_as_float(bias_bits[i]);
+        // score * scale and + bias * log2(e) are separate roundings, as in apply_mask
+        float s = __fadd_rn(__fmul_rn(static_cast<float>(int(raw[i])), sc[(i & 7) >> 1]),
+                            bias * kLog2e);
+        if (!isfinite(bias)) s = -INFINITY;
+        if (causal && c0 + 32 * c + i > row) s = -INFINITY;
+        x[i] = s;
+      }
+    } else {
+      tmem_load_wait();
+      tmem_regs_ready<32>(raw);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int kv = c0 + 32 * c + i;
+        float s = static_cast<float>(int(raw[i]));
+        if (int_scores) {
+          if (last && kv >= k_len) s = -1.0e30f;
+        } else {
+          if (masked) s = apply_mask(a, batch, head, row, kv, row_ok, s, sc[(i & 7) >> 1]);
+          else s = __fmul_rn(s, sc[(i & 7) >> 1]);
+          if (causal && kv > row) s = -INFINITY;
+          if (last && kv >= k_len) s = -INFINITY;
+        }
+        x[i] = s;
+      }
+    }
     tile_max_chunk(x, tm);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(x[i]);
+    tmem_store32(tmem_row + 32 * c, raw);
   }
+  tmem_store_wait();
   const float tile_m = int_scores ? tile_max_finish<kScoresInt>(tm, sc)
                                   : tile_max_finish<kScoresScaled>(tm, sc);
   uint32_t numer = 0;
 #pragma unroll 1
   for (int c = 0; c < CTA_K / 32; ++c) {
+    uint32_t raw[32];
     float x[32];
     uint32_t P[8], s4[8];
-    load_chunk(c, x);
+    tmem_load32(tmem_row + 32 * c, raw);
+    tmem_load_wait();
+    tmem_regs_ready<32>(raw);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(raw[i]);
     if (int_scores) tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, -tile_m, P, numer, s4);
     else tile_exp_chunk<kScoresScaled, CAPTURE>(x, sc, -tile_m, P, numer, s4);
     if constexpr (CAPTURE) {
@@ -279,7 +381,7 @@ template <bool CAPTURE, int CTA_K, int D>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
-  using L = SmemLayout<D>;
+  using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -306,12 +408,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       mbar_init(bar(Bars::VFULL + s), 1);
       mbar_init(bar(Bars::VEMPTY + s), 1);
     }
-    for (int b = 0; b < 3; ++b) {
+    for (int b = 0; b < kBuffers; ++b) {
       mbar_init(bar(Bars::SFULL + b), 1);
-      mbar_init(bar(Bars::SFREE + b), 128);
+      mbar_init(bar(Bars::OFULL + b), 1);
+      mbar_init(bar(Bars::BUFFREE + b), 128);
     }
-    mbar_init(bar(Bars::OFULL), 1);
-    mbar_init(bar(Bars::OFREE), 128);
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(Bars::STATFREE + i), 128);
       mbar_init(bar(Bars::PFULL + i), 128);
@@ -324,7 +425,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + L::tmem_slot);
-  const uint32_t tmem_o = tmem + 384;  // S buffers at columns 0, 128, 256
 
   const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE);
   float2* stats = reinterpret_cast<float2*>(smem + L::stats);
@@ -353,7 +453,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           mbar_expect_tx(bar(Bars::KFULL + s), CTA_K * D);
 #pragma unroll
           for (int panel = 0; panel < L::kPanels; ++panel)
-            tma_load_3d(sbase + L::k + s * L::kQKBytes + panel * kTile, &map_k,
+            tma_load_3d(sbase + L::k + s * L::kKStage + panel * L::kKPanel, &map_k,
                         bar(Bars::KFULL + s), 128 * panel, seq.tile(step) * CTA_K, int(kvh));
           k_issued = step + 1;
         }
@@ -380,14 +480,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
     } else if (warp == 17 && lane == 0) {
       // ---------------------------------------------------------------- MMA issue: S = Q.K^T
-      // Tile it goes to S buffer it % 3 as soon as the softmax group has read that buffer's
-      // previous tile.  Issuing the two GEMMs from two threads halves the per-tile barrier
-      // round-trips on each.
+      // Tile it goes to buffer it % 4 as soon as the correction group has read that buffer's
+      // previous tile (it - 4) out.  Issuing the two GEMMs from two threads halves the per-tile
+      // barrier round-trips on each.
       constexpr uint32_t idesc_qk = idesc_i8(true, true, CTA_K);
       bool ok = mbar_wait<true>(bar(Bars::QFULL), 0, gave_up, 201);
       for (int it = 0; it < seq.n_iter && ok; ++it) {
-        const int b = it % 3, u = it / 3, s = it % L::kKSt, r = it / L::kKSt;
-        ok = mbar_wait2<true>(bar(Bars::KFULL + s), r & 1, bar(Bars::SFREE + b), (u & 1) ^ 1,
+        const int b = it % kBuffers, u = it / kBuffers, s = it % L::kKSt, r = it / L::kKSt;
+        ok = mbar_wait2<true>(bar(Bars::KFULL + s), r & 1, bar(Bars::BUFFREE + b), (u & 1) ^ 1,
                               gave_up, 202);
         if (!ok) break;
         tc_fence_after();
@@ -395,7 +495,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         for (int panel = 0; panel < L::kPanels; ++panel) {
           const uint64_t desc_q = smem_desc_kmajor<L::kPanelBytes>(sbase + L::q + panel * kTile);
           const uint64_t desc_k = smem_desc_kmajor<L::kPanelBytes>(
-              sbase + L::k + s * L::kQKBytes + panel * kTile);
+              sbase + L::k + s * L::kKStage + panel * L::kKPanel);
 #pragma unroll
           for (int kk = 0; kk < L::kPanelBytes / 32; ++kk)
             mma_i8(tmem + 128 * b, desc_q + 2 * kk, desc_k + 2 * kk, idesc_qk, (panel | kk) > 0);
@@ -410,9 +510,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       for (int it = 0; it < seq.n_iter && ok; ++it) {
         const int s = it % L::kVSt, r = it / L::kVSt;
         const int slot = it % L::kSlots, j = it / L::kSlots;
-        ok = mbar_wait3<true>(bar(Bars::PFULL + slot), j & 1, bar(Bars::VFULL + s), r & 1,
-                              bar(Bars::OFREE), (it & 1) ^ 1, gave_up, 204);
+        ok = mbar_wait2<true>(bar(Bars::PFULL + slot), j & 1, bar(Bars::VFULL + s), r & 1,
+                              gave_up, 204);
         if (!ok) break;
+        const int b = it % kBuffers;
+        const uint32_t tmem_o = tmem + 128 * b;  // the tile's scores have all been read by now
         tc_fence_after();
         const uint64_t desc_p = smem_desc_k128(sbase + L::p + slot * kTile);
         const uint64_t desc_v = smem_desc_k128(sbase + L::v + s * kTile);
@@ -421,7 +523,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
         for (int kk = 0; kk < CTA_K / 32; ++kk)
           mma_i8(tmem_o, desc_p + 2 * kk, desc_v + v_k0 + 2 * kk, idesc_pv, kk > 0);
-        mma_commit(bar(Bars::OFULL));
+        mma_commit(bar(Bars::OFULL + b));
         mma_commit(bar(Bars::VEMPTY + s));
         mma_commit(bar(Bars::PFREE + slot));
       }
@@ -429,7 +531,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   } else if (wg < kSoftmaxGroups) {
     // ------------------------------------------------------------------ softmax of tiles it = wg, wg+3, ...
     if constexpr (kRegsSoftmax > kRegsLaunch) regs_inc<kRegsSoftmax>();
-    const int b = wg;
+    const int b = wg;                      // first tile of this group
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
@@ -441,15 +543,21 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         D == 256 ? __ldg(a.q_scale + bh * (n_q * 64) + (row / 16) * 8 + (row & 7))
                  : __ldg(a.q_scale + bh * (n_q * 32) + (row / 32) * 8 + (row & 7));
     const float* k_scale = a.k_scale + kvh * (n_k * 4);
+    uint32_t* mask_stage = nullptr;  // this warp's staging area for per-query mask blocks
+    if constexpr (L::kMaskStageBytes > 0)
+      mask_stage = reinterpret_cast<uint32_t*>(smem + L::mask_stage) + warp * L::kMaskStageWords;
     bool ok = true;
     float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
+    if (b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
+        seq.ids == nullptr)
+      mask_prefetch_runs(a, batch, head, row, 0);
     if (b < seq.n_iter) {
       const int first_tile = seq.tile(b);
 #pragma unroll
       for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + first_tile * 4 + g);
     }
     for (int it = b; it < seq.n_iter && ok; it += kSoftmaxGroups) {
-      const int sb = it % 3, u = it / 3;
+      const int sb = it % kBuffers, u = it / kBuffers;
       const uint32_t tmem_row = tmem_lane + 128 * sb;
       const int tile = seq.tile(it);
       const bool last = seq.last_rules(it, tile);
@@ -461,11 +569,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
         for (int g = 0; g < 4; ++g) ks_next[g] = __ldg(k_scale + next_tile * 4 + g);
       }
-      // The P buffer is free once P.V of this group's previous tile is done, the statistics slot
-      // once the correction group has read the tile four back; S is ready when the MMA warp says so.
+      // The P slot is free once the P.V that read it is done, the statistics slot once the
+      // correction group has read the tile four back; S is ready when the MMA warp says so.
       const int slot = it % L::kSlots;
       float2* stat = stats + slot * 128 + row_in;
-      uint16_t* my_sums = sums + (slot * 128 + row_in) * 32;
+      uint16_t* my_sums = sums + (slot * 128 + row_in) * (CTA_K / 4);
       unsigned char* p_row = smem + L::p + slot * kTile + row_in * 128;
       ok = mbar_wait3(bar(Bars::PFREE + slot), ((it / L::kSlots) & 1) ^ 1, bar(Bars::STATFREE + slot),
                       ((it / L::kSlots) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, gave_up, 301);
@@ -475,17 +583,17 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       if (int_scores && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
-                                                     my_sums, bar(Bars::SFREE + sb));
+                                                     my_sums);
       else if (below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
-                                                        my_sums, bar(Bars::SFREE + sb));
-      else {
+                                                        my_sums);
+      else
         softmax_tile_general<CAPTURE, CTA_K>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                              row_in & 7, stat, my_sums, int_scores, last, row,
-                                             tile * CTA_K);
-        tc_fence_before();
-        mbar_arrive(bar(Bars::SFREE + sb));
-      }
+                                             tile * CTA_K, mask_stage);
+      // every score of the tile has been read (the loads were waited for) and the probabilities
+      // are in shared memory: P.V may now overwrite the buffer
+      tc_fence_before();
       fence_async_smem();
       mbar_arrive(bar(Bars::PFULL + slot));
     }
@@ -506,59 +614,44 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = true;
-    // Software-pipelined by one tile.  Each iteration first folds the accumulator of tile it - 1
-    // (whose weights were computed in the previous iteration) and hands it back, so that the P.V
-    // of tile `it` can start the moment its probabilities exist; then it consumes the statistics
-    // of tile `it` (running maximum, denominator, weights).
+    // Software-pipelined by one tile: iteration `it` folds the accumulator of tile it - 1 (whose
+    // weights were computed one iteration earlier) and takes the statistics of tile it (running
+    // maximum, denominator, weights).  This group is the one strictly sequential stage of the
+    // kernel, so its per-tile latency sets the pace: both events are waited for together, the
+    // first accumulator chunk is requested at once, and the statistics -- a short chain of
+    // dependent FP32 operations -- are worked out while that chunk travels.
     float prev_o_scale = 1.0f, prev_w = 0.0f;
     float m_o = -INFINITY;  // maximum the FP32 output rows are scaled to (dense path only)
     for (int it = 0; it <= seq.n_iter && ok; ++it) {
-      float cur_o_scale = 1.0f, cur_w = 0.0f;
-      if (it >= 1) {
-        const int j = it - 1;
-        ok = mbar_wait(bar(Bars::OFULL), j & 1, gave_up, 402);
-        if (!ok) break;
+      const bool fold = it >= 1, take = it < seq.n_iter;
+      const int j = it - 1;
+      const int ob = j & (kBuffers - 1);
+      const int slot = it % L::kSlots;
+      const uint32_t tmem_o = tmem + 128 * ob;
+      if (fold && take)
+        ok = mbar_wait2(bar(Bars::OFULL + ob), (j / kBuffers) & 1, bar(Bars::PFULL + slot),
+                        (it / L::kSlots) & 1, gave_up, 401);
+      else if (fold)
+        ok = mbar_wait(bar(Bars::OFULL + ob), (j / kBuffers) & 1, gave_up, 401);
+      else
+        ok = mbar_wait(bar(Bars::PFULL + slot), (it / L::kSlots) & 1, gave_up, 402);
+      if (!ok) break;
+      uint32_t acc[16];
+      if (fold) {
         tc_fence_after();
-        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
-        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
-        uint32_t acc[16];
         tmem_load16(tmem_o + lane_base, acc);
-#pragma unroll
-        for (int c = 0; c < kOut / 16; ++c) {
-          tmem_load_wait();
-          tmem_regs_ready<16>(acc);
-          uint64_t f2[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
-                               static_cast<float>(int(acc[2 * i + 1])));
-          if (c < kOut / 16 - 1) {
-            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
-          } else {
-            tc_fence_before();
-            mbar_arrive(bar(Bars::OFREE));
-          }
-          if (rescale) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
-        }
       }
-      if (it < seq.n_iter) {
+      float cur_o_scale = 1.0f, cur_w = 0.0f;
+      if (take) {
         const bool last_iter = it == seq.n_iter - 1;
         const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
-        ok = mbar_wait(bar(Bars::PFULL + (it % L::kSlots)), (it / L::kSlots) & 1, gave_up, 401);
-        if (!ok) break;
-        const int slot = it % L::kSlots;
         const float2 stat = stats[slot * 128 + row_in];
         const uint32_t numer = __float_as_uint(stat.y);
         const TileScales ts = tile_begin(st, stat.x);
         cur_o_scale = ts.o_scale;
         cur_w = ts.w;
         if constexpr (CAPTURE) {
-          const uint16_t* s16 = sums + (slot * 128 + row_in) * 32;
+          const uint16_t* s16 = sums + (slot * 128 + row_in) * (CTA_K / 4);
 #pragma unroll
           for (int c = 0; c < CTA_K / 32; ++c) {
             uint16_t s4[8];
@@ -590,6 +683,32 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           cur_w = ex2_approx(stat.x - m_o);
         }
         mbar_arrive(bar(Bars::STATFREE + slot));
+      }
+      if (fold) {
+        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
+        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
+#pragma unroll
+        for (int c = 0; c < kOut / 16; ++c) {
+          tmem_load_wait();
+          tmem_regs_ready<16>(acc);
+          uint64_t f2[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
+                               static_cast<float>(int(acc[2 * i + 1])));
+          if (c < kOut / 16 - 1) {
+            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
+          } else {
+            tc_fence_before();
+            mbar_arrive(bar(Bars::BUFFREE + ob));  // Q.K^T of tile j + 4 may take the buffer
+          }
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
+        }
       }
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
@@ -710,10 +829,10 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
   cudaGetDevice(&device);
   if (configured != device) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(SmemLayout<D>::bytes));
+                                         int(SmemLayout<D, CTA_K>::bytes));
     if (e != cudaSuccess)
       return fail(RISA_B200_CUDA, "attention: cannot reserve %zu bytes of shared memory: %s",
-                  SmemLayout<D>::bytes, cudaGetErrorString(e));
+                  SmemLayout<D, CTA_K>::bytes, cudaGetErrorString(e));
     // setmaxnreg hands out the registers the CTA is launched with; if the compiler ever gave this
     // kernel fewer than the roles ask for, the increase could never be granted (it blocks, beyond
     // the reach of the bounded waits), so such a build must not run
@@ -729,8 +848,8 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
                   128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue) / kThreads);
     configured = device;
   }
-  const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D>::kHalves, a.batch);
-  kernel<<<grid, kThreads, SmemLayout<D>::bytes, stream>>>(map_q, map_k, map_v, a);
+  const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D, CTA_K>::kHalves, a.batch);
+  kernel<<<grid, kThreads, SmemLayout<D, CTA_K>::bytes, stream>>>(map_q, map_k, map_v, a);
   return check_launch("attention (tensor-core kernel)");
 }
 

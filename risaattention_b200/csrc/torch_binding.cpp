@@ -1,0 +1,343 @@
+// PyTorch C++ extension over the C-ABI of librisa_b200.so: the native module the Python runtime
+// calls.  It mirrors the reference project's nanobind module `_C` (csrc/bindings.cpp:642-673): same
+// function names, argument order, keyword names and defaults, so the reference's own Python
+// runtime can use it unchanged.  A tensor argument may be a torch.Tensor or a DLPack capsule (what
+// the reference's runtime passes); scratch pointers may be tensors or raw integer addresses.  The
+// module only unpacks shapes, strides and pointers and forwards them: every kernel, and every
+// check on what the kernels can take, lives behind include/risa_b200.h.  A non-zero status becomes
+// RuntimeError carrying risa_b200_last_error().
+#include <torch/extension.h>
+
+#include <ATen/DLConvertor.h>
+
+#include <cstdint>
+#include <optional>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/risa_b200.h"
+
+namespace py = pybind11;
+
+namespace {
+
+void check(int status) {
+  if (status != RISA_B200_OK) throw std::runtime_error(risa_b200_last_error());
+}
+
+// torch.Tensor passes through; a DLPack capsule is imported without a copy (and, as DLPack
+// prescribes, can be imported only once).
+at::Tensor tensor_of(const py::handle& object, const char* what) {
+  if (THPVariable_Check(object.ptr())) return THPVariable_Unpack(object.ptr());
+  if (PyCapsule_CheckExact(object.ptr())) {
+    auto* managed =
+        static_cast<DLManagedTensor*>(PyCapsule_GetPointer(object.ptr(), "dltensor"));
+    if (managed == nullptr) {
+      PyErr_Clear();
+      throw std::runtime_error(std::string(what) +
+                               ": DLPack capsule was already consumed or is not a tensor");
+    }
+    at::Tensor tensor = at::fromDLPack(managed);
+    PyCapsule_SetName(object.ptr(), "used_dltensor");
+    return tensor;
+  }
+  throw std::runtime_error(std::string(what) + ": expected a torch.Tensor or a DLPack capsule");
+}
+
+std::optional<at::Tensor> optional_tensor(const py::object& object, const char* what) {
+  if (object.is_none()) return std::nullopt;
+  return tensor_of(object, what);
+}
+
+// Device address from a tensor, a capsule, an integer address or None.
+void* address_of(const py::object& object, const char* what) {
+  if (object.is_none()) return nullptr;
+  if (py::isinstance<py::int_>(object))
+    return reinterpret_cast<void*>(object.cast<uintptr_t>());
+  return tensor_of(object, what).data_ptr();
+}
+
+void* stream_of(uintptr_t stream_ptr) { return reinterpret_cast<void*>(stream_ptr); }
+
+int dtype_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kHalf: return 1;
+    case at::kBFloat16: return 2;
+    case at::kBool: return 3;
+    default: return -1;
+  }
+}
+
+void quantize_tensors(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                      const at::Tensor& q_int8, const at::Tensor& q_scale,
+                      const at::Tensor& k_int8, const at::Tensor& k_scale,
+                      const at::Tensor& v_int8, const at::Tensor& v_scale,
+                      const at::Tensor& v_center, int cta_k, int input_dtype_code,
+                      bool use_midpoint_affine, uintptr_t stream_ptr, void* anchors,
+                      void* kv_table, void* q_table, std::optional<at::Tensor> workspace) {
+  if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4 || v_int8.dim() != 2)
+    throw std::runtime_error("risa_sdpa_quantize: q, k, v must be 4D and packed V 2D");
+  const int b = int(q.size(0)), hq = int(q.size(1)), lq = int(q.size(2)), d = int(q.size(3));
+  const int hkv = int(k.size(1)), lk = int(k.size(2));
+  if (!workspace.has_value()) {
+    // scratch of the V quantiser, taken from the caching allocator on the current stream
+    const size_t bytes = risa_b200_quantize_v_workspace_size(b, hkv, lk, d);
+    workspace = at::empty({int64_t(bytes)}, q.options().dtype(at::kByte));
+  }
+  check(risa_b200_quantize_qk(q.data_ptr(), q_int8.data_ptr(), q_scale.data_ptr<float>(),
+                              k.data_ptr(), k_int8.data_ptr(), k_scale.data_ptr<float>(), b, hq,
+                              lq, hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2),
+                              k.stride(0), k.stride(1), k.stride(2), input_dtype_code,
+                              static_cast<int32_t*>(anchors), static_cast<const int32_t*>(q_table),
+                              static_cast<const int32_t*>(kv_table), stream_of(stream_ptr)));
+  check(risa_b200_quantize_v(v.data_ptr(), v_int8.data_ptr(), v_scale.data_ptr<float>(),
+                             v_center.data_ptr<float>(), b, hkv, lk, d, int(v_int8.size(1)),
+                             v.stride(0), v.stride(1), v.stride(2), input_dtype_code,
+                             use_midpoint_affine ? 1 : 0, static_cast<const int32_t*>(kv_table),
+                             workspace->data_ptr(), size_t(workspace->numel()),
+                             stream_of(stream_ptr)));
+}
+
+void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at::Tensor& v_int8,
+                    const at::Tensor& o, const at::Tensor& q_scale, const at::Tensor& k_scale,
+                    const at::Tensor& v_scale, const at::Tensor& v_center, int cta_k,
+                    float sm_scale, int output_dtype_code, uintptr_t stream_ptr,
+                    const std::optional<at::Tensor>& attn_mask,
+                    const std::optional<at::Tensor>& row_offsets,
+                    const std::optional<at::Tensor>& block_indices,
+                    const std::optional<at::Tensor>& block_mass, bool is_causal,
+                    const std::optional<at::Tensor>& lse,
+                    const std::optional<at::Tensor>& key_mask_tiles) {
+  if (q_int8.dim() != 4 || k_int8.dim() != 4 || o.dim() != 4)
+    throw std::runtime_error("risa_sdpa_prequantized: packed q, k and the output must be 4D");
+  const int64_t b = q_int8.size(0), hq = q_int8.size(1), lq = q_int8.size(2), d = q_int8.size(3);
+  const int64_t hkv = k_int8.size(1), lk = k_int8.size(2);
+  const int64_t padded = (lk + cta_k - 1) / cta_k * cta_k;
+  if (v_int8.dim() != 2 || v_int8.size(0) != b * hkv * d || v_int8.size(1) != padded ||
+      o.size(0) != b || o.size(1) != hq || o.size(2) != lq || o.size(3) != d ||
+      k_int8.size(0) != b || k_int8.size(3) != d)
+    throw std::runtime_error("risa_sdpa_prequantized: incompatible quantized tensor shapes");
+  const bool hnd = (lq <= 1 || o.stride(2) == d) && (hq <= 1 || o.stride(1) == lq * d);
+  const bool nhd = (hq <= 1 || o.stride(1) == d) && (lq <= 1 || o.stride(2) == hq * d);
+  if (!q_int8.is_contiguous() || !k_int8.is_contiguous() || !v_int8.is_contiguous() ||
+      o.stride(3) != 1 || !(hnd || nhd))
+    throw std::runtime_error("risa_sdpa_prequantized: quantized tensors must be contiguous and "
+                             "output must use HND- or NHD-contiguous storage");
+  if (lse.has_value() &&
+      (lse->dim() != 3 || lse->size(0) != b || lse->size(1) != hq || lse->size(2) != lq ||
+       lse->scalar_type() != at::kFloat || !lse->is_contiguous()))
+    throw std::runtime_error(
+        "risa_sdpa_prequantized: LSE must be contiguous float32 [batch_size,Hq,query_length]");
+  int64_t ms[4] = {0, 0, 0, 0};
+  int mask_code = -1;
+  const void* mask_ptr = nullptr;
+  if (attn_mask.has_value()) {
+    const at::Tensor& m = *attn_mask;
+    if (m.dim() != 4 || m.size(0) != b || m.size(1) != hq || m.size(2) != lq || m.size(3) != lk)
+      throw std::runtime_error("risa_sdpa_prequantized: attention mask must be expanded to "
+                               "[batch_size,query_heads,query_length,key_length]");
+    mask_code = dtype_code(m);
+    if (mask_code < 0)
+      throw std::runtime_error("risa_sdpa_prequantized: attention mask must be bool, float16, "
+                               "bfloat16, or float32");
+    mask_ptr = m.data_ptr();
+    for (int i = 0; i < 4; ++i) ms[i] = m.stride(i);
+  }
+  const int64_t o_b = b <= 1 ? hq * lq * d : o.stride(0);
+  const int64_t o_n = lq <= 1 ? d : o.stride(2);
+  const int64_t o_h = hq <= 1 ? lq * d : o.stride(1);
+  auto i32 = [](const std::optional<at::Tensor>& t) {
+    return t.has_value() ? static_cast<const int32_t*>(t->data_ptr()) : nullptr;
+  };
+  check(risa_b200_attention(
+      q_int8.data_ptr(), k_int8.data_ptr(), v_int8.data_ptr(), o.data_ptr(),
+      q_scale.data_ptr<float>(), k_scale.data_ptr<float>(), v_scale.data_ptr<float>(),
+      v_center.data_ptr<float>(), mask_ptr, ms[0], ms[1], ms[2], ms[3], mask_code, cta_k, int(b),
+      int(lq), int(lk), int(hq), int(hkv), int(d), o_b, o_n, o_h, sm_scale, output_dtype_code,
+      i32(row_offsets), i32(block_indices),
+      block_mass.has_value() ? block_mass->data_ptr<float>() : nullptr, is_causal ? 1 : 0,
+      lse.has_value() ? lse->data_ptr<float>() : nullptr, i32(key_mask_tiles),
+      stream_of(stream_ptr)));
+}
+
+// ---- the reference module's entry points -------------------------------------------------------
+void risa_sdpa_quantize(py::object q, py::object k, py::object v, py::object q_int8,
+                        py::object q_scale, py::object k_int8, py::object k_scale,
+                        py::object v_int8, py::object v_scale, py::object v_center, int cta_k,
+                        int input_dtype_code, bool use_midpoint_affine, uintptr_t stream_ptr,
+                        py::object anchor_indices_ptr, py::object permutation_ptr,
+                        py::object q_permutation_ptr, py::object workspace) {
+  quantize_tensors(tensor_of(q, "q"), tensor_of(k, "k"), tensor_of(v, "v"),
+                   tensor_of(q_int8, "q_int8"), tensor_of(q_scale, "q_scale"),
+                   tensor_of(k_int8, "k_int8"), tensor_of(k_scale, "k_scale"),
+                   tensor_of(v_int8, "v_int8"), tensor_of(v_scale, "v_scale"),
+                   tensor_of(v_center, "v_center"), cta_k, input_dtype_code, use_midpoint_affine,
+                   stream_ptr, address_of(anchor_indices_ptr, "anchor_indices_ptr"),
+                   address_of(permutation_ptr, "permutation_ptr"),
+                   address_of(q_permutation_ptr, "q_permutation_ptr"),
+                   optional_tensor(workspace, "workspace"));
+}
+
+void risa_sdpa_prequantized(py::object q_int8, py::object k_int8, py::object v_int8, py::object o,
+                            py::object q_scale, py::object k_scale, py::object v_scale,
+                            py::object v_center, int cta_k, float sm_scale, int output_dtype_code,
+                            uintptr_t stream_ptr, py::object attn_mask,
+                            py::object sparse_row_offsets, py::object sparse_block_indices,
+                            py::object block_mass, bool is_causal, py::object lse,
+                            py::object key_mask_tiles) {
+  attend_tensors(tensor_of(q_int8, "q_int8"), tensor_of(k_int8, "k_int8"),
+                 tensor_of(v_int8, "v_int8"), tensor_of(o, "o"), tensor_of(q_scale, "q_scale"),
+                 tensor_of(k_scale, "k_scale"), tensor_of(v_scale, "v_scale"),
+                 tensor_of(v_center, "v_center"), cta_k, sm_scale, output_dtype_code, stream_ptr,
+                 optional_tensor(attn_mask, "attn_mask"),
+                 optional_tensor(sparse_row_offsets, "sparse_row_offsets"),
+                 optional_tensor(sparse_block_indices, "sparse_block_indices"),
+                 optional_tensor(block_mass, "block_mass"), is_causal,
+                 optional_tensor(lse, "lse"), optional_tensor(key_mask_tiles, "key_mask_tiles"));
+}
+
+void risa_sdpa(py::object q, py::object k, py::object v, py::object o, py::object q_int8,
+               py::object q_scale, py::object k_int8, py::object k_scale, py::object v_int8,
+               py::object v_scale, py::object v_center, float sm_scale, int input_dtype_code,
+               int output_dtype_code, bool use_midpoint_affine, uintptr_t stream_ptr,
+               py::object anchor_indices_ptr, py::object attn_mask, int cta_k, bool is_causal,
+               py::object key_mask_tiles) {
+  const at::Tensor tq = tensor_of(q, "q"), tk = tensor_of(k, "k"), tv = tensor_of(v, "v"),
+                   to = tensor_of(o, "o");
+  if (tq.dim() != 4 || tk.dim() != 4 || tv.dim() != 4 || to.dim() != 4)
+    throw std::runtime_error("risa_sdpa: q, k, v, o must be 4D [batch_size,num_heads,L,head_dim]");
+  if (input_dtype_code < 0 || input_dtype_code > 2)
+    throw std::runtime_error("risa_sdpa: input_dtype_code must be 0 (fp32), 1 (fp16), or 2 (bf16)");
+  void* anchors = address_of(anchor_indices_ptr, "anchor_indices_ptr");
+  if (anchors == nullptr) throw std::runtime_error("risa_sdpa: anchor_indices scratch is required");
+  const std::optional<at::Tensor> mask = optional_tensor(attn_mask, "attn_mask");
+  if (cta_k == 0)  // csrc/bindings.cpp:549-551
+    cta_k = (!mask.has_value() && tq.size(3) >= 128 && tk.size(2) > 1024) ? 128 : 64;
+  const at::Tensor qi = tensor_of(q_int8, "q_int8"), qs = tensor_of(q_scale, "q_scale"),
+                   ki = tensor_of(k_int8, "k_int8"), ks = tensor_of(k_scale, "k_scale"),
+                   vi = tensor_of(v_int8, "v_int8"), vs = tensor_of(v_scale, "v_scale"),
+                   vc = tensor_of(v_center, "v_center");
+  quantize_tensors(tq, tk, tv, qi, qs, ki, ks, vi, vs, vc, cta_k, input_dtype_code,
+                   use_midpoint_affine, stream_ptr, anchors, nullptr, nullptr, std::nullopt);
+  attend_tensors(qi, ki, vi, to, qs, ks, vs, vc, cta_k, sm_scale, output_dtype_code, stream_ptr,
+                 mask, std::nullopt, std::nullopt, std::nullopt, is_causal, std::nullopt,
+                 optional_tensor(key_mask_tiles, "key_mask_tiles"));
+}
+
+size_t retained_mass_selector_workspace_size(int row_count) {
+  return risa_b200_selector_workspace_size(row_count);
+}
+
+void select_retained_mass_csr(py::object sorted_mass, py::object descending_indices,
+                              py::object counts, py::object support, py::object row_totals,
+                              py::object row_offsets, py::object block_indices, py::object summary,
+                              py::object scan_workspace, double theta, uintptr_t stream_ptr) {
+  const at::Tensor mass = tensor_of(sorted_mass, "sorted_mass");
+  const at::Tensor order = tensor_of(descending_indices, "descending_indices");
+  const at::Tensor scan = tensor_of(scan_workspace, "scan_workspace");
+  if (mass.dim() != 2 || mass.scalar_type() != at::kFloat || order.scalar_type() != at::kLong)
+    throw std::runtime_error("select_retained_mass_csr: sorted masses must be 2D float32 with "
+                             "int64 indices");
+  check(risa_b200_select_retained_mass(
+      mass.data_ptr<float>(), order.data_ptr<int64_t>(),
+      static_cast<int32_t*>(tensor_of(counts, "counts").data_ptr()),
+      static_cast<uint8_t*>(tensor_of(support, "support").data_ptr()),
+      tensor_of(row_totals, "row_totals").data_ptr<double>(),
+      static_cast<int32_t*>(tensor_of(row_offsets, "row_offsets").data_ptr()),
+      static_cast<int32_t*>(tensor_of(block_indices, "block_indices").data_ptr()),
+      tensor_of(summary, "summary").data_ptr<double>(), scan.numel() ? scan.data_ptr() : nullptr,
+      size_t(scan.numel()) * scan.element_size(), int(mass.size(0)), int(mass.size(1)), theta,
+      stream_of(stream_ptr)));
+}
+
+void prepare_key_mask_tiles(py::object mask, py::object tiles, int tile_size,
+                            uintptr_t stream_ptr) {
+  const at::Tensor m = tensor_of(mask, "mask"), t = tensor_of(tiles, "tiles");
+  if (m.dim() != 4 || m.stride(2) != 0 || (tile_size != 64 && tile_size != 128))
+    throw std::runtime_error("prepare_key_mask_tiles requires an expanded broadcast key mask");
+  check(risa_b200_prepare_key_mask_tiles(m.data_ptr(), static_cast<int32_t*>(t.data_ptr()),
+                                         int(m.size(0)), int(m.size(1)), int(m.size(3)), tile_size,
+                                         m.stride(0), m.stride(1), m.stride(3), dtype_code(m),
+                                         stream_of(stream_ptr)));
+}
+
+void risa_lse_shift(py::object q, py::object k, py::object anchors, py::object out, float scale,
+                    uintptr_t stream_ptr) {
+  const at::Tensor tq = tensor_of(q, "q"), tk = tensor_of(k, "k");
+  check(risa_b200_correct_lse(tq.data_ptr(), tk.data_ptr(),
+                              static_cast<const int32_t*>(address_of(anchors, "anchors")),
+                              tensor_of(out, "out").data_ptr<float>(), int(tq.size(0)),
+                              int(tq.size(1)), int(tk.size(1)), int(tq.size(2)), int(tq.size(3)),
+                              tq.stride(0), tq.stride(1), tq.stride(2), tk.stride(0), tk.stride(1),
+                              tk.stride(2), scale, dtype_code(tq), stream_of(stream_ptr)));
+}
+
+// ---- additions of this library (declared in include/risa_b200.h) ------------------------------
+size_t dense_scratch_size(int batch, int q_heads, int q_len, int kv_heads, int k_len, int head_dim,
+                          int cta_k) {
+  return risa_b200_dense_scratch_size(batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k);
+}
+
+void risa_dense_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                          const at::Tensor& o, const at::Tensor& scratch, int cta_k,
+                          int input_dtype_code, bool use_midpoint_affine, float sm_scale,
+                          int output_dtype_code, bool is_causal, uintptr_t stream_ptr) {
+  check(risa_b200_dense_attention(
+      q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), scratch.data_ptr(),
+      size_t(scratch.numel()), int(q.size(0)), int(q.size(1)), int(q.size(2)), int(k.size(1)),
+      int(k.size(2)), int(q.size(3)), cta_k, q.stride(0), q.stride(1), q.stride(2), k.stride(0),
+      k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2), input_dtype_code,
+      use_midpoint_affine ? 1 : 0, sm_scale, output_dtype_code, o.stride(0), o.stride(2),
+      o.stride(1), is_causal ? 1 : 0, stream_of(stream_ptr)));
+}
+
+size_t quantize_v_workspace_size(int batch, int kv_heads, int k_len, int head_dim) {
+  return risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "B200-native RISA attention kernels (PyTorch C++ extension over librisa_b200.so)";
+  m.attr("fused_gather_version") = 1;
+  m.def("risa_lse_shift", &risa_lse_shift, py::arg("q"), py::arg("k"), py::arg("anchors"),
+        py::arg("out"), py::arg("scale"), py::arg("stream_ptr"));
+  m.def("risa_sdpa_quantize", &risa_sdpa_quantize, py::arg("q"), py::arg("k"), py::arg("v"),
+        py::arg("q_int8"), py::arg("q_scale"), py::arg("k_int8"), py::arg("k_scale"),
+        py::arg("v_int8"), py::arg("v_scale"), py::arg("v_center"), py::arg("cta_k"),
+        py::arg("input_dtype_code"), py::arg("use_midpoint_affine"), py::arg("stream_ptr"),
+        py::arg("anchor_indices_ptr"), py::arg("permutation_ptr") = 0, py::kw_only(),
+        py::arg("q_permutation_ptr") = 0, py::arg("workspace") = py::none());
+  m.def("prepare_key_mask_tiles", &prepare_key_mask_tiles, py::arg("mask"), py::arg("tiles"),
+        py::arg("tile_size"), py::arg("stream_ptr"));
+  m.def("risa_sdpa_prequantized", &risa_sdpa_prequantized, py::arg("q_int8"), py::arg("k_int8"),
+        py::arg("v_int8"), py::arg("o"), py::arg("q_scale"), py::arg("k_scale"),
+        py::arg("v_scale"), py::arg("v_center"), py::arg("cta_k"), py::arg("sm_scale"),
+        py::arg("output_dtype_code"), py::arg("stream_ptr"), py::arg("attn_mask") = py::none(),
+        py::arg("sparse_row_offsets") = py::none(), py::arg("sparse_block_indices") = py::none(),
+        py::arg("block_mass") = py::none(), py::arg("is_causal") = false,
+        py::arg("lse") = py::none(), py::arg("key_mask_tiles") = py::none());
+  m.def("select_retained_mass_csr", &select_retained_mass_csr, py::arg("sorted_mass"),
+        py::arg("descending_indices"), py::arg("counts"), py::arg("support"),
+        py::arg("row_totals"), py::arg("row_offsets"), py::arg("block_indices"),
+        py::arg("summary"), py::arg("scan_workspace"), py::arg("theta"), py::arg("stream_ptr"));
+  m.def("retained_mass_selector_workspace_size", &retained_mass_selector_workspace_size,
+        py::arg("row_count"));
+  m.def("risa_sdpa", &risa_sdpa, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"),
+        py::arg("q_int8"), py::arg("q_scale"), py::arg("k_int8"), py::arg("k_scale"),
+        py::arg("v_int8"), py::arg("v_scale"), py::arg("v_center"), py::arg("sm_scale"),
+        py::arg("input_dtype_code"), py::arg("output_dtype_code"), py::arg("use_midpoint_affine"),
+        py::arg("stream_ptr"), py::arg("anchor_indices_ptr"), py::arg("attn_mask") = py::none(),
+        py::arg("cta_k") = 0, py::arg("is_causal") = false,
+        py::arg("key_mask_tiles") = py::none());
+  m.def("dense_scratch_size", &dense_scratch_size);
+  m.def("risa_dense_attention", &risa_dense_attention);
+  m.def("quantize_v_workspace_size", &quantize_v_workspace_size);
+  m.def("device_status", [] { check(risa_b200_device_status()); });
+  m.def("set_attention_path", [](int path) { return risa_b200_set_attention_path(path); });
+  m.def("bounded_wait_self_test", [](uint64_t limit_ns, uintptr_t stream_ptr) {
+    check(risa_b200_bounded_wait_self_test(limit_ns, stream_of(stream_ptr)));
+  });
+  m.def("abi_version", [] { return risa_b200_abi_version(); });
+}

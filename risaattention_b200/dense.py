@@ -68,9 +68,10 @@ def int8_attention(q, k, v, *, scale=None, attn_mask=None, v_quantization="absma
             fuse_gather=fuse_gather)
         return int8_attention_from_prequantized(packed, return_lse=return_lse)
     affine = uses_centered_values(v_quantization)
-    if not torch.compiler.is_compiling():
-        # eager call: same implementation as the registered operators, without the dispatcher's
-        # per-call cost (the operators stay registered for traced and compiled graphs)
+    if not torch.compiler.is_compiling() and type(q) is torch.Tensor:
+        # eager call on plain tensors: same implementation as the registered operators, without
+        # the dispatcher's per-call cost (traced / compiled graphs and tensor subclasses such as
+        # fake tensors go through the operators and their shape-only implementations)
         return execute_dense_attention(q, k, v, scale=scale, attn_mask=attn_mask,
                                        use_midpoint_affine=affine, is_causal=is_causal)
     if attn_mask is None:

@@ -85,3 +85,32 @@ def test_pattern_properties():
         q_length=256, kv_length=512, query_block_size=128, key_block_size=128,
         attention_scale=0.1, retained_mass_target=0.9, measured_retained_mass=0.95)
     assert p.coverage == 3 / 8 and p.sparsity == 5 / 8 and p.index_bytes == 24
+
+
+def test_fake_tensor_and_operator_schema():
+    """Under fake tensors (what torch.compile traces with) the public call resolves to the
+    registered ``risa_attention::*`` operators, whose shape-only implementations answer without a
+    device (reference tests/contracts/test_risa_attention.py:45-52)."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import risaattention_b200 as risa
+    from risaattention_b200 import dense
+
+    assert dense.OPERATORS_REGISTERED == (True, True)
+    schema = str(torch.ops.risa_attention.int8_attention.default._schema)
+    assert schema == ("risa_attention::int8_attention(Tensor q, Tensor k, Tensor v, float? scale, "
+                      "bool use_midpoint_affine, bool is_causal) -> Tensor")
+    schema = str(torch.ops.risa_attention.int8_attention_masked.default._schema)
+    assert schema == ("risa_attention::int8_attention_masked(Tensor q, Tensor k, Tensor v, "
+                      "Tensor attn_mask, float? scale, bool use_midpoint_affine, bool is_causal) "
+                      "-> Tensor")
+    with FakeTensorMode():
+        q = torch.empty(1, 2, 17, 64, device="cuda")
+        for mode in ("midpoint_affine", "absmax"):
+            out = risa.int8_attention(q, q, q, is_causal=True, v_quantization=mode)
+            assert out.shape == q.shape and out.device == q.device and out.dtype == q.dtype
+        mask = torch.ones(17, 17, dtype=torch.bool, device="cuda")
+        assert risa.int8_attention(q, q, q, attn_mask=mask).shape == q.shape
+    with pytest.raises(ValueError, match="v_quantization"):
+        risa.int8_attention(torch.empty(1), torch.empty(1), torch.empty(1), v_quantization="x")

@@ -172,7 +172,13 @@ def test_key_mask_tiles(ref, dtype):
         tiles = torch.empty(2, 4, -(-lk // tile) + 1, dtype=torch.int32, device="cuda")
         _backend._C.prepare_key_mask_tiles(mask, tiles, tile,
                                            torch.cuda.current_stream().cuda_stream)
-        assert torch.equal(tiles, ref.key_mask_tiles(mask, tile))
+        want = ref.key_mask_tiles(mask, tile)
+        # defined content: the count in the last slot and that many ascending tile ids in front
+        # (what lies between is scratch in both implementations)
+        assert torch.equal(tiles[..., -1], want[..., -1])
+        listed = torch.arange(tiles.shape[-1] - 1, device="cuda") < want[..., -1:]
+        assert torch.equal(tiles[..., :-1][listed], want[..., :-1][listed])
+        assert int(want[0, 1, -1]) == 0  # a fully hidden head lists nothing
 
 
 def test_key_mask_tile_list_attention(ref):

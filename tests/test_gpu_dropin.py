@@ -14,6 +14,13 @@ from risaattention_b200 import _backend  # noqa: E402
 CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
+@pytest.fixture(params=["extension", "ctypes"])
+def native(request):
+    """Both host-side surfaces over the C-ABI: the PyTorch C++ extension (what the package uses)
+    and the ctypes object."""
+    return _backend._C if request.param == "extension" else _backend._ABI
+
+
 def cap(t):
     """What the reference's wrap_for_dlpack produces for an ordinary CUDA tensor."""
     return None if t is None else torch.utils.dlpack.to_dlpack(t)
@@ -37,8 +44,8 @@ def _buffers(q, k, cta_k):
 
 @pytest.mark.parametrize("lk", [700, 2304])
 @pytest.mark.parametrize("causal", [False, True])
-def test_risa_sdpa_called_like_the_reference(lk, causal):
-    C = _backend._C
+def test_risa_sdpa_called_like_the_reference(native, lk, causal):
+    C = native
     g = torch.Generator(device="cuda").manual_seed(lk)
     q = torch.randn(2, 8, 300, 128, device="cuda", generator=g).bfloat16()
     k = torch.randn(2, 2, lk, 128, device="cuda", generator=g).bfloat16()
@@ -66,8 +73,8 @@ def test_risa_sdpa_called_like_the_reference(lk, causal):
                     cap(buf["v_scale"]), cap(buf["v_center"]), 128 ** -0.5, 2, 2, False, stream, 0)
 
 
-def test_masked_sdpa_with_key_mask_tiles_keyword():
-    C = _backend._C
+def test_masked_sdpa_with_key_mask_tiles_keyword(native):
+    C = native
     g = torch.Generator(device="cuda").manual_seed(1)
     q = torch.randn(1, 4, 512, 128, device="cuda", generator=g).half()
     k = torch.randn(1, 2, 2048, 128, device="cuda", generator=g).half()
@@ -88,8 +95,8 @@ def test_masked_sdpa_with_key_mask_tiles_keyword():
     assert torch.equal(out, want)
 
 
-def test_prequantize_attend_construct_reuse_called_like_the_reference():
-    C = _backend._C
+def test_prequantize_attend_construct_reuse_called_like_the_reference(native):
+    C = native
     g = torch.Generator(device="cuda").manual_seed(2)
     q = torch.randn(1, 4, 1000, 128, device="cuda", generator=g).bfloat16()
     k = torch.randn(1, 2, 3000, 128, device="cuda", generator=g).bfloat16() * 0.1 + 3

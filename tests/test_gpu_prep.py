@@ -164,7 +164,7 @@ def test_quantize_v_c_abi_head_dims_outside_the_kernel_set(ref, dim, lk, affine)
                 torch.empty(channels, device="cuda"), torch.empty(channels, device="cuda"))
 
     codes, scale, center = buffers()
-    C = _backend._C
+    C = _backend._ABI
     ws = torch.empty(C.quantize_v_workspace_size(b, hkv, lk, dim), dtype=torch.uint8, device="cuda")
     guard = torch.zeros(4096, dtype=torch.uint8, device="cuda")  # allocated right after the outputs
     C._check(C.lib.risa_b200_quantize_v(

@@ -77,3 +77,46 @@ def test_keyword_names_and_defaults_match_the_reference_module():
         "sm_scale", "output_dtype_code", "stream_ptr", "attn_mask", "sparse_row_offsets",
         "sparse_block_indices", "block_mass", "is_causal", "lse", "key_mask_tiles"]
     assert [p.default for p in pre[12:]] == [None, None, None, None, False, None, None]
+
+
+def _extension_parameters(name):
+    """(parameter names, names that have defaults) of a function of the C++ extension, read from
+    the signature line pybind11 puts at the top of its docstring."""
+    line = getattr(_backend._C, name).__doc__.splitlines()[0]
+    inside = line[line.index("(") + 1:line.rindex(")")]
+    names, defaults, depth, token = [], set(), 0, ""
+    for ch in inside + ",":
+        if ch in "[(":
+            depth += 1
+        elif ch in "])":
+            depth -= 1
+        if ch == "," and depth == 0:
+            token = token.strip()
+            if token and token != "*":
+                name_part = token.split(":")[0].strip()
+                names.append(name_part)
+                if "=" in token:
+                    defaults.add(name_part)
+            token = ""
+        else:
+            token += ch
+    return names, defaults
+
+
+@pytest.mark.parametrize("call", CALLS, ids=lambda c: f"{c['entry_point']}@{c['line']}")
+def test_reference_call_fits_the_cpp_extension(call):
+    """The PyTorch C++ extension takes the same calls: enough positional parameters, every keyword
+    the reference uses present by name, everything the reference leaves out defaulted."""
+    if _backend._C is None:
+        pytest.skip(f"extension not built: {_backend._EXTENSION_ERROR}")
+    names, defaults = _extension_parameters(call["entry_point"])
+    reference = inspect.signature(getattr(_backend._Native, call["entry_point"]))
+    reference_names = [n for n in reference.parameters if n != "self"]
+    assert names == reference_names  # same order and names as the ctypes surface checked above
+    positional = call["positional"] + (STAR_ARGS.get(call["entry_point"], 0)
+                                       if call["star_args"] else 0)
+    used = set(names[:positional]) | set(call["keywords"])
+    if call["star_kwargs"]:
+        assert set(STAR_KWARGS.get(call["entry_point"], [])) <= set(names)
+    assert set(call["keywords"]) <= set(names)
+    assert all(n in defaults for n in names if n not in used)

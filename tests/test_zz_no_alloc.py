@@ -34,7 +34,7 @@ def _call(lib, name, v, padded, affine, workspace=None):
 def test_static_scratch_matches_workspace_entry_point():
     from risaattention_b200 import _backend
 
-    lib = _backend._C.lib
+    lib = _backend._ABI.lib
     limit = lib.risa_b200_quantize_v_static_limit()
     assert limit == 4 << 20
     g = torch.Generator(device="cuda").manual_seed(123)
@@ -54,7 +54,7 @@ def test_static_scratch_matches_workspace_entry_point():
 def test_static_scratch_rejects_oversized_problem():
     from risaattention_b200 import _backend
 
-    lib = _backend._C.lib
+    lib = _backend._ABI.lib
     heads, length = 40, 32768                       # needs ~13 MiB of scratch
     assert lib.risa_b200_quantize_v_workspace_size(1, heads, length, 128) > \
         lib.risa_b200_quantize_v_static_limit()
