@@ -96,6 +96,40 @@ int risa_b200_attention(const void* q, const void* k, const void* v, void* o, co
                         const int32_t* sparse_block_indices, float* block_mass, int is_causal,
                         float* lse, const int32_t* key_mask_tiles, void* stream);
 
+/* Pattern construction inside the dense pass.  Same attention as risa_b200_attention with a
+ * block-mass workspace (same outputs, bit for bit), but instead of writing 8 bytes per (query, key
+ * tile) to a workspace of the reference's layout, sorting the block masses with a library sort and
+ * running a separate selection kernel, every CTA keeps the statistics of its 128 queries in a slot
+ * of `scratch` (one slot per CTA resident at once: 148 x n_k KiB instead of B*Hq*Lq*(2 n_k + 2)
+ * floats), reduces them to the block masses of its query block after its last key tile, orders
+ * them (descending, equal masses by ascending tile id) and closes the retained-mass prefix at
+ * `theta` in the reference's FP64 order.  Replaces, as one launch: launch_attention in capture mode
+ * + the block-mass kernel (csrc/kernels/attention_int8.cuh:51-143,1028-1088), torch.sort and
+ * stage 1 of launch_select_retained_mass (src/risa_attention/sparse.py:18-52,
+ * csrc/kernels/sparse_selection.cu:9-67).  Outputs per CSR row r = (batch, head, query block):
+ * counts[r] kept tiles, bitmaps[r, ceil(n_k/32)] kept tiles as bits, row_totals[r, 2] = kept and
+ * total mass (doubles); block_masses (optional, may be NULL) = f32 [rows, n_k].
+ * risa_b200_pack_selected then turns counts + bitmaps into CSR row offsets and ascending tile ids
+ * and writes summary = {kept mass, total mass, kept tiles} (stages 2-3 of the reference selector,
+ * sparse_selection.cu:69-127).  Limits: tensor-core kernel shapes only, n_k <=
+ * risa_b200_select_max_key_tiles(cta_k); scratch 256-byte aligned, at least
+ * risa_b200_select_scratch_size() bytes; its slot flags are cleared on `stream` by the call. */
+size_t risa_b200_select_scratch_size(int k_len, int cta_k);
+int risa_b200_select_max_key_tiles(int cta_k);
+int risa_b200_attention_select(const void* q, const void* k, const void* v, void* o,
+                               const float* q_scale, const float* k_scale, const float* v_scale,
+                               const float* v_center, const void* mask, int64_t mask_stride_b,
+                               int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+                               int mask_dtype_code, int cta_k, int batch, int q_len, int k_len,
+                               int q_heads, int kv_heads, int head_dim, int64_t o_stride_b,
+                               int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+                               int out_dtype_code, int is_causal, double theta, void* scratch,
+                               size_t scratch_bytes, float* block_masses, int32_t* counts,
+                               uint32_t* bitmaps, double* row_totals, void* stream);
+int risa_b200_pack_selected(const int32_t* counts, const uint32_t* bitmaps,
+                            const double* row_totals, int32_t* row_offsets, int32_t* block_indices,
+                            double* summary, int row_count, int key_blocks, void* stream);
+
 /* One call for the unmasked dense path: quantise Q, K and V into caller-provided scratch and run
  * the attention kernel on it.  Same kernels, same results as risa_b200_quantize_qk +
  * risa_b200_quantize_v + risa_b200_attention issued one after the other on `stream`; it exists so a

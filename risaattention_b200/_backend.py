@@ -44,6 +44,14 @@ _SIGNATURES = {
         c_i32,
         [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
                                                                    c_i32, c_vp, c_vp, c_vp]),
+    "risa_b200_select_scratch_size": (c_sz, [c_i32] * 2),
+    "risa_b200_select_max_key_tiles": (c_i32, [c_i32]),
+    "risa_b200_attention_select": (
+        c_i32,
+        [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_i32, c_f64, c_vp,
+                                                                   c_sz, c_vp, c_vp, c_vp, c_vp,
+                                                                   c_vp]),
+    "risa_b200_pack_selected": (c_i32, [c_vp] * 6 + [c_i32, c_i32, c_vp]),
     "risa_b200_dense_scratch_size": (c_sz, [c_i32] * 7),
     "risa_b200_dense_attention": (
         c_i32, [c_vp] * 5 + [c_sz] + [c_i32] * 7 + [c_i64] * 9 + [c_i32, c_i32, c_f32, c_i32] +
@@ -220,6 +228,37 @@ class _Native:
             cta_k, b, lq, lk, hq, hkv, d, o_b, o_n, o_h, sm_scale, output_dtype_code,
             _ptr(sparse_row_offsets), _ptr(sparse_block_indices), _ptr(block_mass),
             int(is_causal), _ptr(lse), _ptr(key_mask_tiles), stream_ptr))
+
+    # -- pattern construction inside the dense pass (no counterpart in the reference module) ------
+    def select_scratch_size(self, k_len, cta_k) -> int:
+        return int(self.lib.risa_b200_select_scratch_size(k_len, cta_k))
+
+    def select_max_key_tiles(self, cta_k) -> int:
+        return int(self.lib.risa_b200_select_max_key_tiles(cta_k))
+
+    def risa_sdpa_select(self, q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale, v_center,
+                         cta_k, sm_scale, output_dtype_code, stream_ptr, theta, scratch, counts,
+                         bitmaps, row_totals, attn_mask=None, is_causal=False, block_masses=None):
+        b, hq, lq, d = q_int8.shape
+        hkv, lk = k_int8.shape[1], k_int8.shape[2]
+        ms, mask_code = (0, 0, 0, 0), -1
+        if attn_mask is not None:
+            ms, mask_code = attn_mask.stride(), DTYPE_CODES[attn_mask.dtype]
+        o_b = hq * lq * d if b <= 1 else o.stride(0)
+        o_n = d if lq <= 1 else o.stride(2)
+        o_h = lq * d if hq <= 1 else o.stride(1)
+        self._check(self.lib.risa_b200_attention_select(
+            _ptr(q_int8), _ptr(k_int8), _ptr(v_int8), _ptr(o), _ptr(q_scale), _ptr(k_scale),
+            _ptr(v_scale), _ptr(v_center), _ptr(attn_mask), ms[0], ms[1], ms[2], ms[3], mask_code,
+            cta_k, b, lq, lk, hq, hkv, d, o_b, o_n, o_h, sm_scale, output_dtype_code,
+            int(is_causal), float(theta), _ptr(scratch), scratch.numel() * scratch.element_size(),
+            _ptr(block_masses), _ptr(counts), _ptr(bitmaps), _ptr(row_totals), stream_ptr))
+
+    def pack_selected(self, counts, bitmaps, row_totals, row_offsets, block_indices, summary,
+                      key_blocks, stream_ptr):
+        self._check(self.lib.risa_b200_pack_selected(
+            _ptr(counts), _ptr(bitmaps), _ptr(row_totals), _ptr(row_offsets), _ptr(block_indices),
+            _ptr(summary), counts.numel(), key_blocks, stream_ptr))
 
     # -- select_retained_mass_csr (csrc/bindings.cpp, sparse_selection.cu) ----------------------
     def retained_mass_selector_workspace_size(self, row_count: int) -> int:

@@ -80,6 +80,25 @@ def _check_pattern(quantized, pattern):
             raise TypeError("sparse CSR row offsets and block indices must be contiguous int32")
 
 
+def allocate_output(quantized, output_layout):
+    """Output tensor of a packed call: logical [batch, heads, seq, head_dim], stored heads-major
+    ("hnd") or sequence-major ("nhd")."""
+    batch, q_heads, q_len, dim = quantized.q.shape
+    out_dtype = _output_dtype(quantized.input_dtype)
+    device = quantized.q.device
+    if output_layout == "nhd":
+        return torch.empty(batch, q_len, q_heads, dim, dtype=out_dtype,
+                           device=device).permute(0, 2, 1, 3)
+    return torch.empty(batch, q_heads, q_len, dim, dtype=out_dtype, device=device)
+
+
+def finish_output(output, quantized):
+    """Drops head-dim padding and restores FP32 for FP32 callers."""
+    if quantized.original_head_dim != output.shape[-1]:
+        output = output[..., :quantized.original_head_dim]
+    return output.float() if quantized.input_dtype == torch.float32 else output
+
+
 def capture_workspace_elements(quantized) -> int:
     batch, q_heads, q_len, _ = quantized.q.shape
     tiles = math.ceil(quantized.k.shape[2] / quantized.cta_k)
@@ -127,11 +146,7 @@ def int8_attention_from_prequantized(quantized, *, sparse_pattern=None, output_l
 
     batch, q_heads, q_len, dim = quantized.q.shape
     out_dtype = _output_dtype(quantized.input_dtype)
-    if output_layout == "nhd":
-        output = torch.empty(batch, q_len, q_heads, dim, dtype=out_dtype,
-                             device=device).permute(0, 2, 1, 3)
-    else:
-        output = torch.empty(batch, q_heads, q_len, dim, dtype=out_dtype, device=device)
+    output = allocate_output(quantized, output_layout)
     lse = torch.empty((batch, q_heads, q_len), dtype=torch.float32, device=device) \
         if return_lse else None
     tiles = None
@@ -146,10 +161,7 @@ def int8_attention_from_prequantized(quantized, *, sparse_pattern=None, output_l
         sparse_row_offsets=None if sparse_pattern is None else sparse_pattern.row_offsets,
         sparse_block_indices=None if sparse_pattern is None else sparse_pattern.block_indices,
         block_mass=_block_mass, is_causal=quantized.is_causal, lse=lse, key_mask_tiles=tiles)
-    if quantized.original_head_dim != dim:
-        output = output[..., :quantized.original_head_dim]
-    if quantized.input_dtype == torch.float32:
-        output = output.float()
+    output = finish_output(output, quantized)
     if return_lse:
         lse.add_(quantized.lse_shift)
         return output, lse

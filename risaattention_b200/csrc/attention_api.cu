@@ -66,7 +66,20 @@ extern "C" int risa_b200_set_attention_path(int path) {
   return previous;
 }
 
-extern "C" int risa_b200_attention(
+namespace {
+
+// Outputs and scratch of the in-pass pattern construction (risa_b200_attention_select).
+struct SelectRequest {
+  double theta;
+  void* scratch;
+  int slots;
+  float* masses;
+  int32_t* counts;
+  uint32_t* bitmaps;
+  double* totals;
+};
+
+int run_attention(
     const void* q, const void* k, const void* v, void* o, const float* q_scale,
     const float* k_scale, const float* v_scale, const float* v_center, const void* mask,
     int64_t mask_stride_b, int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
@@ -74,7 +87,7 @@ extern "C" int risa_b200_attention(
     int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
     int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
     float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles,
-    void* stream_ptr) {
+    void* stream_ptr, const SelectRequest* select) {
   RISA_REQUIRE(cta_k == 64 || cta_k == 128, "risa_attention: cta_k must be 64 or 128");
   RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
                "risa_attention: unsupported head_dim");
@@ -97,7 +110,7 @@ extern "C" int risa_b200_attention(
                    reinterpret_cast<uintptr_t>(v) % 16 == 0 && reinterpret_cast<uintptr_t>(o) % 4 == 0 &&
                    o_stride_b % 2 == 0 && o_stride_n % 2 == 0 && o_stride_h % 2 == 0,
                "risa_attention: packed operands must be 16-byte aligned and output strides even");
-  AttentionArgs a;
+  AttentionArgs a{};
   a.q = static_cast<const int8_t*>(q);
   a.k = static_cast<const int8_t*>(k);
   a.v = static_cast<const int8_t*>(v);
@@ -134,6 +147,22 @@ extern "C" int risa_b200_attention(
                          ? key_mask_tiles
                          : nullptr;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (select) {
+    RISA_REQUIRE(attention_tc_supported(a),
+                 "attention_select: shape or alignment outside the tensor-core kernel");
+    const int n_k = (k_len + cta_k - 1) / cta_k;
+    RISA_REQUIRE(n_k <= attention_tc_select_max_tiles(cta_k),
+                 "attention_select: at most %d key tiles of %d keys",
+                 attention_tc_select_max_tiles(cta_k), cta_k);
+    a.select_scratch = select->scratch;
+    a.select_slots = select->slots;
+    a.select_theta = select->theta;
+    a.select_masses = select->masses;
+    a.select_counts = select->counts;
+    a.select_bitmaps = select->bitmaps;
+    a.select_totals = select->totals;
+    return attention_tc(a, stream);
+  }
   int status;
   if (g_attention_path == 0 && attention_tc_supported(a))
     status = attention_tc(a, stream);
@@ -146,6 +175,84 @@ extern "C" int risa_b200_attention(
     return check_launch("attention (block mass)");
   }
   return RISA_B200_OK;
+}
+
+// Slots of the selection scratch: one per CTA that can be resident at once (the kernel's shared
+// memory allows one CTA per SM).
+int select_slot_count() {
+  static thread_local int cached_device = -1, cached = 0;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return 0;
+  if (device != cached_device) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+      return 0;
+    cached = sms;
+    cached_device = device;
+  }
+  return cached;
+}
+
+size_t select_flag_bytes(int slots) { return (size_t(slots) * 4 + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" int risa_b200_attention(
+    const void* q, const void* k, const void* v, void* o, const float* q_scale,
+    const float* k_scale, const float* v_scale, const float* v_center, const void* mask,
+    int64_t mask_stride_b, int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+    int mask_dtype_code, int cta_k, int batch, int q_len, int k_len, int q_heads, int kv_heads,
+    int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+    int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
+    float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles,
+    void* stream_ptr) {
+  return run_attention(q, k, v, o, q_scale, k_scale, v_scale, v_center, mask, mask_stride_b,
+                       mask_stride_h, mask_stride_q, mask_stride_k, mask_dtype_code, cta_k, batch,
+                       q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
+                       o_stride_h, sm_scale, out_dtype_code, sparse_row_offsets,
+                       sparse_block_indices, block_mass, is_causal, lse, key_mask_tiles, stream_ptr,
+                       nullptr);
+}
+
+extern "C" size_t risa_b200_select_scratch_size(int k_len, int cta_k) {
+  if (k_len <= 0 || (cta_k != 64 && cta_k != 128)) return 0;
+  const int slots = select_slot_count();
+  const size_t n_k = (size_t(k_len) + cta_k - 1) / cta_k;
+  return slots == 0 ? 0 : select_flag_bytes(slots) + size_t(slots) * n_k * 128 * 8;
+}
+
+extern "C" int risa_b200_select_max_key_tiles(int cta_k) {
+  return (cta_k == 64 || cta_k == 128) ? attention_tc_select_max_tiles(cta_k) : 0;
+}
+
+extern "C" int risa_b200_attention_select(
+    const void* q, const void* k, const void* v, void* o, const float* q_scale,
+    const float* k_scale, const float* v_scale, const float* v_center, const void* mask,
+    int64_t mask_stride_b, int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+    int mask_dtype_code, int cta_k, int batch, int q_len, int k_len, int q_heads, int kv_heads,
+    int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+    int out_dtype_code, int is_causal, double theta, void* scratch, size_t scratch_bytes,
+    float* block_masses, int32_t* counts, uint32_t* bitmaps, double* row_totals,
+    void* stream_ptr) {
+  RISA_REQUIRE(theta > 0.0 && theta <= 1.0, "theta must be finite and in (0, 1]");
+  RISA_REQUIRE(counts && bitmaps && row_totals, "attention_select: null output");
+  const size_t need = risa_b200_select_scratch_size(k_len, cta_k);
+  RISA_REQUIRE(need != 0 && scratch != nullptr && scratch_bytes >= need &&
+                   reinterpret_cast<uintptr_t>(scratch) % 256 == 0,
+               "attention_select: scratch must be 256-byte aligned device memory of at least "
+               "risa_b200_select_scratch_size() = %zu bytes", need);
+  const int slots = select_slot_count();
+  // every slot starts unclaimed (stream-ordered; nothing else of the scratch needs a defined start)
+  cudaError_t e = cudaMemsetAsync(scratch, 0, select_flag_bytes(slots),
+                                  static_cast<cudaStream_t>(stream_ptr));
+  if (e != cudaSuccess)
+    return fail(RISA_B200_CUDA, "attention_select: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  const SelectRequest request{theta, scratch, slots, block_masses, counts, bitmaps, row_totals};
+  return run_attention(q, k, v, o, q_scale, k_scale, v_scale, v_center, mask, mask_stride_b,
+                       mask_stride_h, mask_stride_q, mask_stride_k, mask_dtype_code, cta_k, batch,
+                       q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
+                       o_stride_h, sm_scale, out_dtype_code, nullptr, nullptr, nullptr, is_causal,
+                       nullptr, nullptr, stream_ptr, &request);
 }
 
 // ---- fused dense call: quantise into caller scratch, then attend --------------------------------

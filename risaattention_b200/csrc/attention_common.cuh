@@ -26,6 +26,16 @@ struct AttentionArgs {
   int is_causal;
   float* lse;
   const int32_t* key_mask_tiles;
+  // In-pass pattern construction (tensor-core kernel only; all null / zero otherwise): the CTA keeps
+  // its per-(query, tile) statistics in a slot of `select_scratch`, reduces them to block masses
+  // after its last tile and closes the retained-mass prefix itself.
+  void* select_scratch;      // [slots] int32 claim flags (256-byte aligned block), then the slots
+  int select_slots;          // number of slots (>= CTAs resident at once)
+  double select_theta;
+  float* select_masses;      // optional [B*Hq*n_q, n_k] block masses
+  int32_t* select_counts;    // [B*Hq*n_q] tiles kept per row
+  uint32_t* select_bitmaps;  // [B*Hq*n_q, ceil(n_k / 32)] kept tiles as bits
+  double* select_totals;     // [B*Hq*n_q, 2] kept mass, total mass
 };
 
 // Capture workspace (FP32 words), identical to the reference's (attention_int8.cuh:58-60,
@@ -91,5 +101,6 @@ __device__ __forceinline__ void store_pair(void* p, float a, float b, int out_dt
 int attention_rows(const AttentionArgs& a, cudaStream_t stream);
 bool attention_tc_supported(const AttentionArgs& a);
 int attention_tc(const AttentionArgs& a, cudaStream_t stream);
+int attention_tc_select_max_tiles(int cta_k);
 
 }  // namespace risa_b200

@@ -28,11 +28,13 @@
 // waits for its loads in flight, the rows of the CTA are written as NaN and a device status word
 // records the site; the CTA then exits instead of spinning.
 #include "attention_common.cuh"
+#include "select.cuh"
 #include "tc_ptx.cuh"
 
 #include <climits>
 #include <cuda.h>
 #include <mutex>
+#include <type_traits>
 
 namespace risa_b200 {
 namespace {
@@ -45,6 +47,9 @@ constexpr int kTile = 128 * 128;      // bytes of one 128 x 128 INT8 tile
 constexpr int kThreads = 640;
 constexpr int kSoftmaxGroups = 3;     // softmax warpgroups; tile it is handled by group it % 3
 constexpr int kBuffers = 4;           // tensor-memory accumulator buffers; tile it uses it % 4
+// What a launch produces besides the output: nothing, the reference's capture workspace, or the
+// retained-mass selection of every query block.
+enum Mode : int { kDense = 0, kCapture = 1, kSelect = 2 };
 constexpr int kRegsLaunch = 96;        // what ptxas gives 640 threads (65536 / 640, multiple of 8)
 constexpr int kRegsSoftmax = 96, kRegsCorrection = 168, kRegsIssue = 24;
 // setmaxnreg redistributes the registers the CTA was launched with (threads x launch count); a
@@ -377,10 +382,11 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
-template <bool CAPTURE, int CTA_K, int D>
+template <int MODE, int CTA_K, int D>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
+  constexpr bool CAPTURE = MODE != kDense;  // exact per-tile statistics and denominators
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -605,7 +611,39 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const bool row_ok = row < a.q_len;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     CaptureLayout cap;
-    if constexpr (CAPTURE) cap = capture_layout(a, n_q, n_k);
+    if constexpr (MODE == kCapture) cap = capture_layout(a, n_q, n_k);
+    // In-pass selection: the CTA's (probability sum, tile maximum) pairs go to a slot of the
+    // scratch, [tile][row] so that a warp's stores are one contiguous run.  A slot is claimed by
+    // compare-and-swap on its flag, starting at this SM's number; there are at least as many
+    // slots as CTAs resident at once, so the scan ends, and it is bounded like every other wait.
+    uint2* pairs = nullptr;
+    int claimed = -1;
+    if constexpr (MODE == kSelect) {
+      if (half == 0) {
+        volatile int* slot_word = reinterpret_cast<volatile int*>(smem + L::tmem_slot + 12);
+        if (row_in == 0) {
+          int* flags = static_cast<int*>(a.select_scratch);
+          unsigned int smid;
+          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+          int s = int(smid % unsigned(a.select_slots)), found = -1;
+          for (int tries = 0; tries < 64 * a.select_slots && found < 0; ++tries) {
+            if (atomicCAS(flags + s, 0, 1) == 0) found = s;
+            else s = s + 1 == a.select_slots ? 0 : s + 1;
+          }
+          if (found < 0) {
+            atomicCAS(&g_wait_status, 0u, 501u);
+            asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(gave_up), "r"(501u)
+                         : "memory");
+          }
+          *slot_word = found;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        claimed = *slot_word;
+        const size_t flag_bytes = (size_t(a.select_slots) * 4 + 255) / 256 * 256;
+        pairs = reinterpret_cast<uint2*>(static_cast<char*>(a.select_scratch) + flag_bytes) +
+                size_t(max(claimed, 0)) * n_k * 128 + row_in;
+      }
+    }
     const int64_t grow = bh * a.q_len + row;
     RowState st;
     row_state_init(st);
@@ -613,7 +651,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     uint64_t O2[kOut / 2];
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
-    bool ok = true;
+    bool ok = !(MODE == kSelect && half == 0 && claimed < 0);
     // Software-pipelined by one tile: iteration `it` folds the accumulator of tile it - 1 (whose
     // weights were computed one iteration earlier) and takes the statistics of tile it (running
     // maximum, denominator, weights).  This group is the one strictly sequential stage of the
@@ -659,7 +697,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
             if (last) denominator_chunk<true>(st, ts, c == 0, s4);
             else denominator_chunk<false>(st, ts, c == 0, s4);
           }
-          if (row_ok && half == 0) {
+          if constexpr (MODE == kSelect) {
+            if (half == 0) pairs[size_t(it) * 128] = make_uint2(numer, __float_as_uint(ts.tile_m));
+          } else if (row_ok && half == 0) {
             if (last_iter) {
               float* out = cap.last + grow * 2;
               out[0] = static_cast<float>(numer);
@@ -718,7 +758,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     for (int i = 0; i < kOut / 2; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
     const float denom = CAPTURE ? row_denominator(st) : st.d[0];
     if (ok && row_ok) {
-      if (CAPTURE && half == 0) {
+      if (MODE == kCapture && half == 0) {
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
@@ -760,6 +800,74 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         *reinterpret_cast<uint4*>(o_row + 2 * ch) =
             make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
       if (a.lse && half == 0) a.lse[grow] = __int_as_float(0x7fffffff);
+    }
+    if constexpr (MODE == kSelect) {
+      if (half == 0 && claimed >= 0) {
+        // ---- block masses of this query block, then the retained-mass prefix ------------------
+        // mass[t] = sum over the block's queries of numerator * 2^(tile_max - m_final) / d_final,
+        // summed in the reference's tree (attention_int8.cuh:1067-1086: shift-down inside each
+        // warp, then the four warp sums as (w0 + w2) + (w1 + w3)), because the masses feed an
+        // exact selection.  The rings are idle by now: the capture sums' area is reused.
+        float* s_mass = reinterpret_cast<float*>(smem + L::sums);  // [n_k]
+        float* s_sorted = s_mass + n_k;                            // [n_k] descending
+        float* s_warp = s_sorted + n_k;                            // [4][n_k], then the ranks
+        const int w = warp & 3;
+        const bool live = ok && row_ok;
+#pragma unroll 4
+        for (int t = 0; t < n_k; ++t) {
+          const uint2 pr = pairs[size_t(t) * 128];
+          float mass = 0.0f;
+          if (live)
+            mass = denom > 0.0f ? __uint2float_rn(pr.x) * ex2_approx(__uint_as_float(pr.y) - st.m) /
+                                      denom
+                                : 0.0f;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) mass += __shfl_down_sync(0xffffffffu, mass, off);
+          if (lane == 0) s_warp[w * n_k + t] = mass;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int64_t block_row = bh * n_q + bx;
+        for (int t = row_in; t < n_k; t += 128) {
+          const float mass = __fadd_rn(__fadd_rn(s_warp[t], s_warp[2 * n_k + t]),
+                                       __fadd_rn(s_warp[n_k + t], s_warp[3 * n_k + t]));
+          s_mass[t] = mass;
+          if (a.select_masses) a.select_masses[block_row * n_k + t] = mass;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // descending order by counting: rank = tiles with a larger mass, ties by ascending tile id
+        int* s_rank = reinterpret_cast<int*>(s_warp);
+        for (int t = row_in; t < n_k; t += 128) {
+          const float mine = s_mass[t];
+          int rank = 0;
+          for (int u = 0; u < n_k; ++u) {
+            const float other = s_mass[u];
+            rank += (other > mine || (other == mine && u < t)) ? 1 : 0;
+          }
+          s_sorted[rank] = mine;
+          s_rank[t] = rank;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (w == 0) {
+          const RetainedPrefix kept = retained_prefix(s_sorted, uint32_t(n_k), a.select_theta);
+          const uint32_t words = bitmap_words(uint32_t(n_k));
+          for (uint32_t wd = 0; wd < words; ++wd) {
+            const int t = int(32 * wd) + lane;
+            const uint32_t bits =
+                __ballot_sync(0xffffffffu, t < n_k && uint32_t(s_rank[t]) < kept.count);
+            if (lane == 0) a.select_bitmaps[block_row * words + wd] = bits;
+          }
+          if (lane == 0) {
+            a.select_counts[block_row] = int32_t(kept.count);
+            a.select_totals[block_row * 2] = kept.selected;
+            a.select_totals[block_row * 2 + 1] = kept.total;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (row_in == 0) {
+          __threadfence();
+          atomicExch(static_cast<int*>(a.select_scratch) + claimed, 0);  // slot free again
+        }
+      }
     }
   }
 
@@ -820,10 +928,10 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool CAPTURE, int CTA_K, int D>
+template <int MODE, int CTA_K, int D>
 int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
               const CUtensorMap& map_v, cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<CAPTURE, CTA_K, D>;
+  auto kernel = attention_tc_kernel<MODE, CTA_K, D>;
   static thread_local int configured = -1;  // per instantiation, thread and device
   int device = -1;
   cudaGetDevice(&device);
@@ -882,23 +990,25 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
       !make_map(&map_v, a.v, uint64_t(n_k) * a.cta_k, d, uint64_t(a.batch) * a.kv_heads, 128,
                 v_rows))
     return fail(RISA_B200_CUDA, "attention: tensor map creation failed");
-  const bool capture = a.block_mass != nullptr;
-  if (a.head_dim == 256) {
-    if (a.cta_k == 64)
-      return capture ? launch_tc<true, 64, 256>(a, map_q, map_k, map_v, stream)
-                     : launch_tc<false, 64, 256>(a, map_q, map_k, map_v, stream);
-    return capture ? launch_tc<true, 128, 256>(a, map_q, map_k, map_v, stream)
-                   : launch_tc<false, 128, 256>(a, map_q, map_k, map_v, stream);
-  }
-  if (a.head_dim == 64)
-    return capture ? launch_tc<true, 64, 64>(a, map_q, map_k, map_v, stream)
-                   : launch_tc<false, 64, 64>(a, map_q, map_k, map_v, stream);
-  if (a.cta_k == 64)
-    return capture ? launch_tc<true, 64, 128>(a, map_q, map_k, map_v, stream)
-                   : launch_tc<false, 64, 128>(a, map_q, map_k, map_v, stream);
-  return capture ? launch_tc<true, 128, 128>(a, map_q, map_k, map_v, stream)
-                 : launch_tc<false, 128, 128>(a, map_q, map_k, map_v, stream);
+  const int mode = a.select_scratch ? kSelect : a.block_mass ? kCapture : kDense;
+  auto launch = [&](auto cta_k, auto head_dim) {
+    constexpr int K = decltype(cta_k)::value, HD = decltype(head_dim)::value;
+    if (mode == kSelect) return launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
+    if (mode == kCapture) return launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
+    return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
+  };
+  using std::integral_constant;
+  if (a.head_dim == 256)
+    return a.cta_k == 64 ? launch(integral_constant<int, 64>{}, integral_constant<int, 256>{})
+                         : launch(integral_constant<int, 128>{}, integral_constant<int, 256>{});
+  if (a.head_dim == 64) return launch(integral_constant<int, 64>{}, integral_constant<int, 64>{});
+  return a.cta_k == 64 ? launch(integral_constant<int, 64>{}, integral_constant<int, 128>{})
+                       : launch(integral_constant<int, 128>{}, integral_constant<int, 128>{});
 }
+
+// Largest key-tile count whose masses, sorted copy and per-warp partials fit the shared-memory
+// area the in-pass selection reuses (24 bytes per key tile).
+int attention_tc_select_max_tiles(int cta_k) { return 256 * cta_k / 24; }
 
 }  // namespace risa_b200
 

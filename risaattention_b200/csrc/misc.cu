@@ -311,3 +311,19 @@ extern "C" int risa_b200_select_retained_mass(const float* sorted_mass, const in
       uint64_t(words) * 4);
   return check_launch("select_retained_mass");
 }
+
+extern "C" int risa_b200_pack_selected(const int32_t* counts, const uint32_t* bitmaps,
+                                       const double* row_totals, int32_t* row_offsets,
+                                       int32_t* block_indices, double* summary, int row_count,
+                                       int key_blocks, void* stream_ptr) {
+  RISA_REQUIRE(counts && bitmaps && row_totals && row_offsets && block_indices && summary,
+               "pack_selected: null tensor");
+  RISA_REQUIRE(row_count > 0 && key_blocks > 0, "pack_selected: empty problem");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  offsets_and_summary_kernel<<<1, 256, 0, stream>>>(counts, row_totals, row_offsets, summary,
+                                                    uint32_t(row_count));
+  expand_bitmaps_kernel<<<(row_count + 7) / 8, 256, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(bitmaps), row_offsets, block_indices, uint32_t(row_count),
+      uint32_t(key_blocks), uint64_t(bitmap_words(uint32_t(key_blocks))) * 4);
+  return check_launch("pack_selected");
+}

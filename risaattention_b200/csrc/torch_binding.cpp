@@ -292,6 +292,50 @@ void risa_dense_attention(const at::Tensor& q, const at::Tensor& k, const at::Te
       o.stride(1), is_causal ? 1 : 0, stream_of(stream_ptr)));
 }
 
+void risa_sdpa_select(const at::Tensor& q_int8, const at::Tensor& k_int8, const at::Tensor& v_int8,
+                      const at::Tensor& o, const at::Tensor& q_scale, const at::Tensor& k_scale,
+                      const at::Tensor& v_scale, const at::Tensor& v_center, int cta_k,
+                      float sm_scale, int output_dtype_code, uintptr_t stream_ptr, double theta,
+                      const at::Tensor& scratch, const at::Tensor& counts,
+                      const at::Tensor& bitmaps, const at::Tensor& row_totals,
+                      std::optional<at::Tensor> attn_mask, bool is_causal,
+                      std::optional<at::Tensor> block_masses) {
+  const int64_t b = q_int8.size(0), hq = q_int8.size(1), lq = q_int8.size(2), d = q_int8.size(3);
+  const int64_t hkv = k_int8.size(1), lk = k_int8.size(2);
+  int64_t ms[4] = {0, 0, 0, 0};
+  int mask_code = -1;
+  const void* mask_ptr = nullptr;
+  if (attn_mask.has_value()) {
+    mask_code = dtype_code(*attn_mask);
+    mask_ptr = attn_mask->data_ptr();
+    for (int i = 0; i < 4; ++i) ms[i] = attn_mask->stride(i);
+  }
+  const int64_t o_b = b <= 1 ? hq * lq * d : o.stride(0);
+  const int64_t o_n = lq <= 1 ? d : o.stride(2);
+  const int64_t o_h = hq <= 1 ? lq * d : o.stride(1);
+  check(risa_b200_attention_select(
+      q_int8.data_ptr(), k_int8.data_ptr(), v_int8.data_ptr(), o.data_ptr(),
+      q_scale.data_ptr<float>(), k_scale.data_ptr<float>(), v_scale.data_ptr<float>(),
+      v_center.data_ptr<float>(), mask_ptr, ms[0], ms[1], ms[2], ms[3], mask_code, cta_k, int(b),
+      int(lq), int(lk), int(hq), int(hkv), int(d), o_b, o_n, o_h, sm_scale, output_dtype_code,
+      is_causal ? 1 : 0, theta, scratch.data_ptr(), size_t(scratch.numel()) * scratch.element_size(),
+      block_masses.has_value() ? block_masses->data_ptr<float>() : nullptr,
+      static_cast<int32_t*>(counts.data_ptr()), static_cast<uint32_t*>(bitmaps.data_ptr()),
+      row_totals.data_ptr<double>(), stream_of(stream_ptr)));
+}
+
+void pack_selected(const at::Tensor& counts, const at::Tensor& bitmaps,
+                   const at::Tensor& row_totals, const at::Tensor& row_offsets,
+                   const at::Tensor& block_indices, const at::Tensor& summary, int key_blocks,
+                   uintptr_t stream_ptr) {
+  check(risa_b200_pack_selected(
+      static_cast<const int32_t*>(counts.data_ptr()),
+      static_cast<const uint32_t*>(bitmaps.data_ptr()), row_totals.data_ptr<double>(),
+      static_cast<int32_t*>(row_offsets.data_ptr()),
+      static_cast<int32_t*>(block_indices.data_ptr()), summary.data_ptr<double>(),
+      int(counts.numel()), key_blocks, stream_of(stream_ptr)));
+}
+
 size_t quantize_v_workspace_size(int batch, int kv_heads, int k_len, int head_dim) {
   return risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim);
 }
@@ -334,6 +378,17 @@ PYBIND11_MODULE(_C, m) {
   m.def("dense_scratch_size", &dense_scratch_size);
   m.def("risa_dense_attention", &risa_dense_attention);
   m.def("quantize_v_workspace_size", &quantize_v_workspace_size);
+  m.def("select_scratch_size",
+        [](int k_len, int cta_k) { return risa_b200_select_scratch_size(k_len, cta_k); });
+  m.def("select_max_key_tiles", [](int cta_k) { return risa_b200_select_max_key_tiles(cta_k); });
+  m.def("risa_sdpa_select", &risa_sdpa_select, py::arg("q_int8"), py::arg("k_int8"),
+        py::arg("v_int8"), py::arg("o"), py::arg("q_scale"), py::arg("k_scale"),
+        py::arg("v_scale"), py::arg("v_center"), py::arg("cta_k"), py::arg("sm_scale"),
+        py::arg("output_dtype_code"), py::arg("stream_ptr"), py::arg("theta"), py::arg("scratch"),
+        py::arg("counts"), py::arg("bitmaps"), py::arg("row_totals"),
+        py::arg("attn_mask") = py::none(), py::arg("is_causal") = false,
+        py::arg("block_masses") = py::none());
+  m.def("pack_selected", &pack_selected);
   m.def("device_status", [] { check(risa_b200_device_status()); });
   m.def("set_attention_path", [](int path) { return risa_b200_set_attention_path(path); });
   m.def("bounded_wait_self_test", [](uint64_t limit_ns, uintptr_t stream_ptr) {

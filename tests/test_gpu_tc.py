@@ -265,3 +265,88 @@ def test_tc_head_dim_256_capture_bit_exact(ref, cta_k, causal):
     _status()
     assert torch.equal(got["workspace"].view(torch.int32), want["workspace"].view(torch.int32))
     assert torch.equal(got["out"], want["out"])
+
+
+SELECT_SHAPES = [
+    # d, lq, lk, hq, hkv, batch, cta_k
+    (128, 300, 1153, 4, 2, 1, 128),
+    (128, 137, 2049, 2, 1, 2, 128),
+    (128, 260, 1000, 4, 4, 1, 64),
+    (64, 200, 700, 2, 1, 1, 64),
+    (256, 130, 1100, 2, 2, 1, 128),
+    (256, 137, 263, 2, 1, 1, 64),
+    (128, 1000, 4096, 4, 4, 1, 128),
+]
+
+
+@pytest.mark.parametrize("shape", SELECT_SHAPES)
+@pytest.mark.parametrize("variant", ["plain", "causal", "key_bias"])
+def test_in_pass_selection_bit_exact(ref, shape, variant):
+    """Pattern construction inside the attention launch: block masses, kept-tile sets, counts and
+    the attention output itself are the reference's (capture workspace -> block-mass kernel ->
+    torch.sort -> selector) bit for bit, for several thresholds including theta = 1."""
+    from risaattention_b200 import _backend
+    from tests.test_gpu_attention import _masks
+
+    d, lq, lk, hq, hkv, b, cta_k = shape
+    _, _, _, pk = _packed(ref, d, lq, lk, hq, hkv, cta_k, seed=11 + lk, b=b)
+    causal = variant == "causal"
+    mask = _masks("key_bias", b, hq, lq, lk) if variant == "key_bias" else None
+    scale = d ** -0.5
+    want = ref.attention(pk, sm_scale=scale, mask=mask, is_causal=causal, capture=True)
+    n_q, n_k = -(-lq // 128), -(-lk // cta_k)
+    rows, words = b * hq * n_q, -(-n_k // 32)
+    want_masses = want["workspace"][: rows * n_k].view(rows, n_k)
+    C = _backend._C
+    assert n_k <= C.select_max_key_tiles(cta_k)
+    stream = torch.cuda.current_stream().cuda_stream
+    for theta in (0.5, 0.9, 0.99, 1.0):
+        out = torch.empty(b, hq, lq, d, dtype=torch.bfloat16, device="cuda")
+        counts = torch.empty(rows, dtype=torch.int32, device="cuda")
+        bitmaps = torch.empty(rows, words, dtype=torch.int32, device="cuda")
+        totals = torch.empty(rows, 2, dtype=torch.float64, device="cuda")
+        masses = torch.empty(rows, n_k, device="cuda")
+        scratch = torch.empty(C.select_scratch_size(lk, cta_k), dtype=torch.uint8, device="cuda")
+        C.risa_sdpa_select(pk["q"], pk["k"], pk["v"], out, pk["q_scale"], pk["k_scale"],
+                           pk["v_scale"], pk["v_center"], cta_k, scale, 2, stream, theta, scratch,
+                           counts, bitmaps, totals, attn_mask=mask, is_causal=causal,
+                           block_masses=masses)
+        offsets = torch.empty(rows + 1, dtype=torch.int32, device="cuda")
+        storage = torch.empty(rows * n_k, dtype=torch.int32, device="cuda")
+        summary = torch.empty(3, dtype=torch.float64, device="cuda")
+        C.pack_selected(counts, bitmaps, totals, offsets, storage, summary, n_k, stream)
+        torch.cuda.synchronize()
+        _status()
+        if variant == "key_bias":
+            # masked scores may differ from the reference's in the last FP32 bit (its compiler
+            # fuses score * scale + bias per instantiation): masses to 1e-4, selection against
+            # this library's own capture path instead
+            torch.testing.assert_close(masses, want_masses, rtol=0, atol=1e-4)
+            own = _ours(pk, sm_scale=scale, path=0, mask=mask, is_causal=causal, capture=True)
+            base = own["workspace"][: rows * n_k].view(rows, n_k)
+            assert torch.equal(masses, base)
+            assert torch.equal(out, own["out"])
+        else:
+            base = want_masses
+            assert torch.equal(masses, want_masses)
+            assert torch.equal(out, want["out"])
+        rro, rbi, rmeasured = ref.select_retained_mass(base, theta)
+        kept = int(summary[2])
+        assert torch.equal(offsets, rro) and torch.equal(storage[:kept], rbi)
+        assert abs(float(summary[0]) / max(float(summary[1]), 1e-20) - rmeasured) < 1e-12
+        assert torch.equal(counts, rro[1:] - rro[:-1])
+
+
+def test_in_pass_selection_orders_equal_masses_by_tile_id(ref):
+    """Equal block masses (constant keys: every tile of a row weighs the same) are kept in
+    ascending tile order, so the kept set is the first `count` tiles; the count itself is the
+    reference selector's."""
+    import risaattention_b200 as risa
+
+    q = torch.randn(1, 2, 256, 128, device="cuda").bfloat16()
+    k = torch.ones(1, 1, 2048, 128, device="cuda").bfloat16()
+    v = torch.randn(1, 1, 2048, 128, device="cuda").bfloat16()
+    _, pattern = risa.construct_sparse_int8_attention(q, k, v, theta=0.5)
+    counts = (pattern.row_offsets[1:] - pattern.row_offsets[:-1]).tolist()
+    assert counts == [8] * 4
+    assert pattern.block_indices.view(4, 8).tolist() == [list(range(8))] * 4
