@@ -536,7 +536,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     }
   } else if (wg < kSoftmaxGroups) {
     // ------------------------------------------------------------------ softmax of tiles it = wg, wg+3, ...
+    // every group must end up at its constant: a group left at the launch count while another one
+    // grows would over-subscribe the pool (see the static_assert above)
     if constexpr (kRegsSoftmax > kRegsLaunch) regs_inc<kRegsSoftmax>();
+    else if constexpr (kRegsSoftmax < kRegsLaunch) regs_dec<kRegsSoftmax>();
     const int b = wg;                      // first tile of this group
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
@@ -652,81 +655,32 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = !(MODE == kSelect && half == 0 && claimed < 0);
-    // Software-pipelined by one tile: iteration `it` folds the accumulator of tile it - 1 (whose
-    // weights were computed one iteration earlier) and takes the statistics of tile it (running
-    // maximum, denominator, weights).  This group is the one strictly sequential stage of the
-    // kernel, so its per-tile latency sets the pace: both events are waited for together, the
-    // first accumulator chunk is requested at once, and the statistics -- a short chain of
-    // dependent FP32 operations -- are worked out while that chunk travels.
+    // Software-pipelined by one tile: iteration `it` first folds the accumulator of tile it - 1
+    // (whose weights were computed one iteration earlier) and hands its buffer back, then takes the
+    // statistics of tile it (running maximum, denominator, weights); the fold must not wait for the
+    // next tile's probabilities, or every accumulator buffer would be held one tile longer.  The
+    // statistics slot is handed back as soon as it has been read, and without capture the
+    // statistics are a single exponential: denominator and output row are both kept in units of a
+    // stale maximum m_o that is only moved when the true maximum has run ahead of it by 2^8, so
+    // d = d * f + sum * 2^(tile_m - m_o) and O = O * f + PV * 2^(tile_m - m_o) share weight and
+    // (rare) rescale factor f, and their quotient needs no correction at the end.
     float prev_o_scale = 1.0f, prev_w = 0.0f;
-    float m_o = -INFINITY;  // maximum the FP32 output rows are scaled to (dense path only)
+    float m_o = -INFINITY;  // maximum the dense path's denominator and output rows are scaled to
     for (int it = 0; it <= seq.n_iter && ok; ++it) {
       const bool fold = it >= 1, take = it < seq.n_iter;
       const int j = it - 1;
       const int ob = j & (kBuffers - 1);
       const int slot = it % L::kSlots;
       const uint32_t tmem_o = tmem + 128 * ob;
-      if (fold && take)
-        ok = mbar_wait2(bar(Bars::OFULL + ob), (j / kBuffers) & 1, bar(Bars::PFULL + slot),
-                        (it / L::kSlots) & 1, gave_up, 401);
-      else if (fold)
-        ok = mbar_wait(bar(Bars::OFULL + ob), (j / kBuffers) & 1, gave_up, 401);
-      else
-        ok = mbar_wait(bar(Bars::PFULL + slot), (it / L::kSlots) & 1, gave_up, 402);
-      if (!ok) break;
-      uint32_t acc[16];
-      if (fold) {
-        tc_fence_after();
-        tmem_load16(tmem_o + lane_base, acc);
-      }
       float cur_o_scale = 1.0f, cur_w = 0.0f;
-      if (take) {
-        const bool last_iter = it == seq.n_iter - 1;
-        const bool last = CAPTURE && seq.last_rules(it, seq.tile(it));
-        const float2 stat = stats[slot * 128 + row_in];
-        const uint32_t numer = __float_as_uint(stat.y);
-        const TileScales ts = tile_begin(st, stat.x);
-        cur_o_scale = ts.o_scale;
-        cur_w = ts.w;
-        if constexpr (CAPTURE) {
-          const uint16_t* s16 = sums + (slot * 128 + row_in) * (CTA_K / 4);
-#pragma unroll
-          for (int c = 0; c < CTA_K / 32; ++c) {
-            uint16_t s4[8];
-            *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
-            if (last) denominator_chunk<true>(st, ts, c == 0, s4);
-            else denominator_chunk<false>(st, ts, c == 0, s4);
-          }
-          if constexpr (MODE == kSelect) {
-            if (half == 0) pairs[size_t(it) * 128] = make_uint2(numer, __float_as_uint(ts.tile_m));
-          } else if (row_ok && half == 0) {
-            if (last_iter) {
-              float* out = cap.last + grow * 2;
-              out[0] = static_cast<float>(numer);
-              out[1] = ts.tile_m;
-            } else {
-              uint32_t* out = cap.full + (grow * (n_k - 1) + it) * 2;
-              out[0] = numer;
-              out[1] = __float_as_uint(ts.tile_m);
-            }
-          }
-        } else {
-          denominator_single(st, ts, numer);
-          // the output rows follow a stale maximum that is only moved when the true one has run
-          // ahead by 2^8: almost no tile then needs the accumulated row rescaled
-          float factor = 1.0f;
-          if (st.m > m_o + 8.0f) {
-            factor = ex2_approx(m_o - st.m);
-            m_o = st.m;
-          }
-          cur_o_scale = factor;
-          cur_w = ex2_approx(stat.x - m_o);
-        }
-        mbar_arrive(bar(Bars::STATFREE + slot));
-      }
       if (fold) {
+        ok = mbar_wait(bar(Bars::OFULL + ob), (j / kBuffers) & 1, gave_up, 401);
+        if (!ok) break;
+        tc_fence_after();
         const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
         const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
+        uint32_t acc[16];
+        tmem_load16(tmem_o + lane_base, acc);
 #pragma unroll
         for (int c = 0; c < kOut / 16; ++c) {
           tmem_load_wait();
@@ -750,6 +704,50 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
         }
       }
+      if (take) {
+        ok = mbar_wait(bar(Bars::PFULL + slot), (it / L::kSlots) & 1, gave_up, 402);
+        if (!ok) break;
+        const float2 stat = stats[slot * 128 + row_in];
+        const uint32_t numer = __float_as_uint(stat.y);
+        if constexpr (CAPTURE) {
+          const bool last_iter = it == seq.n_iter - 1;
+          const bool last = seq.last_rules(it, seq.tile(it));
+          const TileScales ts = tile_begin(st, stat.x);
+          cur_o_scale = ts.o_scale;
+          cur_w = ts.w;
+          const uint16_t* s16 = sums + (slot * 128 + row_in) * (CTA_K / 4);
+#pragma unroll
+          for (int c = 0; c < CTA_K / 32; ++c) {
+            uint16_t s4[8];
+            *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
+            if (last) denominator_chunk<true>(st, ts, c == 0, s4);
+            else denominator_chunk<false>(st, ts, c == 0, s4);
+          }
+          mbar_arrive(bar(Bars::STATFREE + slot));
+          if constexpr (MODE == kSelect) {
+            if (half == 0) pairs[size_t(it) * 128] = make_uint2(numer, __float_as_uint(ts.tile_m));
+          } else if (row_ok && half == 0) {
+            if (last_iter) {
+              float* out = cap.last + grow * 2;
+              out[0] = static_cast<float>(numer);
+              out[1] = ts.tile_m;
+            } else {
+              uint32_t* out = cap.full + (grow * (n_k - 1) + it) * 2;
+              out[0] = numer;
+              out[1] = __float_as_uint(ts.tile_m);
+            }
+          }
+        } else {
+          mbar_arrive(bar(Bars::STATFREE + slot));
+          st.m = fmaxf(st.m, stat.x);
+          if (st.m > m_o + 8.0f) {
+            cur_o_scale = ex2_approx(m_o - st.m);
+            m_o = st.m;
+          }
+          cur_w = ex2_approx(stat.x - m_o);
+          st.d[0] = fmaf(static_cast<float>(numer), cur_w, st.d[0] * cur_o_scale);
+        }
+      }
       prev_o_scale = cur_o_scale;
       prev_w = cur_w;
     }
@@ -762,8 +760,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
-      // dense path: bring the rows from the stale maximum to the final one together with 1 / d
-      const float inv = CAPTURE ? rcp_approx(denom) : rcp_approx(denom) * ex2_approx(m_o - st.m);
+      // dense path: denominator and rows share the stale maximum's units, the quotient is exact
+      const float inv = rcp_approx(denom);
       const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
       const float* vs = a.v_scale + kvh * D + kOut * half;
       const float* vc = a.v_center + kvh * D + kOut * half;
@@ -789,7 +787,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         *reinterpret_cast<uint4*>(o_row + 2 * ch) =
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      if (a.lse && half == 0) a.lse[grow] = row_lse(denom, st.m);
+      // the LSE wants the denominator's own reference point: the stale maximum without capture
+      if (a.lse && half == 0) a.lse[grow] = row_lse(denom, CAPTURE ? st.m : m_o);
     } else if (row_ok) {
       // a wait of this CTA expired: mark the rows it owns, so that a failed launch cannot be taken
       // for a result (NaN in both 16-bit output formats, NaN LSE)

@@ -53,14 +53,15 @@ __device__ __forceinline__ void tile_max_init(TileMax& t) {
   t.g[0] = t.g[1] = t.g[2] = t.g[3] = init;
 }
 
-// x: 32 consecutive key columns starting at a multiple of 32.  For kScoresInt they are exact
-// integers (tail keys already replaced by -1e30 in the last tile), for kScoresScaled they are in
-// the log2 domain with masked entries at -inf.
+// x: NCOL (32 or 16) consecutive key columns starting at a multiple of NCOL.  For kScoresInt they
+// are exact integers (tail keys already replaced by -1e30 in the last tile), for kScoresScaled they
+// are in the log2 domain with masked entries at -inf.
+template <int NCOL = 32>
 __device__ __forceinline__ void tile_max_chunk(const float* x, TileMax& t) {
 #pragma unroll
   for (int g = 0; g < 4; ++g)
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < NCOL / 16; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) t.g[g] = fmaxf(t.g[g], x[lane_column(j, g, e)]);
 }
@@ -98,22 +99,23 @@ __device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
   return s;
 }
 
-// Probabilities of one 32-key chunk.  P receives 8 packed words in storage order (word 4j+g = lane
-// g of 16-key group j), numer accumulates their U8 sum, s4 (optional) receives the sum of each word.
+// Probabilities of one chunk of NCOL (32 or 16) keys.  P receives NCOL / 4 packed words in storage
+// order (word 4j+g = lane g of 16-key group j), numer accumulates their U8 sum, s4 (optional)
+// receives the sum of each word.
 // U8 codes: adding 2^23 to a probability in [0, 255.5) rounds it to nearest-even into the low
 // mantissa byte (the same integers cvt.rni.sat.u8 gives on this range) and three byte permutes pack
 // four of them, which keeps the conversion off the half-rate conversion pipe.  The work is written
 // stage by stage over all 32 columns (scale, exponential, round, pack) so that 32 independent
 // operations are in flight per stage instead of one dependent chain per word.
-template <int KIND, bool WANT_SUMS>
+template <int KIND, bool WANT_SUMS, int NCOL = 32>
 __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
                                                uint32_t* P, uint32_t& numer, uint32_t* s4) {
   // Columns 2k and 2k + 1 share a K scale group, so scale and magic add run as packed FP32 pairs
   // (one instruction for two columns, same per-lane rounding as the scalar form).
-  float p[32];
+  float p[NCOL];
   const uint64_t nm2 = pack_f32x2(neg_m, neg_m);
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
+  for (int i = 0; i < NCOL; i += 2) {
     const uint64_t x2 = pack_f32x2(x[i], x[i + 1]);
     uint64_t r;
     if (KIND == kScoresScaled) {
@@ -125,18 +127,18 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
     unpack_f32x2(r, p[i], p[i + 1]);
   }
 #pragma unroll
-  for (int i = 0; i < 32; ++i) p[i] = ex2_approx(p[i]);
-  uint32_t u[32];
+  for (int i = 0; i < NCOL; ++i) p[i] = ex2_approx(p[i]);
+  uint32_t u[NCOL];
   const uint64_t magic2 = pack_f32x2(8388608.0f, 8388608.0f);
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
+  for (int i = 0; i < NCOL; i += 2) {
     float a, b;
     unpack_f32x2(add_f32x2(pack_f32x2(p[i], p[i + 1]), magic2), a, b);
     u[i] = __float_as_uint(a);
     u[i + 1] = __float_as_uint(b);
   }
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < NCOL / 16; ++j) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       const uint32_t lo = __byte_perm(u[lane_column(j, g, 0)], u[lane_column(j, g, 1)], 0x0040);
@@ -146,7 +148,7 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
   }
   uint32_t odd = 0;  // second partial sum: two short dependent chains instead of one
 #pragma unroll
-  for (int w = 0; w < 8; ++w) {
+  for (int w = 0; w < NCOL / 4; ++w) {
     if constexpr (WANT_SUMS) {
       s4[w] = __dp4a(P[w], 0x01010101u, 0u);
       numer += s4[w];
