@@ -62,6 +62,10 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
 // measured fastest (one copy leaves the loads too little to hide behind, four copies fall out of the
 // instruction cache next to the other roles' code).
 constexpr int kExpUnroll = 2;
+#ifndef RISA_EXP_POLY_PAIRS
+#define RISA_EXP_POLY_PAIRS 0
+#endif
+constexpr int kExpPolyPairs = RISA_EXP_POLY_PAIRS;  // of every four column pairs, on the FP32 pipes
 constexpr unsigned int kSelfTestSite = 900;  // site number reported by the bounded-wait self test
 
 // Per head_dim and key-tile width: what one CTA holds and how deep its rings are.  head_dim 256 is
@@ -219,7 +223,9 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     }
     if (c > 0) tmem_load32(tmem_row + 32 * (c - 1), raw);
     uint32_t P[8], s4[8];
-    tile_exp_chunk<KIND, CAPTURE>(x, sc, neg_m, P, numer, s4);
+    // without capture the codes are not observable one by one: part of the exponentials moves to
+    // the FP32 pipes (kExpPolyPairs of every four column pairs)
+    tile_exp_chunk<KIND, CAPTURE, 32, CAPTURE ? 0 : kExpPolyPairs>(x, sc, neg_m, P, numer, s4);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
@@ -655,66 +661,34 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = !(MODE == kSelect && half == 0 && claimed < 0);
-    // Software-pipelined by one tile: iteration `it` first folds the accumulator of tile it - 1
-    // (whose weights were computed one iteration earlier) and hands its buffer back, then takes the
-    // statistics of tile it (running maximum, denominator, weights); the fold must not wait for the
-    // next tile's probabilities, or every accumulator buffer would be held one tile longer.  The
-    // statistics slot is handed back as soon as it has been read, and without capture the
-    // statistics are a single exponential: denominator and output row are both kept in units of a
-    // stale maximum m_o that is only moved when the true maximum has run ahead of it by 2^8, so
+    // One iteration per tile and one barrier round trip per iteration: a finished accumulator
+    // (OFULL) implies that the tile's probabilities and statistics were published before (P.V is
+    // only issued after them), so the statistics need no wait of their own.  This group is the one
+    // strictly sequential stage of the kernel and every barrier round trip costs a few hundred
+    // cycles even when the phase is long complete, so its per-tile chain is: wait, statistics
+    // (running maximum, denominator, weights), read-back and fold.  Without capture the statistics
+    // are a single exponential: denominator and output row are both kept in units of a stale
+    // maximum m_o that is only moved when the true maximum has run ahead of it by 2^8, so
     // d = d * f + sum * 2^(tile_m - m_o) and O = O * f + PV * 2^(tile_m - m_o) share weight and
     // (rare) rescale factor f, and their quotient needs no correction at the end.
-    float prev_o_scale = 1.0f, prev_w = 0.0f;
     float m_o = -INFINITY;  // maximum the dense path's denominator and output rows are scaled to
-    for (int it = 0; it <= seq.n_iter && ok; ++it) {
-      const bool fold = it >= 1, take = it < seq.n_iter;
-      const int j = it - 1;
-      const int ob = j & (kBuffers - 1);
+    for (int it = 0; it < seq.n_iter && ok; ++it) {
+      const int ob = it & (kBuffers - 1);
       const int slot = it % L::kSlots;
       const uint32_t tmem_o = tmem + 128 * ob;
-      float cur_o_scale = 1.0f, cur_w = 0.0f;
-      if (fold) {
-        ok = mbar_wait(bar(Bars::OFULL + ob), (j / kBuffers) & 1, gave_up, 401);
-        if (!ok) break;
-        tc_fence_after();
-        const bool rescale = __any_sync(0xffffffffu, prev_o_scale != 1.0f);
-        const uint64_t w2 = pack_f32x2(prev_w, prev_w), s2 = pack_f32x2(prev_o_scale, prev_o_scale);
-        uint32_t acc[16];
-        tmem_load16(tmem_o + lane_base, acc);
-#pragma unroll
-        for (int c = 0; c < kOut / 16; ++c) {
-          tmem_load_wait();
-          tmem_regs_ready<16>(acc);
-          uint64_t f2[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
-                               static_cast<float>(int(acc[2 * i + 1])));
-          if (c < kOut / 16 - 1) {
-            tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
-          } else {
-            tc_fence_before();
-            mbar_arrive(bar(Bars::BUFFREE + ob));  // Q.K^T of tile j + 4 may take the buffer
-          }
-          if (rescale) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
-        }
-      }
-      if (take) {
-        ok = mbar_wait(bar(Bars::PFULL + slot), (it / L::kSlots) & 1, gave_up, 402);
-        if (!ok) break;
+      ok = mbar_wait(bar(Bars::OFULL + ob), (it / kBuffers) & 1, gave_up, 401);
+      if (!ok) break;
+      tc_fence_after();
+      float o_scale = 1.0f, w = 0.0f;
+      {
         const float2 stat = stats[slot * 128 + row_in];
         const uint32_t numer = __float_as_uint(stat.y);
         if constexpr (CAPTURE) {
           const bool last_iter = it == seq.n_iter - 1;
           const bool last = seq.last_rules(it, seq.tile(it));
           const TileScales ts = tile_begin(st, stat.x);
-          cur_o_scale = ts.o_scale;
-          cur_w = ts.w;
+          o_scale = ts.o_scale;
+          w = ts.w;
           const uint16_t* s16 = sums + (slot * 128 + row_in) * (CTA_K / 4);
 #pragma unroll
           for (int c = 0; c < CTA_K / 32; ++c) {
@@ -741,15 +715,39 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           mbar_arrive(bar(Bars::STATFREE + slot));
           st.m = fmaxf(st.m, stat.x);
           if (st.m > m_o + 8.0f) {
-            cur_o_scale = ex2_approx(m_o - st.m);
+            o_scale = ex2_approx(m_o - st.m);
             m_o = st.m;
           }
-          cur_w = ex2_approx(stat.x - m_o);
-          st.d[0] = fmaf(static_cast<float>(numer), cur_w, st.d[0] * cur_o_scale);
+          w = ex2_approx(stat.x - m_o);
+          st.d[0] = fmaf(static_cast<float>(numer), w, st.d[0] * o_scale);
         }
       }
-      prev_o_scale = cur_o_scale;
-      prev_w = cur_w;
+      const bool rescale = __any_sync(0xffffffffu, o_scale != 1.0f);
+      const uint64_t w2 = pack_f32x2(w, w), s2 = pack_f32x2(o_scale, o_scale);
+      uint32_t acc[16];
+      tmem_load16(tmem_o + lane_base, acc);
+#pragma unroll
+      for (int c = 0; c < kOut / 16; ++c) {
+        tmem_load_wait();
+        tmem_regs_ready<16>(acc);
+        uint64_t f2[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          f2[i] = pack_f32x2(static_cast<float>(int(acc[2 * i])),
+                             static_cast<float>(int(acc[2 * i + 1])));
+        if (c < kOut / 16 - 1) {
+          tmem_load16(tmem_o + lane_base + 16 * (c + 1), acc);
+        } else {
+          tc_fence_before();
+          mbar_arrive(bar(Bars::BUFFREE + ob));  // Q.K^T of tile it + 4 may take the buffer
+        }
+        if (rescale) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) O2[8 * c + i] = mul_f32x2(O2[8 * c + i], s2);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) O2[8 * c + i] = fma_f32x2(f2[i], w2, O2[8 * c + i]);
+      }
     }
     float O[kOut];
 #pragma unroll
