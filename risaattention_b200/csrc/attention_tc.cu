@@ -98,8 +98,9 @@ struct SmemLayout {
   static constexpr int stats = p + kSlots * kTile;         // float2 [slots][128]: tile max, U8 sum
   static constexpr int sums = stats + 4 * 128 * 8;         // uint16 [slots][128][CTA_K / 4] (capture)
   static constexpr int mask_stage = sums + 4 * 128 * (CTA_K / 2);
-  static constexpr int bars = mask_stage + kMaskStageBytes;  // 8-byte mbarriers
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 6 * 4 + 3;  // a few spare
+  static constexpr int rowstate = mask_stage + kMaskStageBytes;  // float [5][128]: m, d[4] (capture)
+  static constexpr int bars = rowstate + 5 * 128 * 4;      // 8-byte mbarriers
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 7 * 4 + 3;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int gave_up = tmem_slot + 8;            // site of the first expired wait, or 0
   static constexpr int total = tmem_slot + 16;
@@ -152,7 +153,7 @@ struct Bars {
   static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
                        VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages,
                        BUFFREE = SFULL + kBuffers, PFULL = BUFFREE + kBuffers, PFREE = PFULL + 4,
-                       OFULL = PFREE + 4, STATFREE = OFULL + kBuffers;
+                       OFULL = PFREE + 4, STATFREE = OFULL + kBuffers, WFULL = STATFREE + 4;
   // Tensor memory is four accumulator buffers of 128 columns; tile it owns buffer it % 4 for its
   // whole life: Q.K^T writes the scores there (SFULL), the softmax group reads them, P.V then
   // overwrites the same columns with the tile's integer output (OFULL) and the correction group
@@ -249,26 +250,35 @@ __device__ __forceinline__ void mask_block_rows(const AttentionArgs& a, int batc
                                                 uint32_t (&vals)[32]) {
   constexpr uint32_t kMasked = 0x7fc00000u;
   const int kv = kv0 + lane;
-  const bool kv_ok = kv < a.k_len;
-  const int64_t base = int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
-                       int64_t(kv) * a.mask_stride_k;
-  const int code = a.mask_dtype_code;
+  // rows of this block that exist, for a lane whose key exists (0 otherwise: nothing to load)
+  const int rows = kv < a.k_len ? min(32, a.q_len - row0) : 0;
+  const int esize = a.mask_dtype_code == 3 ? 1 : a.mask_dtype_code == 0 ? 4 : 2;
+  const char* ptr = static_cast<const char*>(a.mask) +
+                    (int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
+                     int64_t(row0) * a.mask_stride_q + int64_t(kv) * a.mask_stride_k) * esize;
+  const int64_t step = a.mask_stride_q * esize;
+  // one loop per element type, so that the body is a load, a conversion and a store
+  auto fill = [&](auto convert) {
 #pragma unroll 8
-  for (int r = 0; r < 32; ++r) {
-    const int row = row0 + r;
-    uint32_t bits = kMasked;
-    if (kv_ok && row < a.q_len) {
-      const int64_t off = base + int64_t(row) * a.mask_stride_q;
-      if (code == 3)
-        bits = static_cast<const uint8_t*>(a.mask)[off] != 0 ? 0u : kMasked;
-      else if (code == 0)
-        bits = static_cast<const uint32_t*>(a.mask)[off];
-      else if (code == 1)
-        bits = __float_as_uint(__half2float(static_cast<const __half*>(a.mask)[off]));
-      else
-        bits = uint32_t(static_cast<const uint16_t*>(a.mask)[off]) << 16;
+    for (int r = 0; r < 32; ++r) {
+      stage[r * 33 + lane] = r < rows ? convert(ptr) : kMasked;
+      ptr += step;
     }
-    stage[r * 33 + lane] = bits;
+  };
+  switch (a.mask_dtype_code) {
+    case 3:
+      fill([](const char* q) { return *reinterpret_cast<const uint8_t*>(q) != 0 ? 0u : kMasked; });
+      break;
+    case 0:
+      fill([](const char* q) { return *reinterpret_cast<const uint32_t*>(q); });
+      break;
+    case 1:
+      fill([](const char* q) {
+        return __float_as_uint(__half2float(*reinterpret_cast<const __half*>(q)));
+      });
+      break;
+    default:
+      fill([](const char* q) { return uint32_t(*reinterpret_cast<const uint16_t*>(q)) << 16; });
   }
   __syncwarp();
 #pragma unroll
@@ -429,6 +439,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       mbar_init(bar(Bars::STATFREE + i), 128);
       mbar_init(bar(Bars::PFULL + i), 128);
       mbar_init(bar(Bars::PFREE + i), 1);
+      mbar_init(bar(Bars::WFULL + i), 128);
     }
     mbar_init_fence();
   }
@@ -562,6 +573,36 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     if constexpr (L::kMaskStageBytes > 0)
       mask_stage = reinterpret_cast<uint32_t*>(smem + L::mask_stage) + warp * L::kMaskStageWords;
     bool ok = true;
+    float* rowstate = reinterpret_cast<float*>(smem + L::rowstate);
+    CaptureLayout cap;
+    if constexpr (MODE == kCapture) cap = capture_layout(a, n_q, n_k);
+    uint2* pairs = nullptr;
+    if constexpr (MODE == kSelect) {
+      // The CTA's (probability sum, tile maximum) pairs go to a slot of the scratch, [tile][row] so
+      // that a warp's stores are one contiguous run.  A slot is claimed by compare-and-swap on its
+      // flag, starting at this SM's number; there are at least as many slots as CTAs resident at
+      // once, so the scan ends, and it is bounded like every other wait.  The first group claims
+      // (its tile 0 comes before everybody else's statistics).
+      if (b == 0 && half == 0) {
+        if (row_in == 0) {
+          int* flags = static_cast<int*>(a.select_scratch);
+          unsigned int smid;
+          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+          int s = int(smid % unsigned(a.select_slots)), found = -1;
+          for (int tries = 0; tries < 64 * a.select_slots && found < 0; ++tries) {
+            if (atomicCAS(flags + s, 0, 1) == 0) found = s;
+            else s = s + 1 == a.select_slots ? 0 : s + 1;
+          }
+          if (found < 0) {
+            atomicCAS(&g_wait_status, 0u, 501u);
+            asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(gave_up), "r"(501u)
+                         : "memory");
+          }
+          *reinterpret_cast<volatile int*>(smem + L::tmem_slot + 12) = found;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+    }
     float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
     if (b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
         seq.ids == nullptr)
@@ -611,6 +652,65 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(bar(Bars::PFULL + slot));
+      if constexpr (CAPTURE) {
+        // With capture every tile needs the reference's exact running maximum and four denominator
+        // partials per row (they decide block masses and tile sets bit for bit): a strictly
+        // sequential chain over the tiles, but a short one.  It depends on the tile's probability
+        // sums only, so the thread that produced them advances the row's state -- kept in shared
+        // memory, handed from tile to tile: WFULL of tile it - 1 is the permission for tile it --
+        // while P.V runs, leaves the tile's weights (w, o_scale) for the correction group in the
+        // statistics slot, and writes the per-tile pair to the capture workspace or, for in-pass
+        // selection, to the CTA's slot of the scratch.
+        RowState st;
+        if (it == 0) {
+          row_state_init(st);
+        } else {
+          const int before = (it - 1) % L::kSlots;
+          ok = mbar_wait(bar(Bars::WFULL + before), ((it - 1) / L::kSlots) & 1, gave_up, 303);
+          if (!ok) break;
+          st.m = rowstate[row_in];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) st.d[i] = rowstate[128 * (1 + i) + row_in];
+        }
+        const float2 mine = *stat;  // (tile maximum, probability sum), written above
+        const uint32_t numer = __float_as_uint(mine.y);
+        const TileScales ts = tile_begin(st, mine.x);
+#pragma unroll
+        for (int c = 0; c < CTA_K / 32; ++c) {
+          uint16_t s4[8];
+          *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(my_sums + 8 * c);
+          if (last) denominator_chunk<true>(st, ts, c == 0, s4);
+          else denominator_chunk<false>(st, ts, c == 0, s4);
+        }
+        rowstate[row_in] = st.m;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rowstate[128 * (1 + i) + row_in] = st.d[i];
+        *stat = make_float2(ts.w, ts.o_scale);
+        if (half == 0) {
+          if constexpr (MODE == kSelect) {
+            if (pairs == nullptr) {
+              const int claimed = *reinterpret_cast<volatile int*>(smem + L::tmem_slot + 12);
+              if (claimed < 0) break;  // no slot: the claimer has raised the give-up word
+              const size_t flag_bytes = (size_t(a.select_slots) * 4 + 255) / 256 * 256;
+              pairs = reinterpret_cast<uint2*>(static_cast<char*>(a.select_scratch) + flag_bytes) +
+                      size_t(claimed) * n_k * 128 + row_in;
+            }
+            pairs[size_t(it) * 128] = make_uint2(numer, __float_as_uint(ts.tile_m));
+          } else if (row_ok) {
+            const int64_t grow = bh * a.q_len + row;
+            if (it == seq.n_iter - 1) {
+              float* out = cap.last + grow * 2;
+              out[0] = static_cast<float>(numer);
+              out[1] = ts.tile_m;
+            } else {
+              uint32_t* out = cap.full + (grow * (n_k - 1) + it) * 2;
+              out[0] = numer;
+              out[1] = __float_as_uint(ts.tile_m);
+            }
+          }
+        }
+        mbar_arrive(bar(Bars::WFULL + slot));
+      }
     }
   } else {
     // ------------------------------------------------------------------ correction + epilogue
@@ -619,40 +719,6 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int row = bx * 128 + row_in;
     const bool row_ok = row < a.q_len;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    CaptureLayout cap;
-    if constexpr (MODE == kCapture) cap = capture_layout(a, n_q, n_k);
-    // In-pass selection: the CTA's (probability sum, tile maximum) pairs go to a slot of the
-    // scratch, [tile][row] so that a warp's stores are one contiguous run.  A slot is claimed by
-    // compare-and-swap on its flag, starting at this SM's number; there are at least as many
-    // slots as CTAs resident at once, so the scan ends, and it is bounded like every other wait.
-    uint2* pairs = nullptr;
-    int claimed = -1;
-    if constexpr (MODE == kSelect) {
-      if (half == 0) {
-        volatile int* slot_word = reinterpret_cast<volatile int*>(smem + L::tmem_slot + 12);
-        if (row_in == 0) {
-          int* flags = static_cast<int*>(a.select_scratch);
-          unsigned int smid;
-          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-          int s = int(smid % unsigned(a.select_slots)), found = -1;
-          for (int tries = 0; tries < 64 * a.select_slots && found < 0; ++tries) {
-            if (atomicCAS(flags + s, 0, 1) == 0) found = s;
-            else s = s + 1 == a.select_slots ? 0 : s + 1;
-          }
-          if (found < 0) {
-            atomicCAS(&g_wait_status, 0u, 501u);
-            asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(gave_up), "r"(501u)
-                         : "memory");
-          }
-          *slot_word = found;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        claimed = *slot_word;
-        const size_t flag_bytes = (size_t(a.select_slots) * 4 + 255) / 256 * 256;
-        pairs = reinterpret_cast<uint2*>(static_cast<char*>(a.select_scratch) + flag_bytes) +
-                size_t(max(claimed, 0)) * n_k * 128 + row_in;
-      }
-    }
     const int64_t grow = bh * a.q_len + row;
     RowState st;
     row_state_init(st);
@@ -660,7 +726,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     uint64_t O2[kOut / 2];
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
-    bool ok = !(MODE == kSelect && half == 0 && claimed < 0);
+    bool ok = true;
     // One iteration per tile and one barrier round trip per iteration: a finished accumulator
     // (OFULL) implies that the tile's probabilities and statistics were published before (P.V is
     // only issued after them), so the statistics need no wait of their own.  This group is the one
@@ -676,51 +742,30 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const int ob = it & (kBuffers - 1);
       const int slot = it % L::kSlots;
       const uint32_t tmem_o = tmem + 128 * ob;
-      ok = mbar_wait(bar(Bars::OFULL + ob), (it / kBuffers) & 1, gave_up, 401);
-      if (!ok) break;
-      tc_fence_after();
       float o_scale = 1.0f, w = 0.0f;
-      {
+      if constexpr (CAPTURE) {
+        // the statistics warp has replaced the tile's (maximum, sum) by its weights
+        ok = mbar_wait2(bar(Bars::OFULL + ob), (it / kBuffers) & 1, bar(Bars::WFULL + slot),
+                        (it / L::kSlots) & 1, gave_up, 401);
+        if (!ok) break;
+        tc_fence_after();
+        const float2 wf = stats[slot * 128 + row_in];
+        w = wf.x;
+        o_scale = wf.y;
+        mbar_arrive(bar(Bars::STATFREE + slot));
+      } else {
+        ok = mbar_wait(bar(Bars::OFULL + ob), (it / kBuffers) & 1, gave_up, 401);
+        if (!ok) break;
+        tc_fence_after();
         const float2 stat = stats[slot * 128 + row_in];
-        const uint32_t numer = __float_as_uint(stat.y);
-        if constexpr (CAPTURE) {
-          const bool last_iter = it == seq.n_iter - 1;
-          const bool last = seq.last_rules(it, seq.tile(it));
-          const TileScales ts = tile_begin(st, stat.x);
-          o_scale = ts.o_scale;
-          w = ts.w;
-          const uint16_t* s16 = sums + (slot * 128 + row_in) * (CTA_K / 4);
-#pragma unroll
-          for (int c = 0; c < CTA_K / 32; ++c) {
-            uint16_t s4[8];
-            *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(s16 + 8 * c);
-            if (last) denominator_chunk<true>(st, ts, c == 0, s4);
-            else denominator_chunk<false>(st, ts, c == 0, s4);
-          }
-          mbar_arrive(bar(Bars::STATFREE + slot));
-          if constexpr (MODE == kSelect) {
-            if (half == 0) pairs[size_t(it) * 128] = make_uint2(numer, __float_as_uint(ts.tile_m));
-          } else if (row_ok && half == 0) {
-            if (last_iter) {
-              float* out = cap.last + grow * 2;
-              out[0] = static_cast<float>(numer);
-              out[1] = ts.tile_m;
-            } else {
-              uint32_t* out = cap.full + (grow * (n_k - 1) + it) * 2;
-              out[0] = numer;
-              out[1] = __float_as_uint(ts.tile_m);
-            }
-          }
-        } else {
-          mbar_arrive(bar(Bars::STATFREE + slot));
-          st.m = fmaxf(st.m, stat.x);
-          if (st.m > m_o + 8.0f) {
-            o_scale = ex2_approx(m_o - st.m);
-            m_o = st.m;
-          }
-          w = ex2_approx(stat.x - m_o);
-          st.d[0] = fmaf(static_cast<float>(numer), w, st.d[0] * o_scale);
+        mbar_arrive(bar(Bars::STATFREE + slot));
+        st.m = fmaxf(st.m, stat.x);
+        if (st.m > m_o + 8.0f) {
+          o_scale = ex2_approx(m_o - st.m);
+          m_o = st.m;
         }
+        w = ex2_approx(stat.x - m_o);
+        st.d[0] = fmaf(static_cast<float>(__float_as_uint(stat.y)), w, st.d[0] * o_scale);
       }
       const bool rescale = __any_sync(0xffffffffu, o_scale != 1.0f);
       const uint64_t w2 = pack_f32x2(w, w), s2 = pack_f32x2(o_scale, o_scale);
@@ -752,9 +797,29 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     float O[kOut];
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) unpack_f32x2(O2[i], O[2 * i], O[2 * i + 1]);
-    const float denom = CAPTURE ? row_denominator(st) : st.d[0];
+    int claimed = -1;
+    uint2* pairs = nullptr;
+    if constexpr (CAPTURE) {
+      // final (maximum, four denominator partials) of the row: the state the softmax threads
+      // handed from tile to tile (the last tile's WFULL was waited for above)
+      const float* rowstate = reinterpret_cast<const float*>(smem + L::rowstate);
+      st.m = rowstate[row_in];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st.d[i] = rowstate[128 * (1 + i) + row_in];
+      st.d[0] = row_denominator(st);
+      if constexpr (MODE == kSelect) {
+        if (half == 0) {
+          claimed = *reinterpret_cast<volatile int*>(smem + L::tmem_slot + 12);
+          const size_t flag_bytes = (size_t(a.select_slots) * 4 + 255) / 256 * 256;
+          pairs = reinterpret_cast<uint2*>(static_cast<char*>(a.select_scratch) + flag_bytes) +
+                  size_t(max(claimed, 0)) * n_k * 128 + row_in;
+        }
+      }
+    }
+    const float denom = st.d[0];
     if (ok && row_ok) {
       if (MODE == kCapture && half == 0) {
+        const CaptureLayout cap = capture_layout(a, n_q, n_k);
         cap.state[grow * 2] = st.m;
         cap.state[grow * 2 + 1] = denom;
       }
@@ -945,12 +1010,11 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
     e = cudaFuncGetAttributes(&attr, kernel);
     if (e != cudaSuccess)
       return fail(RISA_B200_CUDA, "attention: cudaFuncGetAttributes: %s", cudaGetErrorString(e));
-    if (attr.numRegs * kThreads <
-        128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue))
+    constexpr int kPool = 128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue);
+    if (attr.numRegs * kThreads < kPool)
       return fail(RISA_B200_CUDA,
                   "attention: kernel was compiled with %d registers per thread, the warp roles "
-                  "need a pool of %d", attr.numRegs,
-                  128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssue) / kThreads);
+                  "need a pool of %d", attr.numRegs, kPool / kThreads);
     configured = device;
   }
   const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D, CTA_K>::kHalves, a.batch);
