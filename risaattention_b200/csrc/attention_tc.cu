@@ -239,6 +239,54 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
+// The same block with 16-byte accesses, for masks whose keys are contiguous and whose rows start on
+// 16-byte boundaries (checked by the caller): a row of the block is 32 * ESIZE bytes = LPR chunks of
+// 16 bytes, so one warp-wide request covers 32 / LPR rows, and the block travels through the
+// staging area as 16-byte chunks.  Chunk j of row r is stored at position j ^ f(r) of its row, f
+// chosen per row width so that both the stores (lanes = chunks of a few rows) and the loads (lanes
+// = rows, same chunk) touch every bank once per quarter warp.
+template <int ESIZE>
+__device__ __forceinline__ void mask_block_rows_vec(const AttentionArgs& a, const char* block,
+                                                    int64_t row_step_bytes, uint32_t* stage,
+                                                    int lane, uint32_t (&vals)[32]) {
+  constexpr int LPR = 2 * ESIZE;   // 16-byte chunks per row: 8 (FP32), 4 (FP16 / BF16), 2 (bool)
+  constexpr int RPI = 32 / LPR;    // rows per warp-wide request
+  constexpr uint32_t kMasked = 0x7fc00000u;
+  auto fold = [](int r) { return LPR == 8 ? (r & 7) : LPR == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1); };
+  uint4* stage16 = reinterpret_cast<uint4*>(stage);
+  const int j = lane % LPR, sub = lane / LPR;
+#pragma unroll
+  for (int i = 0; i < 32 / RPI; ++i) {
+    const int r = i * RPI + sub;
+    stage16[r * LPR + (j ^ fold(r))] =
+        __ldg(reinterpret_cast<const uint4*>(block + r * row_step_bytes + 16 * j));
+  }
+  __syncwarp();
+  uint32_t words[4 * LPR];
+#pragma unroll
+  for (int c = 0; c < LPR; ++c) {
+    const uint4 v = stage16[lane * LPR + (c ^ fold(lane))];
+    words[4 * c] = v.x;
+    words[4 * c + 1] = v.y;
+    words[4 * c + 2] = v.z;
+    words[4 * c + 3] = v.w;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    if constexpr (ESIZE == 4) {
+      vals[i] = words[i];
+    } else if constexpr (ESIZE == 2) {
+      const uint32_t half_bits = (words[i >> 1] >> (16 * (i & 1))) & 0xffffu;
+      vals[i] = a.mask_dtype_code == 2
+                    ? half_bits << 16
+                    : __float_as_uint(__half2float(__ushort_as_half(static_cast<unsigned short>(half_bits))));
+    } else {
+      vals[i] = ((words[i >> 2] >> (8 * (i & 3))) & 0xffu) != 0 ? 0u : kMasked;
+    }
+  }
+}
+
 // Mask values of a block of 32 query rows x 32 keys, fetched by the warp that owns the rows: for
 // every row the 32 lanes read 32 consecutive keys (one coalesced request per row instead of one
 // strided request per lane), the block is turned around through the warp's shared staging area
@@ -249,6 +297,21 @@ __device__ __forceinline__ void mask_block_rows(const AttentionArgs& a, int batc
                                                 int row0, int kv0, uint32_t* stage, int lane,
                                                 uint32_t (&vals)[32]) {
   constexpr uint32_t kMasked = 0x7fc00000u;
+  {
+    // whole block inside the mask, contiguous keys, 16-byte aligned rows: vector form
+    const int esize_v = a.mask_dtype_code == 3 ? 1 : a.mask_dtype_code == 0 ? 4 : 2;
+    const char* block = static_cast<const char*>(a.mask) +
+                        (int64_t(batch) * a.mask_stride_b + int64_t(head) * a.mask_stride_h +
+                         int64_t(row0) * a.mask_stride_q + int64_t(kv0)) * esize_v;
+    const int64_t row_step = a.mask_stride_q * esize_v;
+    if (a.mask_stride_k == 1 && kv0 + 32 <= a.k_len && row0 + 32 <= a.q_len &&
+        (reinterpret_cast<uintptr_t>(block) | uintptr_t(row_step)) % 16 == 0) {
+      if (esize_v == 4) mask_block_rows_vec<4>(a, block, row_step, stage, lane, vals);
+      else if (esize_v == 2) mask_block_rows_vec<2>(a, block, row_step, stage, lane, vals);
+      else mask_block_rows_vec<1>(a, block, row_step, stage, lane, vals);
+      return;
+    }
+  }
   const int kv = kv0 + lane;
   // rows of this block that exist, for a lane whose key exists (0 otherwise: nothing to load)
   const int rows = kv < a.k_len ? min(32, a.q_len - row0) : 0;

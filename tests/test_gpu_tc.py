@@ -350,3 +350,31 @@ def test_in_pass_selection_orders_equal_masses_by_tile_id(ref):
     counts = (pattern.row_offsets[1:] - pattern.row_offsets[:-1]).tolist()
     assert counts == [8] * 4
     assert pattern.block_indices.view(4, 8).tolist() == [list(range(8))] * 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.bool])
+@pytest.mark.parametrize("offset", [0, 3])
+def test_per_query_mask_staging_forms(ref, dtype, offset):
+    """Per-query masks of every element type, with rows that start on 16-byte boundaries (vector
+    staging) and rows that do not (element-wise staging), against the reference's kernels."""
+    from tests.test_gpu_attention import _packed
+
+    lq, lk, hq, hkv = 256, 1024, 4, 2
+    _, _, _, pk = _packed(ref, 128, lq, lk, hq, hkv, 64, affine=True, seed=91)
+    g = torch.Generator(device="cuda").manual_seed(92)
+    storage = torch.empty(1, hq, lq, lk + 16, device="cuda", dtype=dtype)
+    mask = storage[..., offset:offset + lk]
+    if dtype == torch.bool:
+        mask.copy_(torch.rand(1, hq, lq, lk, device="cuda", generator=g) > 0.3)
+        mask[:, :, 5] = False
+    else:
+        mask.copy_(torch.randn(1, hq, lq, lk, device="cuda", generator=g))
+        mask[:, :, :, 7::11] = float("-inf")
+    for causal in (False, True):
+        want = ref.attention(pk, sm_scale=128 ** -0.5, mask=mask, is_causal=causal, want_lse=True)
+        got = _ours(pk, sm_scale=128 ** -0.5, path=0, mask=mask, is_causal=causal, want_lse=True)
+        _status()
+        assert_outputs_match(got["out"], want["out"], TOL)
+        assert torch.equal(torch.isneginf(got["lse"]), torch.isneginf(want["lse"]))
+        fin = torch.isfinite(want["lse"])
+        torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0, atol=5e-4)
