@@ -511,6 +511,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + L::tmem_slot);
+  // everything above needs no result of the kernels before this one; everything below does
+  chain_wait();
 
   const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE);
   float2* stats = reinterpret_cast<float2*>(smem + L::stats);
@@ -1081,7 +1083,8 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
     configured = device;
   }
   const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D, CTA_K>::kHalves, a.batch);
-  kernel<<<grid, kThreads, SmemLayout<D, CTA_K>::bytes, stream>>>(map_q, map_k, map_v, a);
+  launch_chained(kernel, grid, dim3(kThreads), SmemLayout<D, CTA_K>::bytes, stream, map_q, map_k, map_v,
+                 a);
   return check_launch("attention (tensor-core kernel)");
 }
 

@@ -128,6 +128,36 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
 
 #endif
 
+
+// ---- chained launches ---------------------------------------------------------------------------
+// The kernels of one call form a chain in which each needs the results of the one before.  They are
+// launched with programmatic stream serialisation: a kernel's CTAs may be placed on the SMs while
+// the previous kernel drains, and wait at chain_wait() until that kernel has completed and its
+// writes are visible; chain_release() lets the next kernel's CTAs be placed as soon as every CTA of
+// this one has started.  Every kernel launched through launch_chained() must call chain_wait()
+// before its first global memory access, which also keeps the chain ordered transitively.
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+#endif
+
 #define RISA_DISPATCH_FLOAT(code, T, ...)                 \
   do {                                                    \
     if ((code) == 0) { using T = float; __VA_ARGS__; }    \

@@ -104,6 +104,8 @@ __global__ __launch_bounds__(256) void quantize_q_kernel(
     const T* __restrict__ q, int8_t* __restrict__ codes, float* __restrict__ scales, int q_len,
     int q_heads, int scales_per_head, int64_t stride_b, int64_t stride_h, int64_t stride_n,
     const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   constexpr int LPR = D / 16;                       // lanes per row
   constexpr int GROUP_ROWS = D == 256 ? 2 : 4;      // rows per scale group
   constexpr int GLANES = GROUP_ROWS * LPR;          // lanes per group (16 or 32)
@@ -164,6 +166,8 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
     const T* __restrict__ k, int8_t* __restrict__ codes, float* __restrict__ scales,
     const int32_t* __restrict__ anchors, int k_len, int kv_heads, int scales_per_head,
     int64_t stride_b, int64_t stride_h, int64_t stride_n, const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   constexpr int LPR = D / 16;
   constexpr int RPP = 32 / LPR;                 // rows per warp pass
   constexpr int THREADS = k_threads(D, CTA_K);  // at most 64 values per lane
@@ -244,6 +248,8 @@ __global__ __launch_bounds__(128) void detect_anchor_kernel(const T* __restrict_
                                                             int64_t stride_b, int64_t stride_h,
                                                             int64_t stride_n,
                                                             const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   constexpr int S = 9;
   __shared__ float smp[S * 256];
   __shared__ float w_energy[4], w_max[4], w_dist[S][4], w_benergy[4], w_bmax[4];
@@ -347,7 +353,7 @@ void launch_q(const void* q, void* codes, float* scales, int batch, int heads, i
               int64_t sb, int64_t sh, int64_t sn, const int32_t* perm, cudaStream_t stream) {
   const int blocks = (q_len + 127) / 128;
   const int per_head = blocks * (D == 256 ? 64 : 32);
-  quantize_q_kernel<T, D, ROT><<<dim3(blocks, heads, batch), 256, 0, stream>>>(
+  launch_chained(quantize_q_kernel<T, D, ROT>, dim3(blocks, heads, batch), dim3(256), 0, stream,
       static_cast<const T*>(q), static_cast<int8_t*>(codes), scales, q_len, heads, per_head, sb,
       sh, sn, perm);
 }
@@ -357,8 +363,8 @@ void launch_k(const void* k, void* codes, float* scales, const int32_t* anchors,
               int heads, int k_len, int64_t sb, int64_t sh, int64_t sn, const int32_t* perm,
               cudaStream_t stream) {
   const int tiles = (k_len + CTA_K - 1) / CTA_K;
-  quantize_k_kernel<T, D, CTA_K, ROT><<<dim3(tiles, heads, batch), k_threads(D, CTA_K), 0, stream>>>(
-      static_cast<const T*>(k), static_cast<int8_t*>(codes), scales, anchors, k_len, heads,
+  launch_chained(quantize_k_kernel<T, D, CTA_K, ROT>, dim3(tiles, heads, batch),
+                 dim3(k_threads(D, CTA_K)), 0, stream, static_cast<const T*>(k), static_cast<int8_t*>(codes), scales, anchors, k_len, heads,
       tiles * 4, sb, sh, sn, perm);
 }
 
@@ -421,7 +427,7 @@ extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scal
                        kv_heads, k_len, cta_k, st, q_perm, k_perm, stream)
   const bool h4_only = k_len <= 256;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    detect_anchor_kernel<T><<<dim3(kv_heads, batch), 128, 0, stream>>>(
+    launch_chained(detect_anchor_kernel<T>, dim3(kv_heads, batch), dim3(128), 0, stream,
         static_cast<const T*>(k), anchors, k_len, head_dim, kv_heads, k_stride_b, k_stride_h,
         k_stride_n, k_perm);
     if (head_dim == 64) {

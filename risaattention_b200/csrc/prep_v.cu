@@ -44,6 +44,8 @@ __global__ __launch_bounds__(256) void v_range_kernel(const T* __restrict__ v,
                                                       int64_t stride_b, int64_t stride_h,
                                                       int64_t stride_n,
                                                       const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   __shared__ float s_mn[256][9], s_mx[256][9];
   const int groups = head_dim / 8;            // 8, 16 or 32 threads per token row
   const int tokens_per_step = 256 / groups;
@@ -95,6 +97,8 @@ __global__ __launch_bounds__(kSlotsPerCta) void v_quantize_kernel(
     float* __restrict__ residuals, int k_len, int padded_len, int kv_heads, int head_dim,
     int chunks, int slots, int64_t stride_b, int64_t stride_h, int64_t stride_n,
     const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   __shared__ float s_inv[8], s_center[8];
   const int d_tiles = head_dim / 8;
   const int d_tile = blockIdx.y % d_tiles, bh = blockIdx.y / d_tiles;
@@ -182,6 +186,8 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
     float* __restrict__ residuals, int k_len, int padded_len, int kv_heads, int head_dim,
     int chunks, int slots, int64_t stride_b, int64_t stride_h, int64_t stride_n,
     const int32_t* __restrict__ perm) {
+  chain_wait();
+  chain_release();
   __shared__ float s_inv[kTiledChannels], s_center[kTiledChannels];
   // 32 positions per channel; a row pitch of 36 bytes (9 words) spreads the 16 channel quads of a
   // half-warp over 8 banks (any pitch that is a multiple of 16 bytes would put them on 2)
@@ -310,6 +316,8 @@ __global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
 __global__ void v_center_kernel(const float* __restrict__ residuals,
                                 const float2* __restrict__ ranges, float* __restrict__ center_out,
                                 int k_len, int head_dim, int chunks, int slots) {
+  chain_wait();
+  chain_release();
   __shared__ float warp_sum[16];
   const int channel = blockIdx.x;
   float r = residuals[static_cast<int64_t>(channel) * slots + threadIdx.x];
@@ -399,7 +407,7 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
   float* residuals = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.range_bytes);
   const int channels = batch * kv_heads * head_dim;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    v_range_kernel<T><<<dim3(p.chunks, kv_heads, batch), 256, 0, stream>>>(
+    launch_chained(v_range_kernel<T>, dim3(p.chunks, kv_heads, batch), dim3(256), 0, stream,
         static_cast<const T*>(v), ranges, k_len, head_dim, kv_heads, p.chunks, stride_b, stride_h,
         stride_n, perm);
     const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
@@ -409,26 +417,26 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
     const bool tiled = k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0 &&
                        head_dim % kTiledChannels == 0;
     if (tiled && midpoint_affine) {
-      v_quantize_tiled_kernel<T, true><<<tiled_grid, kTiledThreads, 0, stream>>>(
+      launch_chained(v_quantize_tiled_kernel<T, true>, tiled_grid, dim3(kTiledThreads), 0, stream,
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
           residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
           stride_n, perm);
-      v_center_kernel<<<channels, p.slots, 0, stream>>>(residuals, ranges, v_center, k_len,
-                                                        head_dim, p.chunks, p.slots);
+      launch_chained(v_center_kernel, dim3(channels), dim3(p.slots), 0, stream, residuals, ranges,
+                     v_center, k_len, head_dim, p.chunks, p.slots);
     } else if (tiled) {
-      v_quantize_tiled_kernel<T, false><<<tiled_grid, kTiledThreads, 0, stream>>>(
+      launch_chained(v_quantize_tiled_kernel<T, false>, tiled_grid, dim3(kTiledThreads), 0, stream,
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
           residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
           stride_n, perm);
     } else if (midpoint_affine) {
-      v_quantize_kernel<T, true><<<grid, kSlotsPerCta, 0, stream>>>(
+      launch_chained(v_quantize_kernel<T, true>, grid, dim3(kSlotsPerCta), 0, stream,
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
           residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
           stride_n, perm);
-      v_center_kernel<<<channels, p.slots, 0, stream>>>(residuals, ranges, v_center, k_len,
-                                                        head_dim, p.chunks, p.slots);
+      launch_chained(v_center_kernel, dim3(channels), dim3(p.slots), 0, stream, residuals, ranges,
+                     v_center, k_len, head_dim, p.chunks, p.slots);
     } else {
-      v_quantize_kernel<T, false><<<grid, kSlotsPerCta, 0, stream>>>(
+      launch_chained(v_quantize_kernel<T, false>, grid, dim3(kSlotsPerCta), 0, stream,
           static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
           residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
           stride_n, perm);
