@@ -59,6 +59,22 @@ int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_
                          const int32_t* perm, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* Q, K and V of one call: what the reference's binding risa_sdpa_quantize does with its two
+ * launcher calls (csrc/bindings.cpp:195-272: launch_quantize_qk[_gather] then launch_quantize_v[_gather]).
+ * Same results as risa_b200_quantize_qk followed by risa_b200_quantize_v with the same arguments
+ * (kv_perm is the gather table of both K and V); the steps that do not depend on one another -- K
+ * anchor detection, the V range pass and the Q quantiser -- share one launch. */
+int risa_b200_quantize_qkv(const void* q, void* q_codes, float* q_scale, const void* k,
+                           void* k_codes, float* k_scale, const void* v, void* v_codes,
+                           float* v_scale, float* v_center, int batch, int q_heads, int q_len,
+                           int kv_heads, int k_len, int head_dim, int cta_k, int padded_len,
+                           int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                           int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                           int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_n,
+                           int dtype_code, int midpoint_affine, int32_t* anchors,
+                           const int32_t* q_perm, const int32_t* kv_perm, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* V quantisation for callers that must not allocate.  Some users of this library cannot obtain
  * device memory at call time: a serving process that fixes its memory budget at start-up and
  * forbids cudaMalloc afterwards (it stalls every stream of the device and can fail once memory is

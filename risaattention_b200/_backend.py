@@ -34,6 +34,8 @@ _SIGNATURES = {
     "risa_b200_last_error": (ctypes.c_char_p, []),
     "risa_b200_abi_version": (c_i32, []),
     "risa_b200_quantize_qk": (c_i32, [c_vp] * 6 + [c_i32] * 7 + [c_i64] * 6 + [c_i32] + [c_vp] * 4),
+    "risa_b200_quantize_qkv": (
+        c_i32, [c_vp] * 10 + [c_i32] * 8 + [c_i64] * 9 + [c_i32] * 2 + [c_vp] * 4 + [c_sz, c_vp]),
     "risa_b200_quantize_v_workspace_size": (c_sz, [c_i32] * 4),
     "risa_b200_quantize_v": (
         c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 3 + [c_i32] * 2 + [c_vp, c_vp, c_sz, c_vp]),
@@ -125,14 +127,12 @@ class _Native:
                     else torch.cuda.default_stream(q.device)):
                 workspace = torch.empty(self.quantize_v_workspace_size(b, hkv, lk, d),
                                         dtype=torch.uint8, device=q.device)
-        self._check(self.lib.risa_b200_quantize_qk(
-            _ptr(q), _ptr(q_int8), _ptr(q_scale), _ptr(k), _ptr(k_int8), _ptr(k_scale), b, hq, lq,
-            hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
-            k.stride(2), input_dtype_code, _ptr(anchor_indices_ptr), _ptr(q_permutation_ptr),
-            _ptr(permutation_ptr), stream_ptr))
-        self._check(self.lib.risa_b200_quantize_v(
-            _ptr(v), _ptr(v_int8), _ptr(v_scale), _ptr(v_center), b, hkv, lk, d, v_int8.shape[1],
-            v.stride(0), v.stride(1), v.stride(2), input_dtype_code, int(use_midpoint_affine),
+        self._check(self.lib.risa_b200_quantize_qkv(
+            _ptr(q), _ptr(q_int8), _ptr(q_scale), _ptr(k), _ptr(k_int8), _ptr(k_scale), _ptr(v),
+            _ptr(v_int8), _ptr(v_scale), _ptr(v_center), b, hq, lq, hkv, lk, d, cta_k,
+            v_int8.shape[1], q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
+            k.stride(2), v.stride(0), v.stride(1), v.stride(2), input_dtype_code,
+            int(use_midpoint_affine), _ptr(anchor_indices_ptr), _ptr(q_permutation_ptr),
             _ptr(permutation_ptr), _ptr(workspace), workspace.numel() * workspace.element_size(),
             stream_ptr))
 

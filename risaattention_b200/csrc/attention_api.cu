@@ -111,6 +111,8 @@ int run_attention(
                    o_stride_b % 2 == 0 && o_stride_n % 2 == 0 && o_stride_h % 2 == 0,
                "risa_attention: packed operands must be 16-byte aligned and output strides even");
   AttentionArgs a{};
+  a.pack_by256 = 256u;
+  a.pack_by65536 = 65536u;
   a.q = static_cast<const int8_t*>(q);
   a.k = static_cast<const int8_t*>(k);
   a.v = static_cast<const int8_t*>(v);
@@ -317,16 +319,12 @@ extern "C" int risa_b200_dense_attention(
   float* k_scale = reinterpret_cast<float*>(base + s.k_scale);
   float* v_scale = reinterpret_cast<float*>(base + s.v_scale);
   float* v_center = reinterpret_cast<float*>(base + s.v_center);
-  int status = risa_b200_quantize_qk(
-      q, base + s.q_codes, q_scale, k, base + s.k_codes, k_scale, batch, q_heads, q_len, kv_heads,
-      k_len, head_dim, cta_k, q_stride_b, q_stride_h, q_stride_n, k_stride_b, k_stride_h,
-      k_stride_n, dtype_code, reinterpret_cast<int32_t*>(base + s.anchors), nullptr, nullptr,
-      stream);
-  if (status != RISA_B200_OK) return status;
-  status = risa_b200_quantize_v(v, base + s.v_codes, v_scale, v_center, batch, kv_heads, k_len,
-                                head_dim, padded, v_stride_b, v_stride_h, v_stride_n, dtype_code,
-                                midpoint_affine, nullptr, base + s.v_work, s.total - s.v_work,
-                                stream);
+  const int status = risa_b200_quantize_qkv(
+      q, base + s.q_codes, q_scale, k, base + s.k_codes, k_scale, v, base + s.v_codes, v_scale,
+      v_center, batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k, padded, q_stride_b,
+      q_stride_h, q_stride_n, k_stride_b, k_stride_h, k_stride_n, v_stride_b, v_stride_h,
+      v_stride_n, dtype_code, midpoint_affine, reinterpret_cast<int32_t*>(base + s.anchors),
+      nullptr, nullptr, base + s.v_work, s.total - s.v_work, stream);
   if (status != RISA_B200_OK) return status;
   return risa_b200_attention(base + s.q_codes, base + s.k_codes, base + s.v_codes, o, q_scale,
                              k_scale, v_scale, v_center, nullptr, 0, 0, 0, 0, -1, cta_k, batch,

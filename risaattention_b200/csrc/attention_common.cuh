@@ -36,6 +36,9 @@ struct AttentionArgs {
   int32_t* select_counts;    // [B*Hq*n_q] tiles kept per row
   uint32_t* select_bitmaps;  // [B*Hq*n_q, ceil(n_k / 32)] kept tiles as bits
   double* select_totals;     // [B*Hq*n_q, 2] kept mass, total mass
+  // 2^8 and 2^16 as run-time values for the multiply-add packing of probability codes
+  // (softmax_row.cuh, MAD_PACK)
+  uint32_t pack_by256, pack_by65536;
 };
 
 // Capture workspace (FP32 words), identical to the reference's (attention_int8.cuh:58-60,

@@ -174,7 +174,7 @@ struct Bars {
 template <bool CAPTURE, int CTA_K, int KIND>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
-                                                 uint16_t* sums) {
+                                                 uint16_t* sums, PackMultipliers mul) {
   // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
   // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
   // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
@@ -226,7 +226,8 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     uint32_t P[8], s4[8];
     // without capture the codes are not observable one by one: part of the exponentials moves to
     // the FP32 pipes (kExpPolyPairs of every four column pairs)
-    tile_exp_chunk<KIND, CAPTURE, 32, CAPTURE ? 0 : kExpPolyPairs>(x, sc, neg_m, P, numer, s4);
+    tile_exp_chunk<KIND, CAPTURE, 32, CAPTURE ? 0 : kExpPolyPairs, true>(x, sc, neg_m, P, numer, s4,
+                                                                         mul);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
@@ -628,6 +629,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
     const bool int_scores = !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
     const bool causal_fast = a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const PackMultipliers pack_mul{a.pack_by256, a.pack_by65536};
     const bool row_ok = row < a.q_len;
     const float scale2 = a.sm_scale * kLog2e;
     const float q_scale =
@@ -704,10 +706,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       if (int_scores && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
-                                                     my_sums);
+                                                     my_sums, pack_mul);
       else if (below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
-                                                        my_sums);
+                                                        my_sums, pack_mul);
       else
         softmax_tile_general<CAPTURE, CTA_K>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                              row_in & 7, stat, my_sums, int_scores, last, row,

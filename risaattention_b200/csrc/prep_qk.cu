@@ -10,7 +10,7 @@
 //     groups of the tile spread over its warps, so no lane holds more than 64 values.
 // This file is compiled with --use_fast_math on purpose: the reference's scale arithmetic
 // (x / 127.f, 1.f / x) is defined by that mode's approximate division and reciprocal.
-#include "common.cuh"
+#include "prep_v_range.cuh"
 
 namespace risa_b200 {
 namespace {
@@ -99,13 +99,23 @@ __device__ __forceinline__ void store16_codes(int8_t* p, const float* v, float i
 // Q: one CTA per (128-row block, head, batch).  A scale group is 4 rows {r, r+8, r+16, r+24} of a
 // 32-row tile (D <= 128) or 2 rows {r, r+8} of a 16-row tile (D = 256), times all channels.
 // ------------------------------------------------------------------------------------------
+struct QJob {
+  const void* q;
+  int8_t* codes;
+  float* scales;
+  int q_len, q_heads, batch, blocks, scales_per_head;
+  int64_t stride_b, stride_h, stride_n;
+  const int32_t* perm;
+};
+
 template <typename T, int D, int ROT>
-__global__ __launch_bounds__(256) void quantize_q_kernel(
-    const T* __restrict__ q, int8_t* __restrict__ codes, float* __restrict__ scales, int q_len,
-    int q_heads, int scales_per_head, int64_t stride_b, int64_t stride_h, int64_t stride_n,
-    const int32_t* __restrict__ perm) {
-  chain_wait();
-  chain_release();
+__device__ __forceinline__ void quantize_q_block(const QJob& job, int blk, int h, int b) {
+  const T* __restrict__ q = static_cast<const T*>(job.q);
+  int8_t* __restrict__ codes = job.codes;
+  float* __restrict__ scales = job.scales;
+  const int q_len = job.q_len, q_heads = job.q_heads, scales_per_head = job.scales_per_head;
+  const int64_t stride_b = job.stride_b, stride_h = job.stride_h, stride_n = job.stride_n;
+  const int32_t* __restrict__ perm = job.perm;
   constexpr int LPR = D / 16;                       // lanes per row
   constexpr int GROUP_ROWS = D == 256 ? 2 : 4;      // rows per scale group
   constexpr int GLANES = GROUP_ROWS * LPR;          // lanes per group (16 or 32)
@@ -114,7 +124,6 @@ __global__ __launch_bounds__(256) void quantize_q_kernel(
   constexpr int GROUPS = 128 / GROUP_ROWS;          // groups per 128-row block
   constexpr int PASSES = GROUPS / GPP / 8;          // passes per warp (8 warps)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const T* in = q + b * stride_b + h * stride_h;
   const int64_t bh = static_cast<int64_t>(b) * q_heads + h;
   int8_t* out = codes + bh * q_len * D;
@@ -152,6 +161,13 @@ __global__ __launch_bounds__(256) void quantize_q_kernel(
     if ((lane % GLANES) == 0) sc_out[group] = sc;
     if (rows[p] < q_len) store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
   }
+}
+
+template <typename T, int D, int ROT>
+__global__ __launch_bounds__(256) void quantize_q_kernel(const QJob job) {
+  chain_wait();
+  chain_release();
+  quantize_q_block<T, D, ROT>(job, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -241,61 +257,69 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
 // raising the sampled absmax by more than 12.5 %.  The FP32 reduction shape (thread t owns
 // channels t and t+128, shfl_down tree, warps added 0..3) decides borderline cases and is kept.
 // ------------------------------------------------------------------------------------------
+struct AnchorJob {
+  const void* k;
+  int32_t* anchors;
+  int k_len, head_dim, kv_heads, batch;
+  int64_t stride_b, stride_h, stride_n;
+  const int32_t* perm;
+};
+
+// Threads 0..127 of the CTA do the work; a CTA may be larger (every thread takes the barriers).
 template <typename T>
-__global__ __launch_bounds__(128) void detect_anchor_kernel(const T* __restrict__ k,
-                                                            int32_t* __restrict__ anchors,
-                                                            int k_len, int head_dim, int kv_heads,
-                                                            int64_t stride_b, int64_t stride_h,
-                                                            int64_t stride_n,
-                                                            const int32_t* __restrict__ perm) {
-  chain_wait();
-  chain_release();
+__device__ __forceinline__ void detect_anchor_block(const AnchorJob& job, int h, int b) {
   constexpr int S = 9;
   __shared__ float smp[S * 256];
   __shared__ float w_energy[4], w_max[4], w_dist[S][4], w_benergy[4], w_bmax[4];
   __shared__ int chosen;
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int k_len = job.k_len, head_dim = job.head_dim;
+  const int tid = threadIdx.x;
+  const bool active = tid < 128;
   const int lane = tid & 31, warp = tid >> 5;
-  const int64_t bh = static_cast<int64_t>(b) * kv_heads + h;
-  const T* in = k + b * stride_b + h * stride_h;
-  const int32_t* row_map = perm ? perm + bh * k_len : nullptr;
-  for (int idx = tid; idx < S * head_dim; idx += 128) {
-    const int sample = idx / head_dim, channel = idx - sample * head_dim;
-    const int row = sample * (k_len - 1) / (S - 1);
-    const int64_t src = row_map ? __ldg(row_map + row) : row;
-    smp[idx] = load_scalar(in + src * stride_n + channel);
+  const int64_t bh = static_cast<int64_t>(b) * job.kv_heads + h;
+  const T* in = static_cast<const T*>(job.k) + b * job.stride_b + h * job.stride_h;
+  const int32_t* row_map = job.perm ? job.perm + bh * k_len : nullptr;
+  if (active) {
+    for (int idx = tid; idx < S * head_dim; idx += 128) {
+      const int sample = idx / head_dim, channel = idx - sample * head_dim;
+      const int row = sample * (k_len - 1) / (S - 1);
+      const int64_t src = row_map ? __ldg(row_map + row) : row;
+      smp[idx] = load_scalar(in + src * job.stride_n + channel);
+    }
   }
   __syncthreads();
-  float energy = 0.f, vmax = 0.f, dist[S];
+  if (active) {
+    float energy = 0.f, vmax = 0.f, dist[S];
 #pragma unroll
-  for (int c = 0; c < S; ++c) dist[c] = 0.f;
-  for (int channel = tid; channel < head_dim; channel += 128) {
-    float sum = 0.f;
+    for (int c = 0; c < S; ++c) dist[c] = 0.f;
+    for (int channel = tid; channel < head_dim; channel += 128) {
+      float sum = 0.f;
 #pragma unroll
-    for (int sidx = 0; sidx < S; ++sidx) {
-      const float x = smp[sidx * head_dim + channel];
-      energy = fmaf(x, x, energy);
-      vmax = fmaxf(vmax, fabsf(x));
-      sum += x;
+      for (int sidx = 0; sidx < S; ++sidx) {
+        const float x = smp[sidx * head_dim + channel];
+        energy = fmaf(x, x, energy);
+        vmax = fmaxf(vmax, fabsf(x));
+        sum += x;
+      }
+#pragma unroll
+      for (int c = 0; c < S; ++c) {
+        const float dd = S * smp[c * head_dim + channel] - sum;
+        dist[c] = fmaf(dd, dd, dist[c]);
+      }
     }
 #pragma unroll
-    for (int c = 0; c < S; ++c) {
-      const float dd = S * smp[c * head_dim + channel] - sum;
-      dist[c] = fmaf(dd, dd, dist[c]);
+    for (int off = 16; off > 0; off >>= 1) {
+      energy += __shfl_down_sync(0xffffffffu, energy, off);
+      vmax = fmaxf(vmax, __shfl_down_sync(0xffffffffu, vmax, off));
+#pragma unroll
+      for (int c = 0; c < S; ++c) dist[c] += __shfl_down_sync(0xffffffffu, dist[c], off);
     }
-  }
+    if (lane == 0) {
+      w_energy[warp] = energy;
+      w_max[warp] = vmax;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    energy += __shfl_down_sync(0xffffffffu, energy, off);
-    vmax = fmaxf(vmax, __shfl_down_sync(0xffffffffu, vmax, off));
-#pragma unroll
-    for (int c = 0; c < S; ++c) dist[c] += __shfl_down_sync(0xffffffffu, dist[c], off);
-  }
-  if (lane == 0) {
-    w_energy[warp] = energy;
-    w_max[warp] = vmax;
-#pragma unroll
-    for (int c = 0; c < S; ++c) w_dist[c][warp] = dist[c];
+      for (int c = 0; c < S; ++c) w_dist[c][warp] = dist[c];
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -314,24 +338,26 @@ __global__ __launch_bounds__(128) void detect_anchor_kernel(const T* __restrict_
     chosen = best;
   }
   __syncthreads();
-  float benergy = 0.f, bmax = 0.f;
-  for (int channel = tid; channel < head_dim; channel += 128) {
-    const float a = smp[chosen * head_dim + channel];
+  if (active) {
+    float benergy = 0.f, bmax = 0.f;
+    for (int channel = tid; channel < head_dim; channel += 128) {
+      const float a = smp[chosen * head_dim + channel];
 #pragma unroll
-    for (int sidx = 0; sidx < S; ++sidx) {
-      const float r = smp[sidx * head_dim + channel] - a;
-      benergy = fmaf(r, r, benergy);
-      bmax = fmaxf(bmax, fabsf(r));
+      for (int sidx = 0; sidx < S; ++sidx) {
+        const float r = smp[sidx * head_dim + channel] - a;
+        benergy = fmaf(r, r, benergy);
+        bmax = fmaxf(bmax, fabsf(r));
+      }
     }
-  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    benergy += __shfl_down_sync(0xffffffffu, benergy, off);
-    bmax = fmaxf(bmax, __shfl_down_sync(0xffffffffu, bmax, off));
-  }
-  if (lane == 0) {
-    w_benergy[warp] = benergy;
-    w_bmax[warp] = bmax;
+    for (int off = 16; off > 0; off >>= 1) {
+      benergy += __shfl_down_sync(0xffffffffu, benergy, off);
+      bmax = fmaxf(bmax, __shfl_down_sync(0xffffffffu, bmax, off));
+    }
+    if (lane == 0) {
+      w_benergy[warp] = benergy;
+      w_bmax[warp] = bmax;
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -344,18 +370,63 @@ __global__ __launch_bounds__(128) void detect_anchor_kernel(const T* __restrict_
       bm = fmaxf(bm, w_bmax[i]);
     }
     const bool improves = be < te && bm <= tm * 1.125f;
-    anchors[bh] = improves ? chosen * (k_len - 1) / (S - 1) : -1;
+    job.anchors[bh] = improves ? chosen * (k_len - 1) / (S - 1) : -1;
   }
 }
 
+template <typename T>
+__global__ __launch_bounds__(128) void detect_anchor_kernel(const AnchorJob job) {
+  chain_wait();
+  chain_release();
+  detect_anchor_block<T>(job, blockIdx.x, blockIdx.y);
+}
+
+// The three steps of a call's preparation that need nothing from one another -- the K anchor
+// detector, the V range step and the Q quantiser -- as one launch: CTAs [0, anchor CTAs) detect,
+// the next ones take V range chunks, the rest quantise Q blocks.  The detector comes first because
+// it is one long dependent chain per head; the Q blocks fill the GPU behind it.
 template <typename T, int D, int ROT>
-void launch_q(const void* q, void* codes, float* scales, int batch, int heads, int q_len,
-              int64_t sb, int64_t sh, int64_t sn, const int32_t* perm, cudaStream_t stream) {
-  const int blocks = (q_len + 127) / 128;
-  const int per_head = blocks * (D == 256 ? 64 : 32);
-  launch_chained(quantize_q_kernel<T, D, ROT>, dim3(blocks, heads, batch), dim3(256), 0, stream,
-      static_cast<const T*>(q), static_cast<int8_t*>(codes), scales, q_len, heads, per_head, sb,
-      sh, sn, perm);
+__global__ __launch_bounds__(256) void quantize_q_scan_kernel(const QJob q_job,
+                                                              const AnchorJob anchor_job,
+                                                              const VRangeJob range_job) {
+  chain_wait();
+  chain_release();
+  const int n_anchor = anchor_job.kv_heads * anchor_job.batch;
+  const int n_range = range_job.chunks * range_job.kv_heads * range_job.batch;
+  int block = blockIdx.x;
+  if (block < n_anchor) {
+    detect_anchor_block<T>(anchor_job, block % anchor_job.kv_heads, block / anchor_job.kv_heads);
+    return;
+  }
+  block -= n_anchor;
+  if (block < n_range) {
+    const int chunk = block % range_job.chunks, bh = block / range_job.chunks;
+    v_range_block<T>(range_job, chunk, bh % range_job.kv_heads, bh / range_job.kv_heads);
+    return;
+  }
+  block -= n_range;
+  const int blk = block % q_job.blocks, bh = block / q_job.blocks;
+  quantize_q_block<T, D, ROT>(q_job, blk, bh % q_job.q_heads, bh / q_job.q_heads);
+}
+
+// First launch of the preparation: the Q quantiser, and in front of it either the anchor detector
+// as a launch of its own or -- when the V range step of the same call is handed in -- the anchor
+// detector and the range step inside the same grid.
+template <typename T, int D, int ROT>
+void launch_q(const QJob& q_job, const AnchorJob& anchor_job, const VRangeJob* range_job,
+              cudaStream_t stream) {
+  if (range_job) {
+    const int blocks = anchor_job.kv_heads * anchor_job.batch +
+                       range_job->chunks * range_job->kv_heads * range_job->batch +
+                       q_job.blocks * q_job.q_heads * q_job.batch;
+    launch_chained(quantize_q_scan_kernel<T, D, ROT>, dim3(blocks), dim3(256), 0, stream, q_job,
+                   anchor_job, *range_job);
+  } else {
+    launch_chained(detect_anchor_kernel<T>, dim3(anchor_job.kv_heads, anchor_job.batch), dim3(128),
+                   0, stream, anchor_job);
+    launch_chained(quantize_q_kernel<T, D, ROT>, dim3(q_job.blocks, q_job.q_heads, q_job.batch),
+                   dim3(256), 0, stream, q_job);
+  }
 }
 
 template <typename T, int D, int CTA_K, int ROT>
@@ -364,25 +435,27 @@ void launch_k(const void* k, void* codes, float* scales, const int32_t* anchors,
               cudaStream_t stream) {
   const int tiles = (k_len + CTA_K - 1) / CTA_K;
   launch_chained(quantize_k_kernel<T, D, CTA_K, ROT>, dim3(tiles, heads, batch),
-                 dim3(k_threads(D, CTA_K)), 0, stream, static_cast<const T*>(k), static_cast<int8_t*>(codes), scales, anchors, k_len, heads,
-      tiles * 4, sb, sh, sn, perm);
+                 dim3(k_threads(D, CTA_K)), 0, stream, static_cast<const T*>(k),
+                 static_cast<int8_t*>(codes), scales, anchors, k_len, heads, tiles * 4, sb, sh, sn,
+                 perm);
 }
 
 template <typename T, int D, int ROT>
-void launch_qk(const void* q, void* qc, float* qs, const void* k, void* kc, float* ks,
-               const int32_t* anchors, int batch, int hq, int lq, int hkv, int lk, int cta_k,
-               const int64_t* st, const int32_t* qperm, const int32_t* kperm,
-               cudaStream_t stream) {
-  launch_q<T, D, ROT>(q, qc, qs, batch, hq, lq, st[0], st[1], st[2], qperm, stream);
+void launch_qk(QJob q_job, const AnchorJob& anchor_job, const VRangeJob* range_job, void* kc,
+               float* ks, int cta_k, cudaStream_t stream) {
+  q_job.scales_per_head = q_job.blocks * (D == 256 ? 64 : 32);
+  launch_q<T, D, ROT>(q_job, anchor_job, range_job, stream);
+  const AnchorJob& a = anchor_job;
   if constexpr (D == 64) {
-    launch_k<T, D, 64, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm, stream);
+    launch_k<T, D, 64, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
+                            a.stride_h, a.stride_n, a.perm, stream);
   } else {
     if (cta_k == 128)
-      launch_k<T, D, 128, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm,
-                               stream);
+      launch_k<T, D, 128, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
+                               a.stride_h, a.stride_n, a.perm, stream);
     else
-      launch_k<T, D, 64, ROT>(k, kc, ks, anchors, batch, hkv, lk, st[3], st[4], st[5], kperm,
-                              stream);
+      launch_k<T, D, 64, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
+                              a.stride_h, a.stride_n, a.perm, stream);
   }
 }
 
@@ -391,13 +464,14 @@ void launch_qk(const void* q, void* qc, float* qs, const void* k, void* kc, floa
 
 using namespace risa_b200;
 
-extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scale, const void* k,
-                                     void* k_codes, float* k_scale, int batch, int q_heads,
-                                     int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
-                                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
-                                     int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
-                                     int dtype_code, int32_t* anchors, const int32_t* q_perm,
-                                     const int32_t* k_perm, void* stream_ptr) {
+int risa_b200::quantize_qk_with_range(const void* q, void* q_codes, float* q_scale, const void* k,
+                                      void* k_codes, float* k_scale, int batch, int q_heads,
+                                      int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
+                                      int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                      int dtype_code, int32_t* anchors, const int32_t* q_perm,
+                                      const int32_t* k_perm, const VRangeJob* range_job,
+                                      void* stream_ptr) {
   RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
                "quantize_qk: padded head_dim must be 64, 128, or 256");
   RISA_REQUIRE((cta_k == 64 || cta_k == 128) && !(head_dim == 64 && cta_k != 64),
@@ -421,15 +495,34 @@ extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scal
                    reinterpret_cast<uintptr_t>(k_codes) % 16 == 0,
                "quantize_qk: code buffers must be 16-byte aligned");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  const int64_t st[6] = {q_stride_b, q_stride_h, q_stride_n, k_stride_b, k_stride_h, k_stride_n};
-#define RISA_QK(D, ROT)                                                                       \
-  launch_qk<T, D, ROT>(q, q_codes, q_scale, k, k_codes, k_scale, anchors, batch, q_heads, q_len, \
-                       kv_heads, k_len, cta_k, st, q_perm, k_perm, stream)
+  QJob q_job;
+  q_job.q = q;
+  q_job.codes = static_cast<int8_t*>(q_codes);
+  q_job.scales = q_scale;
+  q_job.q_len = q_len;
+  q_job.q_heads = q_heads;
+  q_job.batch = batch;
+  q_job.blocks = (q_len + 127) / 128;
+  q_job.scales_per_head = 0;  // set per head_dim below
+  q_job.stride_b = q_stride_b;
+  q_job.stride_h = q_stride_h;
+  q_job.stride_n = q_stride_n;
+  q_job.perm = q_perm;
+  AnchorJob anchor_job;
+  anchor_job.k = k;
+  anchor_job.anchors = anchors;
+  anchor_job.k_len = k_len;
+  anchor_job.head_dim = head_dim;
+  anchor_job.kv_heads = kv_heads;
+  anchor_job.batch = batch;
+  anchor_job.stride_b = k_stride_b;
+  anchor_job.stride_h = k_stride_h;
+  anchor_job.stride_n = k_stride_n;
+  anchor_job.perm = k_perm;
+#define RISA_QK(D, ROT) \
+  launch_qk<T, D, ROT>(q_job, anchor_job, range_job, k_codes, k_scale, cta_k, stream)
   const bool h4_only = k_len <= 256;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    launch_chained(detect_anchor_kernel<T>, dim3(kv_heads, batch), dim3(128), 0, stream,
-        static_cast<const T*>(k), anchors, k_len, head_dim, kv_heads, k_stride_b, k_stride_h,
-        k_stride_n, k_perm);
     if (head_dim == 64) {
       if (h4_only) RISA_QK(64, kRotH4); else RISA_QK(64, kRotH64);
     } else if (head_dim == 128) {
@@ -440,4 +533,43 @@ extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scal
   });
 #undef RISA_QK
   return check_launch("quantize_qk");
+}
+
+extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scale, const void* k,
+                                     void* k_codes, float* k_scale, int batch, int q_heads,
+                                     int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
+                                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                     int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                     int dtype_code, int32_t* anchors, const int32_t* q_perm,
+                                     const int32_t* k_perm, void* stream_ptr) {
+  return quantize_qk_with_range(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
+                                kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
+                                q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code, anchors,
+                                q_perm, k_perm, nullptr, stream_ptr);
+}
+
+// Q, K and V of one call.  Same kernels and results as risa_b200_quantize_qk followed by
+// risa_b200_quantize_v; the V range step travels in the first launch (see quantize_q_scan_kernel).
+extern "C" int risa_b200_quantize_qkv(
+    const void* q, void* q_codes, float* q_scale, const void* k, void* k_codes, float* k_scale,
+    const void* v, void* v_codes, float* v_scale, float* v_center, int batch, int q_heads,
+    int q_len, int kv_heads, int k_len, int head_dim, int cta_k, int padded_len,
+    int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n, int64_t k_stride_b,
+    int64_t k_stride_h, int64_t k_stride_n, int64_t v_stride_b, int64_t v_stride_h,
+    int64_t v_stride_n, int dtype_code, int midpoint_affine, int32_t* anchors,
+    const int32_t* q_perm, const int32_t* kv_perm, void* workspace, size_t workspace_bytes,
+    void* stream_ptr) {
+  VRangeJob range_job;
+  int status = v_range_job(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
+                           padded_len, v_stride_b, v_stride_h, v_stride_n, dtype_code, kv_perm,
+                           workspace, workspace_bytes, &range_job);
+  if (status != RISA_B200_OK) return status;
+  status = quantize_qk_with_range(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
+                                  kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
+                                  q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code,
+                                  anchors, q_perm, kv_perm, &range_job, stream_ptr);
+  if (status != RISA_B200_OK) return status;
+  return quantize_v_after_range(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
+                                padded_len, v_stride_b, v_stride_h, v_stride_n, dtype_code,
+                                midpoint_affine, kv_perm, workspace, stream_ptr);
 }

@@ -13,14 +13,12 @@
 //                chunk ranges itself, writes codes and its slots' residual sums;
 //   3. finish:   (midpoint-affine only) combines the residual sums in the reference order.
 // Compiled with --use_fast_math like the reference so 1.f / x and x / float(L) lower identically.
-#include "common.cuh"
-#include <cfloat>
+#include "prep_v_range.cuh"
 #include <mutex>
 
 namespace risa_b200 {
 namespace {
 
-constexpr int kRangeChunk = 512;   // tokens per range CTA
 constexpr int kSlotsPerCta = 128;  // residual-order slots per quantise CTA
 
 __device__ __forceinline__ int storage_position(int token) {
@@ -30,63 +28,12 @@ __device__ __forceinline__ int storage_position(int token) {
          (((w >> 2) & 1) << 3);
 }
 
+// grid (chunks, Hkv, B), 256 threads.
 template <typename T>
-__device__ __forceinline__ void load8(const T* p, float* v) {
-  Load4<T>::load(p, v);
-  Load4<T>::load(p + 4, v + 4);
-}
-
-// grid (chunks, Hkv, B), 256 threads: thread = (token lane, 8-channel group).
-template <typename T>
-__global__ __launch_bounds__(256) void v_range_kernel(const T* __restrict__ v,
-                                                      float2* __restrict__ ranges, int k_len,
-                                                      int head_dim, int kv_heads, int chunks,
-                                                      int64_t stride_b, int64_t stride_h,
-                                                      int64_t stride_n,
-                                                      const int32_t* __restrict__ perm) {
+__global__ __launch_bounds__(kRangeThreads) void v_range_kernel(const VRangeJob job) {
   chain_wait();
   chain_release();
-  __shared__ float s_mn[256][9], s_mx[256][9];
-  const int groups = head_dim / 8;            // 8, 16 or 32 threads per token row
-  const int tokens_per_step = 256 / groups;
-  const int g = threadIdx.x % groups, tl = threadIdx.x / groups;
-  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int64_t bh = static_cast<int64_t>(b) * kv_heads + h;
-  const T* in = v + b * stride_b + h * stride_h + g * 8;
-  const int32_t* row_map = perm ? perm + bh * k_len : nullptr;
-  float mn[8], mx[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    mn[i] = FLT_MAX;
-    mx[i] = -FLT_MAX;
-  }
-  const int begin = chunk * kRangeChunk;
-  const int end = min(k_len, begin + kRangeChunk);
-  for (int n = begin + tl; n < end; n += tokens_per_step) {
-    float t[8];
-    const int64_t src = row_map ? __ldg(row_map + n) : n;
-    load8(in + src * stride_n, t);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      mn[i] = fminf(mn[i], t[i]);
-      mx[i] = fmaxf(mx[i], t[i]);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    s_mn[threadIdx.x][i] = mn[i];
-    s_mx[threadIdx.x][i] = mx[i];
-  }
-  __syncthreads();
-  if (threadIdx.x < head_dim) {
-    const int c = threadIdx.x, cg = c / 8, ci = c % 8;
-    float lo = FLT_MAX, hi = -FLT_MAX;
-    for (int t = 0; t < tokens_per_step; ++t) {
-      lo = fminf(lo, s_mn[t * groups + cg][ci]);
-      hi = fmaxf(hi, s_mx[t * groups + cg][ci]);
-    }
-    ranges[(bh * chunks + chunk) * head_dim + c] = make_float2(lo, hi);
-  }
+  v_range_block<T>(job, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // grid (slot slices, B*Hkv*D/8), 128 threads.
@@ -376,12 +323,11 @@ extern "C" size_t risa_b200_quantize_v_workspace_size(int batch, int kv_heads, i
   return p.range_bytes + p.residual_bytes;
 }
 
-extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_center,
-                                    int batch, int kv_heads, int k_len, int head_dim,
-                                    int padded_len, int64_t stride_b, int64_t stride_h,
-                                    int64_t stride_n, int dtype_code, int midpoint_affine,
-                                    const int32_t* perm, void* workspace, size_t workspace_bytes,
-                                    void* stream_ptr) {
+int risa_b200::v_range_job(const void* v, void* v_codes, float* v_scale, float* v_center,
+                           int batch, int kv_heads, int k_len, int head_dim, int padded_len,
+                           int64_t stride_b, int64_t stride_h, int64_t stride_n, int dtype_code,
+                           const int32_t* perm, void* workspace, size_t workspace_bytes,
+                           VRangeJob* job) {
   RISA_REQUIRE(v && v_codes && v_scale && v_center, "quantize_v: null tensor");
   RISA_REQUIRE(batch > 0 && kv_heads > 0 && k_len > 0, "quantize_v: sizes must be positive");
   RISA_REQUIRE(head_dim > 0 && head_dim % 8 == 0 && head_dim <= 256,
@@ -402,14 +348,33 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
                "quantize_v: workspace of %zu bytes required", p.range_bytes + p.residual_bytes);
   RISA_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0,
                "quantize_v: workspace must be 16-byte aligned");
+  job->v = v;
+  job->ranges = static_cast<float2*>(workspace);
+  job->k_len = k_len;
+  job->head_dim = head_dim;
+  job->kv_heads = kv_heads;
+  job->batch = batch;
+  job->chunks = p.chunks;
+  job->stride_b = stride_b;
+  job->stride_h = stride_h;
+  job->stride_n = stride_n;
+  job->perm = perm;
+  return RISA_B200_OK;
+}
+
+// Everything after the range step; the arguments were checked by v_range_job().
+int risa_b200::quantize_v_after_range(const void* v, void* v_codes, float* v_scale,
+                                      float* v_center, int batch, int kv_heads, int k_len,
+                                      int head_dim, int padded_len, int64_t stride_b,
+                                      int64_t stride_h, int64_t stride_n, int dtype_code,
+                                      int midpoint_affine, const int32_t* perm, void* workspace,
+                                      void* stream_ptr) {
+  const VPlan p = plan(batch, kv_heads, k_len, head_dim);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   float2* ranges = static_cast<float2*>(workspace);
   float* residuals = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.range_bytes);
   const int channels = batch * kv_heads * head_dim;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    launch_chained(v_range_kernel<T>, dim3(p.chunks, kv_heads, batch), dim3(256), 0, stream,
-        static_cast<const T*>(v), ranges, k_len, head_dim, kv_heads, p.chunks, stride_b, stride_h,
-        stride_n, perm);
     const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
     const dim3 tiled_grid(p.slots / kTiledSlots, channels / kTiledChannels);
     // 16-byte code stores need whole storage groups and an aligned destination; a CTA of the tiled
@@ -443,6 +408,26 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
     }
   });
   return check_launch("quantize_v");
+}
+
+extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_center,
+                                    int batch, int kv_heads, int k_len, int head_dim,
+                                    int padded_len, int64_t stride_b, int64_t stride_h,
+                                    int64_t stride_n, int dtype_code, int midpoint_affine,
+                                    const int32_t* perm, void* workspace, size_t workspace_bytes,
+                                    void* stream_ptr) {
+  VRangeJob job;
+  const int status =
+      v_range_job(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim, padded_len,
+                  stride_b, stride_h, stride_n, dtype_code, perm, workspace, workspace_bytes, &job);
+  if (status != RISA_B200_OK) return status;
+  RISA_DISPATCH_FLOAT(dtype_code, T, {
+    launch_chained(v_range_kernel<T>, dim3(job.chunks, kv_heads, batch), dim3(kRangeThreads), 0,
+                   static_cast<cudaStream_t>(stream_ptr), job);
+  });
+  return quantize_v_after_range(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
+                                padded_len, stride_b, stride_h, stride_n, dtype_code,
+                                midpoint_affine, perm, workspace, stream_ptr);
 }
 
 // ---- allocation-free variant --------------------------------------------------------------------

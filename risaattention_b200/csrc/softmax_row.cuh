@@ -137,9 +137,23 @@ __device__ __forceinline__ uint64_t ex2_poly_f32x2(uint64_t x2) {
 // POLY: of every eight columns, this many pairs (0..4) take their exponential from the FP32 pipes
 // (ex2_poly_f32x2) instead of the special-function unit; only paths whose probability codes are not
 // pinned bit for bit may use it.
-template <int KIND, bool WANT_SUMS, int NCOL = 32, int POLY = 0>
+// MAD_PACK: the four rounded values of a word are combined by three integer multiply-adds
+// (u1 * 2^8 + u0, u3 * 2^8 + u2, hi * 2^16 + lo) instead of three byte permutes, which moves the
+// packing from the ALU pipe, the busiest one of the tensor-core kernel, to the FMA pipe.  The float
+// bit patterns are 0x4B000000 + e + code with e the amount by which the rounding constant exceeds
+// 2^23; everything above bit 31 falls away, so the word comes out as the four codes plus
+// 0x4B000000 + e0 + e1 * 2^8 + e2 * 2^16 + e3 * 2^24, which is 0 mod 2^32 for e = (0, 0, 256, 180).
+// All four constants are even integers, so ties still round to the same (even) code.  The
+// multipliers 2^8 and 2^16 arrive as run-time values (kernel arguments): written as literals they
+// would be turned back into shifts on the ALU pipe.
+struct PackMultipliers {
+  uint32_t by256, by65536;
+};
+
+template <int KIND, bool WANT_SUMS, int NCOL = 32, int POLY = 0, bool MAD_PACK = false>
 __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
-                                               uint32_t* P, uint32_t& numer, uint32_t* s4) {
+                                               uint32_t* P, uint32_t& numer, uint32_t* s4,
+                                               PackMultipliers mul = PackMultipliers{0u, 0u}) {
   // Columns 2k and 2k + 1 share a K scale group, so scale and magic add run as packed FP32 pairs
   // (one instruction for two columns, same per-lane rounding as the scalar form).
   float p[NCOL];
@@ -167,10 +181,13 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
   }
   uint32_t u[NCOL];
   const uint64_t magic2 = pack_f32x2(8388608.0f, 8388608.0f);
+  // columns 8..15 of a 16-key group are bytes 2 and 3 of their words
+  const uint64_t magic2_upper =
+      MAD_PACK ? pack_f32x2(8388608.0f + 256.0f, 8388608.0f + 180.0f) : magic2;
 #pragma unroll
   for (int i = 0; i < NCOL; i += 2) {
     float a, b;
-    unpack_f32x2(add_f32x2(pack_f32x2(p[i], p[i + 1]), magic2), a, b);
+    unpack_f32x2(add_f32x2(pack_f32x2(p[i], p[i + 1]), (i & 8) ? magic2_upper : magic2), a, b);
     u[i] = __float_as_uint(a);
     u[i + 1] = __float_as_uint(b);
   }
@@ -178,9 +195,19 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
   for (int j = 0; j < NCOL / 16; ++j) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const uint32_t lo = __byte_perm(u[lane_column(j, g, 0)], u[lane_column(j, g, 1)], 0x0040);
-      const uint32_t hi = __byte_perm(u[lane_column(j, g, 2)], u[lane_column(j, g, 3)], 0x0040);
-      P[4 * j + g] = __byte_perm(lo, hi, 0x5410);
+      if constexpr (MAD_PACK) {
+        uint32_t lo, hi, w;
+        asm("mad.lo.u32 %0, %1, %2, %3;"
+            : "=r"(lo) : "r"(u[lane_column(j, g, 1)]), "r"(mul.by256), "r"(u[lane_column(j, g, 0)]));
+        asm("mad.lo.u32 %0, %1, %2, %3;"
+            : "=r"(hi) : "r"(u[lane_column(j, g, 3)]), "r"(mul.by256), "r"(u[lane_column(j, g, 2)]));
+        asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(w) : "r"(hi), "r"(mul.by65536), "r"(lo));
+        P[4 * j + g] = w;
+      } else {
+        const uint32_t lo = __byte_perm(u[lane_column(j, g, 0)], u[lane_column(j, g, 1)], 0x0040);
+        const uint32_t hi = __byte_perm(u[lane_column(j, g, 2)], u[lane_column(j, g, 3)], 0x0040);
+        P[4 * j + g] = __byte_perm(lo, hi, 0x5410);
+      }
     }
   }
   uint32_t odd = 0;  // second partial sum: two short dependent chains instead of one

@@ -85,18 +85,14 @@ void quantize_tensors(const at::Tensor& q, const at::Tensor& k, const at::Tensor
     const size_t bytes = risa_b200_quantize_v_workspace_size(b, hkv, lk, d);
     workspace = at::empty({int64_t(bytes)}, q.options().dtype(at::kByte));
   }
-  check(risa_b200_quantize_qk(q.data_ptr(), q_int8.data_ptr(), q_scale.data_ptr<float>(),
-                              k.data_ptr(), k_int8.data_ptr(), k_scale.data_ptr<float>(), b, hq,
-                              lq, hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2),
-                              k.stride(0), k.stride(1), k.stride(2), input_dtype_code,
-                              static_cast<int32_t*>(anchors), static_cast<const int32_t*>(q_table),
-                              static_cast<const int32_t*>(kv_table), stream_of(stream_ptr)));
-  check(risa_b200_quantize_v(v.data_ptr(), v_int8.data_ptr(), v_scale.data_ptr<float>(),
-                             v_center.data_ptr<float>(), b, hkv, lk, d, int(v_int8.size(1)),
-                             v.stride(0), v.stride(1), v.stride(2), input_dtype_code,
-                             use_midpoint_affine ? 1 : 0, static_cast<const int32_t*>(kv_table),
-                             workspace->data_ptr(), size_t(workspace->numel()),
-                             stream_of(stream_ptr)));
+  check(risa_b200_quantize_qkv(
+      q.data_ptr(), q_int8.data_ptr(), q_scale.data_ptr<float>(), k.data_ptr(), k_int8.data_ptr(),
+      k_scale.data_ptr<float>(), v.data_ptr(), v_int8.data_ptr(), v_scale.data_ptr<float>(),
+      v_center.data_ptr<float>(), b, hq, lq, hkv, lk, d, cta_k, int(v_int8.size(1)), q.stride(0),
+      q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
+      v.stride(2), input_dtype_code, use_midpoint_affine ? 1 : 0, static_cast<int32_t*>(anchors),
+      static_cast<const int32_t*>(q_table), static_cast<const int32_t*>(kv_table),
+      workspace->data_ptr(), size_t(workspace->numel()), stream_of(stream_ptr)));
 }
 
 void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at::Tensor& v_int8,

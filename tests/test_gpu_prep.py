@@ -181,3 +181,36 @@ def test_quantize_v_c_abi_head_dims_outside_the_kernel_set(ref, dim, lk, affine)
     assert torch.equal(codes, rc) and torch.equal(scale, rs)
     _centers_match(center, rcen)
     assert int(guard.sum()) == 0
+
+
+@pytest.mark.parametrize("case", [CASES[0], CASES[3], CASES[6]])
+@pytest.mark.parametrize("affine", [False, True])
+def test_separate_entry_points_equal_the_combined_call(case, affine):
+    """risa_b200_quantize_qk + risa_b200_quantize_v (anchor detector, range pass and Q quantiser as
+    launches of their own) give the bytes of risa_b200_quantize_qkv (one launch for the three)."""
+    import ctypes
+
+    from risaattention_b200 import _backend
+    from risaattention_b200._quantization import PackedBuffers
+
+    d, lq, lk, cta_k, hq, hkv = case
+    q, k, v = qkv(2, hq, hkv, lq, lk, d, torch.bfloat16, seed=7 + lq, anchor=True)
+    v = v + 0.75
+    combined = _ours(q, k, v, cta_k, affine)
+    apart = PackedBuffers(q, k, cta_k)
+    C = _backend._ABI
+    stream = torch.cuda.current_stream().cuda_stream
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    b = q.shape[0]
+    C._check(C.lib.risa_b200_quantize_qk(
+        p(q), p(apart.q_codes), p(apart.q_scales), p(k), p(apart.k_codes), p(apart.k_scales), b, hq,
+        lq, hkv, lk, d, cta_k, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1),
+        k.stride(2), 2, p(apart.anchors), None, None, stream))
+    C._check(C.lib.risa_b200_quantize_v(
+        p(v), p(apart.v_codes), p(apart.v_scales), p(apart.v_centers), b, hkv, lk, d,
+        apart.v_codes.shape[1], v.stride(0), v.stride(1), v.stride(2), 2, int(affine), None,
+        p(apart.workspace), apart.workspace.numel(), stream))
+    torch.cuda.synchronize()
+    for name in ("anchors", "q_codes", "q_scales", "k_codes", "k_scales", "v_codes", "v_scales",
+                 "v_centers"):
+        assert torch.equal(getattr(combined, name), getattr(apart, name)), name
