@@ -62,8 +62,9 @@ int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale, float* v_
 /* Q, K and V of one call: what the reference's binding risa_sdpa_quantize does with its two
  * launcher calls (csrc/bindings.cpp:195-272: launch_quantize_qk[_gather] then launch_quantize_v[_gather]).
  * Same results as risa_b200_quantize_qk followed by risa_b200_quantize_v with the same arguments
- * (kv_perm is the gather table of both K and V); the steps that do not depend on one another -- K
- * anchor detection, the V range pass and the Q quantiser -- share one launch. */
+ * (kv_perm is the gather table of both K and V) in two launches: the steps that depend on nothing
+ * (K anchor detection, V range pass, Q quantiser), then the steps that depend on those (K quantiser,
+ * V code pass; key lengths that are not a multiple of 16 keep a separate V launch). */
 int risa_b200_quantize_qkv(const void* q, void* q_codes, float* q_scale, const void* k,
                            void* k_codes, float* k_scale, const void* v, void* v_codes,
                            float* v_scale, float* v_center, int batch, int q_heads, int q_len,

@@ -10,7 +10,7 @@
 //     groups of the tile spread over its warps, so no lane holds more than 64 values.
 // This file is compiled with --use_fast_math on purpose: the reference's scale arithmetic
 // (x / 127.f, 1.f / x) is defined by that mode's approximate division and reciprocal.
-#include "prep_v_range.cuh"
+#include "prep_v_steps.cuh"
 
 namespace risa_b200 {
 namespace {
@@ -177,13 +177,28 @@ __global__ __launch_bounds__(256) void quantize_q_kernel(const QJob job) {
 // ------------------------------------------------------------------------------------------
 constexpr int k_threads(int d, int cta_k) { return d * cta_k / 64 < 128 ? 128 : d * cta_k / 64; }
 
+struct KJob {
+  const void* k;
+  int8_t* codes;
+  float* scales;
+  const int32_t* anchors;
+  int k_len, kv_heads, batch, tiles;
+  int64_t stride_b, stride_h, stride_n;
+  const int32_t* perm;
+};
+
+// One key tile by k_threads(D, CTA_K) consecutive threads.  `sub` is the index of that thread group
+// inside the CTA (0 when the CTA is exactly one group) and `tid` the thread's index inside the
+// group; groups of a CTA meet only at their own named barrier.
 template <typename T, int D, int CTA_K, int ROT>
-__global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
-    const T* __restrict__ k, int8_t* __restrict__ codes, float* __restrict__ scales,
-    const int32_t* __restrict__ anchors, int k_len, int kv_heads, int scales_per_head,
-    int64_t stride_b, int64_t stride_h, int64_t stride_n, const int32_t* __restrict__ perm) {
-  chain_wait();
-  chain_release();
+__device__ __forceinline__ void quantize_k_tile(const KJob& job, int tile, int h, int b, int sub,
+                                                int tid) {
+  const T* __restrict__ k = static_cast<const T*>(job.k);
+  int8_t* __restrict__ codes = job.codes;
+  float* __restrict__ scales = job.scales;
+  const int k_len = job.k_len, kv_heads = job.kv_heads, scales_per_head = job.tiles * 4;
+  const int64_t stride_b = job.stride_b, stride_h = job.stride_h, stride_n = job.stride_n;
+  const int32_t* __restrict__ perm = job.perm;
   constexpr int LPR = D / 16;
   constexpr int RPP = 32 / LPR;                 // rows per warp pass
   constexpr int THREADS = k_threads(D, CTA_K);  // at most 64 values per lane
@@ -193,10 +208,9 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
   constexpr int RW = GROUP_ROWS / WPG;          // rows per warp
   constexpr int PASSES = RW / RPP;
   static_assert(PASSES >= 1 && PASSES * RPP == RW, "tile geometry");
-  __shared__ float warp_max[4][WPG];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ float warp_max[512 / THREADS][4][WPG];
+  const int lane = tid & 31, warp = tid >> 5;
   const int w = warp % 4, s = warp / 4;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const T* in = k + b * stride_b + h * stride_h;
   const int64_t bh = static_cast<int64_t>(b) * kv_heads + h;
   int8_t* out = codes + bh * k_len * D;
@@ -206,7 +220,7 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
   float bias[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-  const int anchor = __ldg(anchors + bh);
+  const int anchor = __ldg(job.anchors + bh);
   if (anchor >= 0) {
     const int64_t src = row_map ? __ldg(row_map + anchor) : anchor;
     load16(in + src * stride_n + chunk * 16, bias);
@@ -237,10 +251,10 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   if constexpr (WPG > 1) {
-    if (lane == 0) warp_max[w][s] = mx;
-    __syncthreads();
+    if (lane == 0) warp_max[sub][w][s] = mx;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + sub), "r"(THREADS) : "memory");
 #pragma unroll
-    for (int i = 0; i < WPG; ++i) mx = fmaxf(mx, warp_max[w][i]);
+    for (int i = 0; i < WPG; ++i) mx = fmaxf(mx, warp_max[sub][w][i]);
   }
   const float sc = mx / 127.f + 1e-7f;
   const float inv = 1.f / sc;
@@ -249,6 +263,40 @@ __global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(
   for (int p = 0; p < PASSES; ++p)
     if (rows[p] < k_len)
       store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
+}
+
+// grid (key tiles, kv heads, batch), k_threads(D, CTA_K) threads.
+template <typename T, int D, int CTA_K, int ROT>
+__global__ __launch_bounds__(k_threads(D, CTA_K)) void quantize_k_kernel(const KJob job) {
+  chain_wait();
+  chain_release();
+  quantize_k_tile<T, D, CTA_K, ROT>(job, blockIdx.x, blockIdx.y, blockIdx.z, 0, threadIdx.x);
+}
+
+// The two steps that need the results of the first launch -- K quantisation (anchors) and the V
+// code step (ranges) -- as one launch of 512-thread CTAs: CTAs [0, V CTAs) are CTAs of the tiled V
+// code step (they run longest), each of the rest holds 512 / k_threads key tiles, one per thread
+// group.
+template <typename T, int D, int CTA_K, int ROT, bool AFFINE>
+__global__ __launch_bounds__(kTiledThreads) void quantize_k_v_codes_kernel(const KJob k_job,
+                                                                            const VCodesJob v_job) {
+  chain_wait();
+  chain_release();
+  const int v_columns = v_job.slots / kTiledSlots;
+  const int v_blocks = v_columns * (v_job.batch * v_job.kv_heads * v_job.head_dim / kTiledChannels);
+  int block = blockIdx.x;
+  if (block < v_blocks) {
+    v_codes_tiled_block<T, AFFINE>(v_job, block % v_columns, block / v_columns);
+    return;
+  }
+  block -= v_blocks;
+  constexpr int THREADS = k_threads(D, CTA_K);
+  constexpr int SUBS = kTiledThreads / THREADS;
+  const int sub = threadIdx.x / THREADS, tid = threadIdx.x % THREADS;
+  const int item = block * SUBS + sub;  // (batch, head, tile), tile fastest
+  if (item >= k_job.tiles * k_job.kv_heads * k_job.batch) return;
+  const int tile = item % k_job.tiles, bh = item / k_job.tiles;
+  quantize_k_tile<T, D, CTA_K, ROT>(k_job, tile, bh % k_job.kv_heads, bh / k_job.kv_heads, sub, tid);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -429,33 +477,39 @@ void launch_q(const QJob& q_job, const AnchorJob& anchor_job, const VRangeJob* r
   }
 }
 
+// Second launch: the K quantiser, together with the V code step when one is handed in.
 template <typename T, int D, int CTA_K, int ROT>
-void launch_k(const void* k, void* codes, float* scales, const int32_t* anchors, int batch,
-              int heads, int k_len, int64_t sb, int64_t sh, int64_t sn, const int32_t* perm,
-              cudaStream_t stream) {
-  const int tiles = (k_len + CTA_K - 1) / CTA_K;
-  launch_chained(quantize_k_kernel<T, D, CTA_K, ROT>, dim3(tiles, heads, batch),
-                 dim3(k_threads(D, CTA_K)), 0, stream, static_cast<const T*>(k),
-                 static_cast<int8_t*>(codes), scales, anchors, k_len, heads, tiles * 4, sb, sh, sn,
-                 perm);
+void launch_k(KJob k_job, const VCodesJob* codes_job, cudaStream_t stream) {
+  k_job.tiles = (k_job.k_len + CTA_K - 1) / CTA_K;
+  if (codes_job) {
+    constexpr int SUBS = kTiledThreads / k_threads(D, CTA_K);
+    const int k_items = k_job.tiles * k_job.kv_heads * k_job.batch;
+    const int v_blocks = codes_job->slots / kTiledSlots *
+                         (codes_job->batch * codes_job->kv_heads * codes_job->head_dim /
+                          kTiledChannels);
+    const dim3 grid(v_blocks + (k_items + SUBS - 1) / SUBS);
+    if (codes_job->midpoint_affine)
+      launch_chained(quantize_k_v_codes_kernel<T, D, CTA_K, ROT, true>, grid, dim3(kTiledThreads), 0,
+                     stream, k_job, *codes_job);
+    else
+      launch_chained(quantize_k_v_codes_kernel<T, D, CTA_K, ROT, false>, grid, dim3(kTiledThreads),
+                     0, stream, k_job, *codes_job);
+  } else {
+    launch_chained(quantize_k_kernel<T, D, CTA_K, ROT>, dim3(k_job.tiles, k_job.kv_heads, k_job.batch),
+                   dim3(k_threads(D, CTA_K)), 0, stream, k_job);
+  }
 }
 
 template <typename T, int D, int ROT>
-void launch_qk(QJob q_job, const AnchorJob& anchor_job, const VRangeJob* range_job, void* kc,
-               float* ks, int cta_k, cudaStream_t stream) {
+void launch_qk(QJob q_job, const AnchorJob& anchor_job, const VRangeJob* range_job,
+               const KJob& k_job, const VCodesJob* codes_job, int cta_k, cudaStream_t stream) {
   q_job.scales_per_head = q_job.blocks * (D == 256 ? 64 : 32);
   launch_q<T, D, ROT>(q_job, anchor_job, range_job, stream);
-  const AnchorJob& a = anchor_job;
   if constexpr (D == 64) {
-    launch_k<T, D, 64, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
-                            a.stride_h, a.stride_n, a.perm, stream);
+    launch_k<T, D, 64, ROT>(k_job, codes_job, stream);
   } else {
-    if (cta_k == 128)
-      launch_k<T, D, 128, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
-                               a.stride_h, a.stride_n, a.perm, stream);
-    else
-      launch_k<T, D, 64, ROT>(a.k, kc, ks, a.anchors, a.batch, a.kv_heads, a.k_len, a.stride_b,
-                              a.stride_h, a.stride_n, a.perm, stream);
+    if (cta_k == 128) launch_k<T, D, 128, ROT>(k_job, codes_job, stream);
+    else launch_k<T, D, 64, ROT>(k_job, codes_job, stream);
   }
 }
 
@@ -464,14 +518,14 @@ void launch_qk(QJob q_job, const AnchorJob& anchor_job, const VRangeJob* range_j
 
 using namespace risa_b200;
 
-int risa_b200::quantize_qk_with_range(const void* q, void* q_codes, float* q_scale, const void* k,
+int risa_b200::quantize_qk_with_v_steps(const void* q, void* q_codes, float* q_scale, const void* k,
                                       void* k_codes, float* k_scale, int batch, int q_heads,
                                       int q_len, int kv_heads, int k_len, int head_dim, int cta_k,
                                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
                                       int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
                                       int dtype_code, int32_t* anchors, const int32_t* q_perm,
                                       const int32_t* k_perm, const VRangeJob* range_job,
-                                      void* stream_ptr) {
+                                      const VCodesJob* codes_job, void* stream_ptr) {
   RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
                "quantize_qk: padded head_dim must be 64, 128, or 256");
   RISA_REQUIRE((cta_k == 64 || cta_k == 128) && !(head_dim == 64 && cta_k != 64),
@@ -519,8 +573,21 @@ int risa_b200::quantize_qk_with_range(const void* q, void* q_codes, float* q_sca
   anchor_job.stride_h = k_stride_h;
   anchor_job.stride_n = k_stride_n;
   anchor_job.perm = k_perm;
+  KJob k_job;
+  k_job.k = k;
+  k_job.codes = static_cast<int8_t*>(k_codes);
+  k_job.scales = k_scale;
+  k_job.anchors = anchors;
+  k_job.k_len = k_len;
+  k_job.kv_heads = kv_heads;
+  k_job.batch = batch;
+  k_job.tiles = 0;  // set per key-tile width by launch_k
+  k_job.stride_b = k_stride_b;
+  k_job.stride_h = k_stride_h;
+  k_job.stride_n = k_stride_n;
+  k_job.perm = k_perm;
 #define RISA_QK(D, ROT) \
-  launch_qk<T, D, ROT>(q_job, anchor_job, range_job, k_codes, k_scale, cta_k, stream)
+  launch_qk<T, D, ROT>(q_job, anchor_job, range_job, k_job, codes_job, cta_k, stream)
   const bool h4_only = k_len <= 256;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
     if (head_dim == 64) {
@@ -542,14 +609,15 @@ extern "C" int risa_b200_quantize_qk(const void* q, void* q_codes, float* q_scal
                                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
                                      int dtype_code, int32_t* anchors, const int32_t* q_perm,
                                      const int32_t* k_perm, void* stream_ptr) {
-  return quantize_qk_with_range(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
-                                kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
-                                q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code, anchors,
-                                q_perm, k_perm, nullptr, stream_ptr);
+  return quantize_qk_with_v_steps(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
+                                  kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
+                                  q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code,
+                                  anchors, q_perm, k_perm, nullptr, nullptr, stream_ptr);
 }
 
-// Q, K and V of one call.  Same kernels and results as risa_b200_quantize_qk followed by
-// risa_b200_quantize_v; the V range step travels in the first launch (see quantize_q_scan_kernel).
+// Q, K and V of one call.  Same results as risa_b200_quantize_qk followed by risa_b200_quantize_v;
+// the V range step travels in the first launch (quantize_q_scan_kernel) and, for key lengths and
+// buffers the tiled code step accepts, the V code step in the second (quantize_k_v_codes_kernel).
 extern "C" int risa_b200_quantize_qkv(
     const void* q, void* q_codes, float* q_scale, const void* k, void* k_codes, float* k_scale,
     const void* v, void* v_codes, float* v_scale, float* v_center, int batch, int q_heads,
@@ -560,16 +628,20 @@ extern "C" int risa_b200_quantize_qkv(
     const int32_t* q_perm, const int32_t* kv_perm, void* workspace, size_t workspace_bytes,
     void* stream_ptr) {
   VRangeJob range_job;
-  int status = v_range_job(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
-                           padded_len, v_stride_b, v_stride_h, v_stride_n, dtype_code, kv_perm,
-                           workspace, workspace_bytes, &range_job);
+  VCodesJob codes_job;
+  int status = v_quantize_jobs(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
+                               padded_len, v_stride_b, v_stride_h, v_stride_n, dtype_code,
+                               midpoint_affine, kv_perm, workspace, workspace_bytes, &range_job,
+                               &codes_job);
   if (status != RISA_B200_OK) return status;
-  status = quantize_qk_with_range(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
-                                  kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
-                                  q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code,
-                                  anchors, q_perm, kv_perm, &range_job, stream_ptr);
+  const bool codes_fused = codes_job.v != nullptr;
+  status = quantize_qk_with_v_steps(q, q_codes, q_scale, k, k_codes, k_scale, batch, q_heads, q_len,
+                                    kv_heads, k_len, head_dim, cta_k, q_stride_b, q_stride_h,
+                                    q_stride_n, k_stride_b, k_stride_h, k_stride_n, dtype_code,
+                                    anchors, q_perm, kv_perm, &range_job,
+                                    codes_fused ? &codes_job : nullptr, stream_ptr);
   if (status != RISA_B200_OK) return status;
   return quantize_v_after_range(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
                                 padded_len, v_stride_b, v_stride_h, v_stride_n, dtype_code,
-                                midpoint_affine, kv_perm, workspace, stream_ptr);
+                                midpoint_affine, kv_perm, workspace, codes_fused, stream_ptr);
 }

@@ -13,20 +13,13 @@
 //                chunk ranges itself, writes codes and its slots' residual sums;
 //   3. finish:   (midpoint-affine only) combines the residual sums in the reference order.
 // Compiled with --use_fast_math like the reference so 1.f / x and x / float(L) lower identically.
-#include "prep_v_range.cuh"
+#include "prep_v_steps.cuh"
 #include <mutex>
 
 namespace risa_b200 {
 namespace {
 
 constexpr int kSlotsPerCta = 128;  // residual-order slots per quantise CTA
-
-__device__ __forceinline__ int storage_position(int token) {
-  // token bits {b3,b2,b1,b0} -> storage bits {b2,b0,b3,b1}: order 0,1,8,9,2,3,10,11,...
-  const int w = token & 15;
-  return (token & ~15) | (w & 1) | (((w >> 3) & 1) << 1) | (((w >> 1) & 1) << 2) |
-         (((w >> 2) & 1) << 3);
-}
 
 // grid (chunks, Hkv, B), 256 threads.
 template <typename T>
@@ -117,146 +110,12 @@ __global__ __launch_bounds__(kSlotsPerCta) void v_quantize_kernel(
   }
 }
 
-// Same work as v_quantize_kernel for key lengths that are a multiple of 16, organised for the memory
-// system: a CTA owns 32 consecutive slots x 64 channels (thread = one slot, four channels), so a
-// half-warp reads one token's 64 channels as one contiguous segment, and the codes of a 32-token
-// window go through shared memory to leave as 16-byte stores (one aligned 16-token storage group
-// of one channel each) instead of single bytes.  Each (slot, channel) residual is still summed by
-// one thread over tokens Lk-1-slot, Lk-1-slot-slots, ... in that order.
 // grid (slots / 32, B*Hkv*D / 64), 512 threads.
-constexpr int kTiledSlots = 32, kTiledChannels = 64, kTiledThreads = 512;
-
 template <typename T, bool AFFINE>
-__global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(
-    const T* __restrict__ v, int8_t* __restrict__ out, float* __restrict__ scale_out,
-    float* __restrict__ center_out, const float2* __restrict__ ranges,
-    float* __restrict__ residuals, int k_len, int padded_len, int kv_heads, int head_dim,
-    int chunks, int slots, int64_t stride_b, int64_t stride_h, int64_t stride_n,
-    const int32_t* __restrict__ perm) {
+__global__ __launch_bounds__(kTiledThreads) void v_quantize_tiled_kernel(const VCodesJob job) {
   chain_wait();
   chain_release();
-  __shared__ float s_inv[kTiledChannels], s_center[kTiledChannels];
-  // 32 positions per channel; a row pitch of 36 bytes (9 words) spreads the 16 channel quads of a
-  // half-warp over 8 banks (any pitch that is a multiple of 16 bytes would put them on 2)
-  __shared__ __align__(4) unsigned char s_tile[2][kTiledChannels][36];
-  const int d_tiles = head_dim / kTiledChannels;
-  const int d_tile = blockIdx.y % d_tiles, bh = blockIdx.y / d_tiles;
-  const int h = bh % kv_heads, b = bh / kv_heads;
-  const int d0 = d_tile * kTiledChannels;
-  const int sl = threadIdx.x >> 4, quad = threadIdx.x & 15;
-  const int slot = blockIdx.x * kTiledSlots + sl;
-  const T* in = v + b * stride_b + h * stride_h + d0 + 4 * quad;
-  const int32_t* row_map = perm ? perm + static_cast<int64_t>(bh) * k_len : nullptr;
-  const int64_t out_row = static_cast<int64_t>(bh) * head_dim + d0;
-
-  // channel range = min / max over the per-chunk partials: spread over the whole CTA (eight chunk
-  // subsets per channel) so that the loads overlap instead of forming one long dependent loop
-  __shared__ float s_lo[kTiledThreads / kTiledChannels][kTiledChannels];
-  __shared__ float s_hi[kTiledThreads / kTiledChannels][kTiledChannels];
-  {
-    const int channel = threadIdx.x % kTiledChannels, part = threadIdx.x / kTiledChannels;
-    float lo = FLT_MAX, hi = -FLT_MAX;
-    const float2* r = ranges + static_cast<int64_t>(bh) * chunks * head_dim + d0 + channel;
-    for (int c = part; c < chunks; c += kTiledThreads / kTiledChannels) {
-      const float2 x = __ldg(r + static_cast<int64_t>(c) * head_dim);
-      lo = fminf(lo, x.x);
-      hi = fmaxf(hi, x.y);
-    }
-    s_lo[part][channel] = lo;
-    s_hi[part][channel] = hi;
-  }
-  __syncthreads();
-  if (threadIdx.x < kTiledChannels) {
-    float lo = FLT_MAX, hi = -FLT_MAX;
-#pragma unroll
-    for (int part = 0; part < kTiledThreads / kTiledChannels; ++part) {
-      lo = fminf(lo, s_lo[part][threadIdx.x]);
-      hi = fmaxf(hi, s_hi[part][threadIdx.x]);
-    }
-    float center, radius;
-    if constexpr (AFFINE) {
-      center = 0.5f * (lo + hi);
-      radius = 0.5f * (hi - lo);
-    } else {
-      center = 0.0f;
-      radius = fmaxf(fabsf(lo), fabsf(hi));
-    }
-    const float sc = fmaxf(radius * (1.f / 127.f), 1e-12f);
-    s_inv[threadIdx.x] = 1.f / sc;
-    s_center[threadIdx.x] = center;
-    if (blockIdx.x == 0) {
-      scale_out[out_row + threadIdx.x] = sc;
-      if constexpr (!AFFINE) center_out[out_row + threadIdx.x] = 0.0f;
-    }
-  }
-  __syncthreads();
-  float inv[4], center[4], residual[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    inv[i] = s_inv[4 * quad + i];
-    center[i] = s_center[4 * quad + i];
-    residual[i] = 0.f;
-  }
-  // Window of iteration `it`: tokens [hi - 31, hi], hi = k_len - 1 - 32 * blockIdx.x - slots * it;
-  // with k_len a multiple of 16 the window is two aligned 16-token storage groups.
-  const int first_hi = k_len - 1 - blockIdx.x * kTiledSlots;
-  int buffer = 0;
-  // The loads of kBatch consecutive windows are issued together (a token's row is only read once,
-  // so nothing but the number of loads in flight hides the memory latency), then the windows are
-  // converted and written one after the other.
-  constexpr int kBatch = 8;
-  for (int batch_hi = first_hi; batch_hi >= 0; batch_hi -= kBatch * slots) {
-    float t[kBatch][4];
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int src = batch_hi - u * slots - sl;
-      if (src >= 0) {
-        const int64_t row = row_map ? __ldg(row_map + src) : src;
-        Load4<T>::load(in + row * stride_n, t[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int hi = batch_hi - u * slots;
-      if (hi < 0) break;  // uniform over the CTA
-      const int lo = hi - (kTiledSlots - 1);
-      const int src = hi - sl;
-      if (src >= 0) {
-        const int position = storage_position(src) - lo;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float normalized = (t[u][i] - center[i]) * inv[i];
-          const uint32_t code = to_s8(normalized);
-          s_tile[buffer][4 * quad + i][position] = static_cast<unsigned char>(code);
-          if constexpr (AFFINE)
-            residual[i] += normalized - static_cast<float>(static_cast<int8_t>(code));
-        }
-      }
-      __syncthreads();  // the other buffer was read before the previous barrier: safe to refill
-      if (threadIdx.x < 2 * kTiledChannels) {
-        const int channel = threadIdx.x >> 1, group = threadIdx.x & 1;
-        const int base = lo + 16 * group;
-        if (base >= 0) {
-          const uint32_t* w = reinterpret_cast<const uint32_t*>(&s_tile[buffer][channel][16 * group]);
-          *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + base) =
-              make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      buffer ^= 1;
-    }
-  }
-  if constexpr (AFFINE) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      residuals[(out_row + 4 * quad + i) * slots + slot] = residual[i];
-  }
-  // zero tail [k_len, padded_len): whole 16-byte groups because k_len is a multiple of 16
-  for (int idx = blockIdx.x * kTiledThreads + threadIdx.x;
-       idx < kTiledChannels * ((padded_len - k_len) / 16); idx += gridDim.x * kTiledThreads) {
-    const int channel = idx % kTiledChannels, group = idx / kTiledChannels;
-    *reinterpret_cast<uint4*>(out + (out_row + channel) * padded_len + k_len + 16 * group) =
-        make_uint4(0u, 0u, 0u, 0u);
-  }
+  v_codes_tiled_block<T, AFFINE>(job, blockIdx.x, blockIdx.y);
 }
 
 // grid (B*Hkv*D), `slots` threads: xor butterfly per warp, warps added in order by thread 0.
@@ -323,11 +182,21 @@ extern "C" size_t risa_b200_quantize_v_workspace_size(int batch, int kv_heads, i
   return p.range_bytes + p.residual_bytes;
 }
 
-int risa_b200::v_range_job(const void* v, void* v_codes, float* v_scale, float* v_center,
-                           int batch, int kv_heads, int k_len, int head_dim, int padded_len,
-                           int64_t stride_b, int64_t stride_h, int64_t stride_n, int dtype_code,
-                           const int32_t* perm, void* workspace, size_t workspace_bytes,
-                           VRangeJob* job) {
+namespace {
+// 16-byte code stores need whole storage groups and an aligned destination; a CTA of the tiled
+// kernel owns kTiledChannels channels of one head, so the head must split into whole groups.
+bool tiled_form(const void* v_codes, int k_len, int head_dim) {
+  return k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0 &&
+         head_dim % kTiledChannels == 0;
+}
+}  // namespace
+
+int risa_b200::v_quantize_jobs(const void* v, void* v_codes, float* v_scale, float* v_center,
+                               int batch, int kv_heads, int k_len, int head_dim, int padded_len,
+                               int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                               int dtype_code, int midpoint_affine, const int32_t* perm,
+                               void* workspace, size_t workspace_bytes, VRangeJob* range,
+                               VCodesJob* codes) {
   RISA_REQUIRE(v && v_codes && v_scale && v_center, "quantize_v: null tensor");
   RISA_REQUIRE(batch > 0 && kv_heads > 0 && k_len > 0, "quantize_v: sizes must be positive");
   RISA_REQUIRE(head_dim > 0 && head_dim % 8 == 0 && head_dim <= 256,
@@ -348,64 +217,85 @@ int risa_b200::v_range_job(const void* v, void* v_codes, float* v_scale, float* 
                "quantize_v: workspace of %zu bytes required", p.range_bytes + p.residual_bytes);
   RISA_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0,
                "quantize_v: workspace must be 16-byte aligned");
-  job->v = v;
-  job->ranges = static_cast<float2*>(workspace);
-  job->k_len = k_len;
-  job->head_dim = head_dim;
-  job->kv_heads = kv_heads;
-  job->batch = batch;
-  job->chunks = p.chunks;
-  job->stride_b = stride_b;
-  job->stride_h = stride_h;
-  job->stride_n = stride_n;
-  job->perm = perm;
+  range->v = v;
+  range->ranges = static_cast<float2*>(workspace);
+  range->k_len = k_len;
+  range->head_dim = head_dim;
+  range->kv_heads = kv_heads;
+  range->batch = batch;
+  range->chunks = p.chunks;
+  range->stride_b = stride_b;
+  range->stride_h = stride_h;
+  range->stride_n = stride_n;
+  range->perm = perm;
+  codes->v = nullptr;
+  if (tiled_form(v_codes, k_len, head_dim)) {
+    codes->v = v;
+    codes->out = static_cast<int8_t*>(v_codes);
+    codes->scale_out = v_scale;
+    codes->center_out = v_center;
+    codes->ranges = range->ranges;
+    codes->residuals = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.range_bytes);
+    codes->k_len = k_len;
+    codes->padded_len = padded_len;
+    codes->kv_heads = kv_heads;
+    codes->head_dim = head_dim;
+    codes->batch = batch;
+    codes->chunks = p.chunks;
+    codes->slots = p.slots;
+    codes->stride_b = stride_b;
+    codes->stride_h = stride_h;
+    codes->stride_n = stride_n;
+    codes->perm = perm;
+    codes->midpoint_affine = midpoint_affine;
+  }
   return RISA_B200_OK;
 }
 
-// Everything after the range step; the arguments were checked by v_range_job().
+// Everything after the range step; the arguments were checked by v_quantize_jobs().
 int risa_b200::quantize_v_after_range(const void* v, void* v_codes, float* v_scale,
                                       float* v_center, int batch, int kv_heads, int k_len,
                                       int head_dim, int padded_len, int64_t stride_b,
                                       int64_t stride_h, int64_t stride_n, int dtype_code,
                                       int midpoint_affine, const int32_t* perm, void* workspace,
-                                      void* stream_ptr) {
+                                      bool codes_done, void* stream_ptr) {
   const VPlan p = plan(batch, kv_heads, k_len, head_dim);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   float2* ranges = static_cast<float2*>(workspace);
   float* residuals = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.range_bytes);
   const int channels = batch * kv_heads * head_dim;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
-    const dim3 tiled_grid(p.slots / kTiledSlots, channels / kTiledChannels);
-    // 16-byte code stores need whole storage groups and an aligned destination; a CTA of the tiled
-    // kernel owns kTiledChannels channels of one head, so the head must split into whole groups
-    const bool tiled = k_len % 16 == 0 && reinterpret_cast<uintptr_t>(v_codes) % 16 == 0 &&
-                       head_dim % kTiledChannels == 0;
-    if (tiled && midpoint_affine) {
-      launch_chained(v_quantize_tiled_kernel<T, true>, tiled_grid, dim3(kTiledThreads), 0, stream,
-          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
-          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
-          stride_n, perm);
-      launch_chained(v_center_kernel, dim3(channels), dim3(p.slots), 0, stream, residuals, ranges,
-                     v_center, k_len, head_dim, p.chunks, p.slots);
-    } else if (tiled) {
-      launch_chained(v_quantize_tiled_kernel<T, false>, tiled_grid, dim3(kTiledThreads), 0, stream,
-          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
-          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
-          stride_n, perm);
-    } else if (midpoint_affine) {
-      launch_chained(v_quantize_kernel<T, true>, grid, dim3(kSlotsPerCta), 0, stream,
-          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
-          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
-          stride_n, perm);
-      launch_chained(v_center_kernel, dim3(channels), dim3(p.slots), 0, stream, residuals, ranges,
-                     v_center, k_len, head_dim, p.chunks, p.slots);
+    if (codes_done) {
+      // the code step has run next to the K quantiser
+    } else if (tiled_form(v_codes, k_len, head_dim)) {
+      VRangeJob range;
+      VCodesJob codes;
+      v_quantize_jobs(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim, padded_len,
+                      stride_b, stride_h, stride_n, dtype_code, midpoint_affine, perm, workspace,
+                      p.range_bytes + p.residual_bytes, &range, &codes);
+      const dim3 tiled_grid(p.slots / kTiledSlots, channels / kTiledChannels);
+      if (midpoint_affine)
+        launch_chained(v_quantize_tiled_kernel<T, true>, tiled_grid, dim3(kTiledThreads), 0, stream,
+                       codes);
+      else
+        launch_chained(v_quantize_tiled_kernel<T, false>, tiled_grid, dim3(kTiledThreads), 0,
+                       stream, codes);
     } else {
-      launch_chained(v_quantize_kernel<T, false>, grid, dim3(kSlotsPerCta), 0, stream,
-          static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
-          residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b, stride_h,
-          stride_n, perm);
+      const dim3 grid(p.slots / kSlotsPerCta, channels / 8);
+      if (midpoint_affine)
+        launch_chained(v_quantize_kernel<T, true>, grid, dim3(kSlotsPerCta), 0, stream,
+            static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
+            residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b,
+            stride_h, stride_n, perm);
+      else
+        launch_chained(v_quantize_kernel<T, false>, grid, dim3(kSlotsPerCta), 0, stream,
+            static_cast<const T*>(v), static_cast<int8_t*>(v_codes), v_scale, v_center, ranges,
+            residuals, k_len, padded_len, kv_heads, head_dim, p.chunks, p.slots, stride_b,
+            stride_h, stride_n, perm);
     }
+    if (midpoint_affine)
+      launch_chained(v_center_kernel, dim3(channels), dim3(p.slots), 0, stream, residuals, ranges,
+                     v_center, k_len, head_dim, p.chunks, p.slots);
   });
   return check_launch("quantize_v");
 }
@@ -416,18 +306,20 @@ extern "C" int risa_b200_quantize_v(const void* v, void* v_codes, float* v_scale
                                     int64_t stride_n, int dtype_code, int midpoint_affine,
                                     const int32_t* perm, void* workspace, size_t workspace_bytes,
                                     void* stream_ptr) {
-  VRangeJob job;
-  const int status =
-      v_range_job(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim, padded_len,
-                  stride_b, stride_h, stride_n, dtype_code, perm, workspace, workspace_bytes, &job);
+  VRangeJob range;
+  VCodesJob codes;
+  const int status = v_quantize_jobs(v, v_codes, v_scale, v_center, batch, kv_heads, k_len,
+                                     head_dim, padded_len, stride_b, stride_h, stride_n,
+                                     dtype_code, midpoint_affine, perm, workspace, workspace_bytes,
+                                     &range, &codes);
   if (status != RISA_B200_OK) return status;
   RISA_DISPATCH_FLOAT(dtype_code, T, {
-    launch_chained(v_range_kernel<T>, dim3(job.chunks, kv_heads, batch), dim3(kRangeThreads), 0,
-                   static_cast<cudaStream_t>(stream_ptr), job);
+    launch_chained(v_range_kernel<T>, dim3(range.chunks, kv_heads, batch), dim3(kRangeThreads), 0,
+                   static_cast<cudaStream_t>(stream_ptr), range);
   });
   return quantize_v_after_range(v, v_codes, v_scale, v_center, batch, kv_heads, k_len, head_dim,
                                 padded_len, stride_b, stride_h, stride_n, dtype_code,
-                                midpoint_affine, perm, workspace, stream_ptr);
+                                midpoint_affine, perm, workspace, false, stream_ptr);
 }
 
 // ---- allocation-free variant --------------------------------------------------------------------
