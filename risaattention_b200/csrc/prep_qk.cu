@@ -134,32 +134,41 @@ __device__ __forceinline__ void quantize_q_block(const QJob& job, int blk, int h
   const int j = (lane % GLANES) / LPR;      // row inside the group
   const int chunk = lane % LPR;             // 16-channel chunk inside the row
 
-  float v[PASSES][16];
-  int rows[PASSES];
+  // Passes are independent (a scale group lives inside one pass); they are taken kBatch at a time so
+  // that a thread holds kBatch * 16 values instead of all of them: fewer registers, more resident
+  // CTAs whose load and arithmetic phases overlap one another.
+  constexpr int kBatch = 2;
+  static_assert(PASSES % kBatch == 0, "pass batching");
+#pragma unroll 1
+  for (int p0 = 0; p0 < PASSES; p0 += kBatch) {
+    float v[kBatch][16];
+    int rows[kBatch];
 #pragma unroll
-  for (int p = 0; p < PASSES; ++p) {
-    const int group = (warp * PASSES + p) * GPP + slot;  // 0..GROUPS-1 == tile*8 + o
-    const int row = blk * 128 + (group >> 3) * TILE_ROWS + (group & 7) + 8 * j;
-    rows[p] = row;
+    for (int p = 0; p < kBatch; ++p) {
+      const int group = (warp * PASSES + p0 + p) * GPP + slot;  // 0..GROUPS-1 == tile*8 + o
+      const int row = blk * 128 + (group >> 3) * TILE_ROWS + (group & 7) + 8 * j;
+      rows[p] = row;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[p][i] = 0.f;
-    if (row < q_len) {
-      const int64_t src = row_map ? __ldg(row_map + row) : row;
-      load16(in + src * stride_n + chunk * 16, v[p]);
+      for (int i = 0; i < 16; ++i) v[p][i] = 0.f;
+      if (row < q_len) {
+        const int64_t src = row_map ? __ldg(row_map + row) : row;
+        load16(in + src * stride_n + chunk * 16, v[p]);
+      }
     }
-  }
 #pragma unroll
-  for (int p = 0; p < PASSES; ++p) {
-    rotate16<ROT>(v[p], D == 256 ? (chunk & 7) : chunk);
-    float mx = absmax16(v[p]);
+    for (int p = 0; p < kBatch; ++p) {
+      rotate16<ROT>(v[p], D == 256 ? (chunk & 7) : chunk);
+      float mx = absmax16(v[p]);
 #pragma unroll
-    for (int off = GLANES / 2; off > 0; off >>= 1)
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    const float sc = mx / 127.f + 1e-7f;
-    const float inv = 1.f / sc;
-    const int group = (warp * PASSES + p) * GPP + slot;
-    if ((lane % GLANES) == 0) sc_out[group] = sc;
-    if (rows[p] < q_len) store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
+      for (int off = GLANES / 2; off > 0; off >>= 1)
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float sc = mx / 127.f + 1e-7f;
+      const float inv = 1.f / sc;
+      const int group = (warp * PASSES + p0 + p) * GPP + slot;
+      if ((lane % GLANES) == 0) sc_out[group] = sc;
+      if (rows[p] < q_len)
+        store16_codes(out + static_cast<int64_t>(rows[p]) * D + chunk * 16, v[p], inv);
+    }
   }
 }
 
@@ -434,7 +443,7 @@ __global__ __launch_bounds__(128) void detect_anchor_kernel(const AnchorJob job)
 // the next ones take V range chunks, the rest quantise Q blocks.  The detector comes first because
 // it is one long dependent chain per head; the Q blocks fill the GPU behind it.
 template <typename T, int D, int ROT>
-__global__ __launch_bounds__(256) void quantize_q_scan_kernel(const QJob q_job,
+__global__ __launch_bounds__(256, 4) void quantize_q_scan_kernel(const QJob q_job,
                                                               const AnchorJob anchor_job,
                                                               const VRangeJob range_job) {
   chain_wait();

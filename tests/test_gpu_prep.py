@@ -35,6 +35,8 @@ CASES = [
     (256, 200, 1153, 128, 4, 2),
     (128, 100, 100, 64, 2, 2),     # H4 with D128
     (256, 33, 64, 64, 2, 1),
+    (128, 128, 8192, 128, 2, 1),   # tiled V code pass, 16 windows per slot
+    (64, 64, 16400, 64, 2, 2),     # ... 33 windows, the last one short
 ]
 
 
