@@ -87,7 +87,7 @@ int run_attention(
     int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
     int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
     float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles,
-    void* stream_ptr, const SelectRequest* select) {
+    void* stream_ptr, const SelectRequest* select, float* tail_scratch = nullptr) {
   RISA_REQUIRE(cta_k == 64 || cta_k == 128, "risa_attention: cta_k must be 64 or 128");
   RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
                "risa_attention: unsupported head_dim");
@@ -144,6 +144,7 @@ int run_attention(
   a.block_mass = block_mass;
   a.is_causal = is_causal != 0;
   a.lse = lse;
+  a.tail_scratch = tail_scratch;  // kTailScratchBytes of the caller's, or null: no split tail
   a.key_mask_tiles = (mask != nullptr && mask_stride_q == 0 && !sparse_row_offsets &&
                       !block_mass && !is_causal)
                          ? key_mask_tiles
@@ -261,7 +262,8 @@ extern "C" int risa_b200_attention_select(
 namespace {
 
 struct DenseScratch {
-  size_t q_codes, k_codes, v_codes, q_scale, k_scale, v_scale, v_center, anchors, v_work, total;
+  size_t q_codes, k_codes, v_codes, q_scale, k_scale, v_scale, v_center, anchors, v_work, tail,
+      total;
 };
 
 constexpr size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
@@ -282,6 +284,7 @@ DenseScratch dense_scratch_layout(int batch, int q_heads, int q_len, int kv_head
   s.v_center = take(channels * sizeof(float));
   s.anchors = take(size_t(batch) * kv_heads * sizeof(int32_t));
   s.v_work = take(risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim));
+  s.tail = take(kTailScratchBytes);  // parts of a split last wave (attention_tc.cu)
   s.total = at;
   return s;
 }
@@ -324,11 +327,11 @@ extern "C" int risa_b200_dense_attention(
       v_center, batch, q_heads, q_len, kv_heads, k_len, head_dim, cta_k, padded, q_stride_b,
       q_stride_h, q_stride_n, k_stride_b, k_stride_h, k_stride_n, v_stride_b, v_stride_h,
       v_stride_n, dtype_code, midpoint_affine, reinterpret_cast<int32_t*>(base + s.anchors),
-      nullptr, nullptr, base + s.v_work, s.total - s.v_work, stream);
+      nullptr, nullptr, base + s.v_work, s.tail - s.v_work, stream);
   if (status != RISA_B200_OK) return status;
-  return risa_b200_attention(base + s.q_codes, base + s.k_codes, base + s.v_codes, o, q_scale,
-                             k_scale, v_scale, v_center, nullptr, 0, 0, 0, 0, -1, cta_k, batch,
-                             q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
-                             o_stride_h, sm_scale, out_dtype_code, nullptr, nullptr, nullptr,
-                             is_causal, nullptr, nullptr, stream);
+  return run_attention(base + s.q_codes, base + s.k_codes, base + s.v_codes, o, q_scale, k_scale,
+                       v_scale, v_center, nullptr, 0, 0, 0, 0, -1, cta_k, batch, q_len, k_len,
+                       q_heads, kv_heads, head_dim, o_stride_b, o_stride_n, o_stride_h, sm_scale,
+                       out_dtype_code, nullptr, nullptr, nullptr, is_causal, nullptr, nullptr,
+                       stream, nullptr, reinterpret_cast<float*>(base + s.tail));
 }

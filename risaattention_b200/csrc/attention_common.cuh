@@ -36,10 +36,21 @@ struct AttentionArgs {
   int32_t* select_counts;    // [B*Hq*n_q] tiles kept per row
   uint32_t* select_bitmaps;  // [B*Hq*n_q, ceil(n_k / 32)] kept tiles as bits
   double* select_totals;     // [B*Hq*n_q, 2] kept mass, total mass
+  // Key-range split of the last, partial wave of CTAs (tensor-core kernel, dense unmasked calls):
+  // CTAs from linear index tail_begin on are replaced by tail_splits CTAs each, every one taking a
+  // contiguous share of the key tiles and leaving its unnormalised output rows, maximum and
+  // denominator in tail_scratch ([tail CTA][part][130][128] floats); a merge launch combines them.
+  // tail_splits <= 1: off.
+  int tail_begin, tail_splits;
+  float* tail_scratch;
   // 2^8 and 2^16 as run-time values for the multiply-add packing of probability codes
   // (softmax_row.cuh, MAD_PACK)
   uint32_t pack_by256, pack_by65536;
 };
+
+// Capacity of AttentionArgs::tail_scratch in parts (one part = 130 x 128 floats).
+constexpr int kTailScratchParts = 160;
+constexpr size_t kTailScratchBytes = size_t(kTailScratchParts) * 130 * 128 * sizeof(float);
 
 // Capture workspace (FP32 words), identical to the reference's (attention_int8.cuh:58-60,
 // 770-797, 871-895): block masses [B*Hq*n_q, n_k]; then for every query row and every visited tile

@@ -31,6 +31,7 @@
 #include "select.cuh"
 #include "tc_ptx.cuh"
 
+#include <algorithm>
 #include <climits>
 #include <cuda.h>
 #include <mutex>
@@ -116,21 +117,27 @@ struct TileSeq {
   const int32_t* ids;
   bool key_list;  // ids come from a key-mask tile list: the list may stop before the last key tile
   int n_k;
-  __device__ __forceinline__ int tile(int it) const { return ids ? __ldg(ids + it) : it; }
+  int first;      // without a list: the CTA visits tiles first .. first + n_iter - 1
+  bool open_end;  // the range stops before the last key tile (a key-range part of a split CTA)
+  __device__ __forceinline__ int tile(int it) const { return ids ? __ldg(ids + it) : first + it; }
   // The reference's generic last-visited-tile arithmetic applies on the last iteration, unless a
-  // key-mask list ends on a tile that is not the final key tile (attention_int8.cuh:552-566).
+  // key-mask list ends on a tile that is not the final key tile (attention_int8.cuh:552-566) or the
+  // CTA is a part of a split key range that does not hold the last tile.
   __device__ __forceinline__ bool last_rules(int it, int tile_id) const {
-    return it == n_iter - 1 && !(key_list && tile_id + 1 < n_k);
+    return it == n_iter - 1 && !open_end && !(key_list && tile_id + 1 < n_k);
   }
 };
 
 template <int CTA_K>
 __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t bh, int bx,
-                                                 int n_q, int n_k, bool capture) {
+                                                 int n_q, int n_k, bool capture, int part,
+                                                 int parts) {
   TileSeq s;
   s.ids = nullptr;
   s.key_list = false;
   s.n_k = n_k;
+  s.first = 0;
+  s.open_end = false;
   if (a.row_offsets) {
     const int64_t r = bh * n_q + bx;
     const int start = __ldg(a.row_offsets + r);
@@ -143,7 +150,9 @@ __device__ __forceinline__ TileSeq tile_sequence(const AttentionArgs& a, int64_t
   } else if (a.is_causal && !capture) {
     s.n_iter = (min(a.k_len, (bx + 1) * 128) + CTA_K - 1) / CTA_K;
   } else {
-    s.n_iter = n_k;
+    s.first = n_k * part / parts;
+    s.n_iter = n_k * (part + 1) / parts - s.first;
+    s.open_end = part + 1 < parts;
   }
   return s;
 }
@@ -474,10 +483,26 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2;
-  const int bx = blockIdx.x, head = blockIdx.y / L::kHalves, half = blockIdx.y % L::kHalves;
-  const int batch = blockIdx.z;
+  const int n_k = (a.k_len + CTA_K - 1) / CTA_K, n_q = (a.q_len + 127) / 128;
+  // Launch order is query block fastest, then (head, half), then batch.  With a split tail the grid
+  // is one-dimensional: CTAs before tail_begin are whole (query block, head) units, the rest come
+  // in groups of tail_splits parts of one unit each.
+  int bx = blockIdx.x, by = blockIdx.y, batch = blockIdx.z, part = 0, parts = 1, tail_unit = -1;
+  if (MODE == kDense && a.tail_splits > 1) {
+    int unit = blockIdx.x;
+    if (unit >= a.tail_begin) {
+      tail_unit = (unit - a.tail_begin) / a.tail_splits;
+      part = (unit - a.tail_begin) % a.tail_splits;
+      parts = a.tail_splits;
+      unit = a.tail_begin + tail_unit;
+    }
+    const int rows_y = a.q_heads * L::kHalves;
+    bx = unit % n_q;
+    by = (unit / n_q) % rows_y;
+    batch = unit / (n_q * rows_y);
+  }
+  const int head = by / L::kHalves, half = by % L::kHalves;
   const int kv_head = head / (a.q_heads / a.kv_heads);
-  const int n_k = (a.k_len + CTA_K - 1) / CTA_K, n_q = gridDim.x;
   const int64_t bh = int64_t(batch) * a.q_heads + head;
   const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
   const uint32_t gave_up = sbase + L::gave_up;  // set by the first wait of this CTA that expires
@@ -515,7 +540,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   // everything above needs no result of the kernels before this one; everything below does
   chain_wait();
 
-  const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE);
+  const TileSeq seq = tile_sequence<CTA_K>(a, bh, bx, n_q, n_k, CAPTURE, part, parts);
   float2* stats = reinterpret_cast<float2*>(smem + L::stats);
   uint16_t* sums = reinterpret_cast<uint16_t*>(smem + L::sums);
 
@@ -884,7 +909,16 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
     }
     const float denom = st.d[0];
-    if (ok && row_ok) {
+    if (MODE == kDense && parts > 1) {
+      // part of a split key range: channel-major unnormalised rows (in units of 2^m_o), then m_o
+      // and the denominator; NaN when a wait of this CTA expired, so the merged rows show it
+      float* mine = a.tail_scratch + (size_t(tail_unit) * parts + part) * (130 * 128) + row_in;
+      const float poison = ok ? 0.0f : __int_as_float(0x7fffffff);
+#pragma unroll
+      for (int ch = 0; ch < kOut; ++ch) mine[ch * 128] = O[ch] + poison;
+      mine[128 * 128] = m_o;
+      mine[129 * 128] = denom + poison;
+    } else if (ok && row_ok) {
       if (MODE == kCapture && half == 0) {
         const CaptureLayout cap = capture_layout(a, n_q, n_k);
         cap.state[grow * 2] = st.m;
@@ -1057,6 +1091,99 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Combines the parts of the split CTAs (AttentionArgs::tail_*): per row the parts' maxima give the
+// common unit, the rows and denominators are added in it, and the row is finished exactly as the
+// attention kernel's epilogue finishes an unsplit one.  grid = (split units, groups of 16 output
+// channels), 128 threads = rows; every load of a thread is independent of the others.
+constexpr int kMergeChannels = 16;
+__global__ __launch_bounds__(128) void tail_merge_kernel(const AttentionArgs a, int halves,
+                                                         int k_out) {
+  chain_wait();
+  constexpr int kMaxParts = 4;
+  const int n_q = (a.q_len + 127) / 128, rows_y = a.q_heads * halves, parts = a.tail_splits;
+  const int unit = a.tail_begin + blockIdx.x, row_in = threadIdx.x, ch0 = blockIdx.y * kMergeChannels;
+  const int bx = unit % n_q, by = (unit / n_q) % rows_y, batch = unit / (n_q * rows_y);
+  const int head = by / halves, half = by % halves;
+  const int row = bx * 128 + row_in;
+  if (row >= a.q_len) return;
+  const int kv_head = head / (a.q_heads / a.kv_heads);
+  const int64_t kvh = int64_t(batch) * a.kv_heads + kv_head;
+  const float* mine = a.tail_scratch + size_t(blockIdx.x) * parts * (130 * 128) + row_in;
+  float part_m[kMaxParts], part_d[kMaxParts], x[kMaxParts][kMergeChannels];
+#pragma unroll
+  for (int p = 0; p < kMaxParts; ++p) {
+    part_m[p] = -INFINITY;
+    part_d[p] = 0.0f;
+    if (p < parts) {
+      part_m[p] = mine[(p * 130 + 128) * 128];
+      part_d[p] = mine[(p * 130 + 129) * 128];
+#pragma unroll
+      for (int c = 0; c < kMergeChannels; ++c) x[p][c] = mine[(p * 130 + ch0 + c) * 128];
+    }
+  }
+  float m = part_m[0];
+#pragma unroll
+  for (int p = 1; p < kMaxParts; ++p) m = fmaxf(m, part_m[p]);
+  float w[kMaxParts], denom = 0.0f;
+#pragma unroll
+  for (int p = 0; p < kMaxParts; ++p) {
+    w[p] = p < parts ? ex2_approx(part_m[p] - m) : 0.0f;
+    denom = fmaf(part_d[p], w[p], denom);
+  }
+  const float inv = rcp_approx(denom);
+  const float* vs = a.v_scale + kvh * a.head_dim + k_out * half + ch0;
+  const float* vc = a.v_center + kvh * a.head_dim + k_out * half + ch0;
+  char* o_row = static_cast<char*>(a.o) + 2 * (k_out * half + ch0) +
+                2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
+#pragma unroll
+  for (int ch = 0; ch < kMergeChannels; ch += 8) {
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float r[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c = ch + 2 * i + j;
+        float acc = 0.0f;
+#pragma unroll
+        for (int p = 0; p < kMaxParts; ++p)
+          if (p < parts) acc = fmaf(x[p][c], w[p], acc);
+        r[j] = fmaf(acc * inv, __ldg(vs + c), __ldg(vc + c));
+      }
+      if (a.out_dtype_code == 1) {
+        const __half2 h = __floats2half2_rn(r[0], r[1]);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(r[0], r[1]);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(o_row + 2 * ch) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+  if (a.lse && half == 0 && blockIdx.y == 0)
+    a.lse[(int64_t(batch) * a.q_heads + head) * a.q_len + row] = row_lse(denom, m);
+}
+
+// How the last, partial wave of a dense unmasked launch is split (0 = not at all): with C whole
+// CTAs on S SMs the last wave holds R = C mod S of them; when they fill at most half the GPU each
+// is cut into min(4, S / R) key-range parts, so the wave takes a part's time instead of a CTA's.
+// Needs the caller's scratch (kTailScratchParts parts), at least eight key tiles per part, and a
+// saving of at least 2048 keys' worth of tiles per CTA (about 16 us), several times what the parts'
+// stores and the merge launch cost.
+int tail_split_factor(const AttentionArgs& a, int ctas, int n_k, int sms) {
+  if (a.tail_scratch == nullptr || a.is_causal || a.mask || a.row_offsets || a.key_mask_tiles ||
+      a.block_mass || ctas <= sms)
+    return 0;
+  const int rest = ctas % sms;
+  if (rest == 0 || rest > sms / 2) return 0;
+  int parts = std::min(4, sms / rest);
+  parts = std::min(parts, n_k / 8);
+  parts = std::min(parts, kTailScratchParts / rest);
+  if (parts < 2) return 0;
+  const int saved_keys = (n_k - (n_k + parts - 1) / parts) * a.cta_k;
+  return saved_keys >= 2048 ? parts : 0;
+}
+
 template <int MODE, int CTA_K, int D>
 int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
               const CUtensorMap& map_v, cudaStream_t stream) {
@@ -1085,8 +1212,31 @@ int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMa
     configured = device;
   }
   const dim3 grid((a.q_len + 127) / 128, a.q_heads * SmemLayout<D, CTA_K>::kHalves, a.batch);
+  if constexpr (MODE == kDense) {
+    static thread_local int sms = 0, sms_device = -1;
+    if (sms_device != device) {
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      sms_device = device;
+    }
+    const int ctas = int(grid.x * grid.y * grid.z), n_k = (a.k_len + CTA_K - 1) / CTA_K;
+    const int parts = tail_split_factor(a, ctas, n_k, sms);
+    if (parts > 0) {
+      AttentionArgs split = a;
+      const int rest = ctas % sms;
+      split.tail_begin = ctas - rest;
+      split.tail_splits = parts;
+      launch_chained(kernel, dim3(split.tail_begin + rest * parts), dim3(kThreads),
+                     SmemLayout<D, CTA_K>::bytes, stream, map_q, map_k, map_v, split);
+      launch_chained(tail_merge_kernel, dim3(rest, SmemLayout<D, CTA_K>::kOut / kMergeChannels),
+                     dim3(128), 0, stream, split,
+                     SmemLayout<D, CTA_K>::kHalves, SmemLayout<D, CTA_K>::kOut);
+      return check_launch("attention (tensor-core kernel, split tail)");
+    }
+  }
+  AttentionArgs whole = a;
+  whole.tail_splits = 0;
   launch_chained(kernel, grid, dim3(kThreads), SmemLayout<D, CTA_K>::bytes, stream, map_q, map_k, map_v,
-                 a);
+                 whole);
   return check_launch("attention (tensor-core kernel)");
 }
 

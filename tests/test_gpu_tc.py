@@ -378,3 +378,37 @@ def test_per_query_mask_staging_forms(ref, dtype, offset):
         assert torch.equal(torch.isneginf(got["lse"]), torch.isneginf(want["lse"]))
         fin = torch.isfinite(want["lse"])
         torch.testing.assert_close(got["lse"][fin], want["lse"][fin], rtol=0, atol=5e-4)
+
+
+@pytest.mark.parametrize("shape", [
+    # dim, q heads, kv heads, length: CTA counts that leave a small last wave on a 148-SM GPU
+    (128, 16, 4, 4096),   # 512 CTAs: 68 in the last wave, two key-range parts each
+    (128, 5, 5, 4096),    # 160 CTAs: 12 in the last wave, four parts each
+    (256, 5, 1, 4096),    # two CTAs per (query block, head): 320 CTAs, 24 in the last wave
+    (64, 5, 5, 4096),     # 64-key tiles, 64 output channels
+])
+def test_split_last_wave_matches_whole_ctas(ref, shape):
+    """The one-call dense path cuts the CTAs of a small last wave into key-range parts and merges
+    them; the prequantised route has no scratch for that and runs whole CTAs.  Same inputs: every
+    element within the output tolerance, almost all bit-identical (only rows of split CTAs can differ,
+    by the last place of their FP32 sums), and both within tolerance of the reference's kernel."""
+    import risaattention_b200 as risa
+    from oracle import ref_gpu
+
+    dim, hq, hkv, length = shape
+    g = torch.Generator(device="cuda").manual_seed(length + dim + hq)
+    q = torch.randn(1, hq, length, dim, device="cuda", generator=g).bfloat16()
+    k = torch.randn(1, hkv, length, dim, device="cuda", generator=g).bfloat16()
+    v = torch.randn(1, hkv, length, dim, device="cuda", generator=g).bfloat16()
+    one_call = risa.int8_attention(q, k, v)
+    packed = risa.prequantize_int8_attention(q, k, v)
+    whole = risa.int8_attention_from_prequantized(packed)
+    torch.cuda.synchronize()
+    assert_outputs_match(one_call, whole, TOL)
+    assert (one_call != whole).float().mean() < 0.02
+    want = torch.empty_like(whole)
+    cta_k = packed.cta_k
+    pk = ref_gpu.prequantize(q, k, v, cta_k=cta_k)
+    ref_gpu.attention(pk, sm_scale=dim ** -0.5, out=want)
+    torch.cuda.synchronize()
+    assert_outputs_match(one_call, want, TOL)
