@@ -509,10 +509,27 @@ def mma_issue_loop_tops(device):
     return ops.value / ms / 1e9
 
 
-def cta_waves(q_heads_local, seq_len, sms=148):
+def tail_split_parts(ctas, key_tiles, sms, cta_k=128):
+    """Key-range parts per CTA of the last wave in the one-call dense path (0: whole CTAs); the
+    library's rule (attention_tc.cu, tail_split_factor) restated for the launch count."""
+    rest = ctas % sms
+    if ctas <= sms or rest == 0 or rest > sms // 2:
+        return 0
+    parts = min(4, sms // rest, key_tiles // 8, 160 // rest)
+    if parts < 2 or (key_tiles - -(-key_tiles // parts)) * cta_k < 2048:
+        return 0
+    return parts
+
+
+def cta_waves(q_heads_local, seq_len, sms=None):
+    if sms is None:
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     ctas = q_heads_local * ((seq_len + 127) // 128)
+    parts = tail_split_parts(ctas, (seq_len + 127) // 128, sms)
+    waves = ctas // sms + (ctas % sms > 0) / max(parts, 1)
     return {"ctas": ctas, "sms": sms, "waves": ctas / sms,
-            "wave_efficiency": (ctas / sms) / -(-ctas // sms)}
+            "last_wave_key_range_parts": parts,
+            "wave_efficiency": (ctas / sms) / waves}
 
 
 def run_ours(args):
@@ -655,7 +672,10 @@ def run_ours(args):
         "clocks": clocks.result,
         "e2e": {"value": total_ops / e2e_ms / 1e9, "unit": "TOPS", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": KERNELS_PER_DENSE_CALL * args.steps * world,
+        # the merge launch of a split last wave counts when the shape takes it
+        "gpu_launches": (KERNELS_PER_DENSE_CALL
+                         + (cta_waves(q.shape[1], L)["last_wave_key_range_parts"] > 0))
+                        * args.steps * world,
         "roofline": {"bound": "tensor", "kernel": "attention_tc_kernel", "achieved": achieved,
                      "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
                      "kernel_ms": att_ms,
