@@ -63,10 +63,6 @@ static_assert(128 * (kSoftmaxGroups * kRegsSoftmax + kRegsCorrection + kRegsIssu
 // measured fastest (one copy leaves the loads too little to hide behind, four copies fall out of the
 // instruction cache next to the other roles' code).
 constexpr int kExpUnroll = 2;
-#ifndef RISA_EXP_POLY_PAIRS
-#define RISA_EXP_POLY_PAIRS 0
-#endif
-constexpr int kExpPolyPairs = RISA_EXP_POLY_PAIRS;  // of every four column pairs, on the FP32 pipes
 constexpr unsigned int kSelfTestSite = 900;  // site number reported by the bounded-wait self test
 
 // Per head_dim and key-tile width: what one CTA holds and how deep its rings are.  head_dim 256 is
@@ -233,10 +229,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     }
     if (c > 0) tmem_load32(tmem_row + 32 * (c - 1), raw);
     uint32_t P[8], s4[8];
-    // without capture the codes are not observable one by one: part of the exponentials moves to
-    // the FP32 pipes (kExpPolyPairs of every four column pairs)
-    tile_exp_chunk<KIND, CAPTURE, 32, CAPTURE ? 0 : kExpPolyPairs, true>(x, sc, neg_m, P, numer, s4,
-                                                                         mul);
+    tile_exp_chunk<KIND, CAPTURE, 32, true>(x, sc, neg_m, P, numer, s4, mul);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)

@@ -99,33 +99,6 @@ __device__ __forceinline__ TileScales tile_begin(RowState& st, float tile_m) {
   return s;
 }
 
-// 2^x for a packed pair of values on the FP32 pipes, without the special-function unit (which a
-// tile's exponentials otherwise keep busy for twice as long as its tensor-core work takes):
-// x = n + f with n = round(x) and |f| <= 1/2 by the add-a-large-constant trick, 2^f by a degree-4
-// polynomial fitted to a relative error of 2.7e-6 (a U8 probability code changes in fewer than one
-// of 10^4 cases against ex2.approx), 2^n by adding n to the exponent field.  x is clamped below at
-// -24 -- the probability rounds to zero long before -- so the exponent arithmetic cannot wrap; the
-// callers' x never exceeds 8.
-__device__ __forceinline__ uint64_t ex2_poly_f32x2(uint64_t x2) {
-  float a, b;
-  unpack_f32x2(x2, a, b);
-  x2 = pack_f32x2(fmaxf(a, -24.0f), fmaxf(b, -24.0f));
-  const uint64_t r2 = add_f32x2(x2, pack_f32x2(12582912.0f, 12582912.0f));  // 1.5 * 2^23
-  const uint64_t n2 = add_f32x2(r2, pack_f32x2(-12582912.0f, -12582912.0f));
-  const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.0f, -1.0f), x2);
-  uint64_t p2 = pack_f32x2(0.009570096619427204f, 0.009570096619427204f);
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.05591785907745361f, 0.05591785907745361f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.240247443318367f, 0.240247443318367f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.6931217908859253f, 0.6931217908859253f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.9999992847442627f, 0.9999992847442627f));
-  float pa, pb, ra, rb;
-  unpack_f32x2(p2, pa, pb);
-  unpack_f32x2(r2, ra, rb);
-  pa = __uint_as_float(__float_as_uint(pa) + (__float_as_uint(ra) << 23));
-  pb = __uint_as_float(__float_as_uint(pb) + (__float_as_uint(rb) << 23));
-  return pack_f32x2(pa, pb);
-}
-
 // Probabilities of one chunk of NCOL (32 or 16) keys.  P receives NCOL / 4 packed words in storage
 // order (word 4j+g = lane g of 16-key group j), numer accumulates their U8 sum, s4 (optional)
 // receives the sum of each word.
@@ -134,9 +107,6 @@ __device__ __forceinline__ uint64_t ex2_poly_f32x2(uint64_t x2) {
 // four of them, which keeps the conversion off the half-rate conversion pipe.  The work is written
 // stage by stage over all 32 columns (scale, exponential, round, pack) so that 32 independent
 // operations are in flight per stage instead of one dependent chain per word.
-// POLY: of every eight columns, this many pairs (0..4) take their exponential from the FP32 pipes
-// (ex2_poly_f32x2) instead of the special-function unit; only paths whose probability codes are not
-// pinned bit for bit may use it.
 // MAD_PACK: the four rounded values of a word are combined by three integer multiply-adds
 // (u1 * 2^8 + u0, u3 * 2^8 + u2, hi * 2^16 + lo) instead of three byte permutes, which moves the
 // packing from the ALU pipe, the busiest one of the tensor-core kernel, to the FMA pipe.  The float
@@ -150,7 +120,7 @@ struct PackMultipliers {
   uint32_t by256, by65536;
 };
 
-template <int KIND, bool WANT_SUMS, int NCOL = 32, int POLY = 0, bool MAD_PACK = false>
+template <int KIND, bool WANT_SUMS, int NCOL = 32, bool MAD_PACK = false>
 __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)[4], float neg_m,
                                                uint32_t* P, uint32_t& numer, uint32_t* s4,
                                                PackMultipliers mul = PackMultipliers{0u, 0u}) {
@@ -172,12 +142,8 @@ __device__ __forceinline__ void tile_exp_chunk(const float* x, const float (&sc)
   }
 #pragma unroll
   for (int i = 0; i < NCOL; i += 2) {
-    if (((i >> 1) & 3) < POLY) {
-      unpack_f32x2(ex2_poly_f32x2(pack_f32x2(p[i], p[i + 1])), p[i], p[i + 1]);
-    } else {
-      p[i] = ex2_approx(p[i]);
-      p[i + 1] = ex2_approx(p[i + 1]);
-    }
+    p[i] = ex2_approx(p[i]);
+    p[i + 1] = ex2_approx(p[i + 1]);
   }
   uint32_t u[NCOL];
   const uint64_t magic2 = pack_f32x2(8388608.0f, 8388608.0f);
