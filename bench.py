@@ -510,15 +510,11 @@ def mma_issue_loop_tops(device):
 
 
 def tail_split_parts(ctas, key_tiles, sms, cta_k=128):
-    """Key-range parts per CTA of the last wave in the one-call dense path (0: whole CTAs); the
-    library's rule (attention_tc.cu, tail_split_factor) restated for the launch count."""
-    rest = ctas % sms
-    if ctas <= sms or rest == 0 or rest > sms // 2:
-        return 0
-    parts = min(4, sms // rest, key_tiles // 8, 160 // rest)
-    if parts < 2 or (key_tiles - -(-key_tiles // parts)) * cta_k < 2048:
-        return 0
-    return parts
+    """Key-range parts per CTA of the last wave in the one-call dense path (0: whole CTAs), asked
+    of the library itself."""
+    from risaattention_b200 import _backend
+
+    return int(_backend._ABI.lib.risa_b200_split_last_wave_parts(ctas, key_tiles, cta_k, sms))
 
 
 def cta_waves(q_heads_local, seq_len, sms=None):

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "risa_b200_quantize_qk": (c_i32, [c_vp] * 6 + [c_i32] * 7 + [c_i64] * 6 + [c_i32] + [c_vp] * 4),
     "risa_b200_quantize_qkv": (
         c_i32, [c_vp] * 10 + [c_i32] * 8 + [c_i64] * 9 + [c_i32] * 2 + [c_vp] * 4 + [c_sz, c_vp]),
+    "risa_b200_split_last_wave_parts": (c_i32, [c_i32] * 4),
     "risa_b200_quantize_v_workspace_size": (c_sz, [c_i32] * 4),
     "risa_b200_quantize_v": (
         c_i32, [c_vp] * 4 + [c_i32] * 5 + [c_i64] * 3 + [c_i32] * 2 + [c_vp, c_vp, c_sz, c_vp]),

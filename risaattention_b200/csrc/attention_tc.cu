@@ -1163,18 +1163,23 @@ __global__ __launch_bounds__(128) void tail_merge_kernel(const AttentionArgs a, 
 // Needs the caller's scratch (kTailScratchParts parts), at least eight key tiles per part, and a
 // saving of at least 2048 keys' worth of tiles per CTA (about 16 us), several times what the parts'
 // stores and the merge launch cost.
-int tail_split_factor(const AttentionArgs& a, int ctas, int n_k, int sms) {
-  if (a.tail_scratch == nullptr || a.is_causal || a.mask || a.row_offsets || a.key_mask_tiles ||
-      a.block_mass || ctas <= sms)
-    return 0;
+int split_parts(int ctas, int n_k, int cta_k, int sms) {
+  if (sms <= 0 || ctas <= sms) return 0;
   const int rest = ctas % sms;
   if (rest == 0 || rest > sms / 2) return 0;
   int parts = std::min(4, sms / rest);
   parts = std::min(parts, n_k / 8);
   parts = std::min(parts, kTailScratchParts / rest);
   if (parts < 2) return 0;
-  const int saved_keys = (n_k - (n_k + parts - 1) / parts) * a.cta_k;
+  const int saved_keys = (n_k - (n_k + parts - 1) / parts) * cta_k;
   return saved_keys >= 2048 ? parts : 0;
+}
+
+int tail_split_factor(const AttentionArgs& a, int ctas, int n_k, int sms) {
+  if (a.tail_scratch == nullptr || a.is_causal || a.mask || a.row_offsets || a.key_mask_tiles ||
+      a.block_mass)
+    return 0;
+  return split_parts(ctas, n_k, a.cta_k, sms);
 }
 
 template <int MODE, int CTA_K, int D>
@@ -1283,6 +1288,10 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
 int attention_tc_select_max_tiles(int cta_k) { return 256 * cta_k / 24; }
 
 }  // namespace risa_b200
+
+extern "C" int risa_b200_split_last_wave_parts(int ctas, int key_tiles, int cta_k, int sms) {
+  return risa_b200::split_parts(ctas, key_tiles, cta_k, sms);
+}
 
 extern "C" int risa_b200_device_status(void) {
   unsigned int status = 0, zero = 0;

@@ -114,3 +114,20 @@ def test_fake_tensor_and_operator_schema():
         assert risa.int8_attention(q, q, q, attn_mask=mask).shape == q.shape
     with pytest.raises(ValueError, match="v_quantization"):
         risa.int8_attention(torch.empty(1), torch.empty(1), torch.empty(1), v_quantization="x")
+
+
+def test_split_last_wave_rule_known_answers():
+    """The rule that decides whether the one-call dense path adds a merge launch is a pure function
+    of the launch shape; pin it on the shapes the design document quotes (148 SMs)."""
+    lib = ctypes.CDLL(str(ROOT / "risaattention_b200" / "librisa_b200.so"))
+    parts = lib.risa_b200_split_last_wave_parts
+    parts.restype = ctypes.c_int
+    assert parts(4096, 256, 128, 148) == 0   # 16 heads at 32K: 100 CTAs in the last wave
+    assert parts(512, 256, 128, 148) == 2    # 2 heads at 32K (one of 8 GPUs): 68 CTAs, 2 parts each
+    assert parts(1024, 256, 128, 148) == 0   # 4 heads at 32K: 136 CTAs
+    assert parts(512, 32, 128, 148) == 2     # 16 heads at 4K
+    assert parts(160, 32, 128, 148) == 4     # 5 heads at 4K: 12 CTAs, 4 parts each
+    assert parts(160, 16, 128, 148) == 0     # 2K: the saving would be below 2048 keys
+    assert parts(128, 256, 128, 148) == 0    # less than one wave
+    assert parts(296, 256, 128, 148) == 0    # whole waves only
+    assert parts(512, 256, 128, 0) == 0
