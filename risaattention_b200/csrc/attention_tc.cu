@@ -760,12 +760,39 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         const float2 mine = *stat;  // (tile maximum, probability sum), written above
         const uint32_t numer = __float_as_uint(mine.y);
         const TileScales ts = tile_begin(st, mine.x);
+        if (last) {
 #pragma unroll
-        for (int c = 0; c < CTA_K / 32; ++c) {
-          uint16_t s4[8];
-          *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(my_sums + 8 * c);
-          if (last) denominator_chunk<true>(st, ts, c == 0, s4);
-          else denominator_chunk<false>(st, ts, c == 0, s4);
+          for (int c = 0; c < CTA_K / 32; ++c) {
+            uint16_t s4[8];
+            *reinterpret_cast<uint4*>(s4) = *reinterpret_cast<const uint4*>(my_sums + 8 * c);
+            denominator_chunk<true>(st, ts, c == 0, s4);
+          }
+        } else {
+          // d[g] = fma(float(sum), w, d[g]) word by word in key order, as denominator_chunk<false>
+          // does, with lanes (0, 1) and (2, 3) as packed pairs: a stored word holds the 16-bit sums
+          // of two neighbouring lanes, a byte permute puts each under the exponent of 2^23, and
+          // one packed subtract of 2^23 gives both exact float values
+          const uint64_t w2 = pack_f32x2(ts.w, ts.w);
+          const uint64_t unbias = pack_f32x2(-8388608.0f, -8388608.0f);
+          uint64_t d01 = pack_f32x2(st.d[0], st.d[1]), d23 = pack_f32x2(st.d[2], st.d[3]);
+#pragma unroll
+          for (int c = 0; c < CTA_K / 32; ++c) {
+            const uint4 words = *reinterpret_cast<const uint4*>(my_sums + 8 * c);
+            const uint32_t pair[4] = {words.x, words.y, words.z, words.w};  // (g0,g1) (g2,g3) x 2
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const uint64_t f01 = add_f32x2(
+                  (uint64_t(__byte_perm(pair[2 * j], 0x4B000000u, 0x7632)) << 32) |
+                      __byte_perm(pair[2 * j], 0x4B000000u, 0x7610), unbias);
+              const uint64_t f23 = add_f32x2(
+                  (uint64_t(__byte_perm(pair[2 * j + 1], 0x4B000000u, 0x7632)) << 32) |
+                      __byte_perm(pair[2 * j + 1], 0x4B000000u, 0x7610), unbias);
+              d01 = fma_f32x2(f01, w2, d01);
+              d23 = fma_f32x2(f23, w2, d23);
+            }
+          }
+          unpack_f32x2(d01, st.d[0], st.d[1]);
+          unpack_f32x2(d23, st.d[2], st.d[3]);
         }
         rowstate[row_in] = st.m;
 #pragma unroll
