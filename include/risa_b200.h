@@ -120,6 +120,26 @@ int risa_b200_attention(const void* q, const void* k, const void* v, void* o, co
                         const int32_t* sparse_block_indices, float* block_mass, int is_causal,
                         float* lse, const int32_t* key_mask_tiles, void* stream);
 
+/* risa_b200_attention with room for the split last wave (see risa_b200_split_last_wave_parts): a
+ * dense, unmasked, non-causal call without tile lists may leave key-range parts of its last CTAs
+ * in `scratch` (16-byte aligned) and finish them with a merge launch; every other call, and
+ * scratch == NULL, behaves exactly as risa_b200_attention.  risa_b200_attention_scratch_size()
+ * gives the bytes to provide for a shape on the current device, 0 when the shape would not be
+ * split there.  Outputs of split rows can differ from the unsplit ones by FP32 summation order. */
+size_t risa_b200_attention_scratch_size(int batch, int q_heads, int q_len, int k_len, int head_dim,
+                                        int cta_k);
+int risa_b200_attention_scratch(const void* q, const void* k, const void* v, void* o,
+                                const float* q_scale, const float* k_scale, const float* v_scale,
+                                const float* v_center, const void* mask, int64_t mask_stride_b,
+                                int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+                                int mask_dtype_code, int cta_k, int batch, int q_len, int k_len,
+                                int q_heads, int kv_heads, int head_dim, int64_t o_stride_b,
+                                int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+                                int out_dtype_code, const int32_t* sparse_row_offsets,
+                                const int32_t* sparse_block_indices, float* block_mass,
+                                int is_causal, float* lse, const int32_t* key_mask_tiles,
+                                void* scratch, size_t scratch_bytes, void* stream);
+
 /* Pattern construction inside the dense pass.  Same attention as risa_b200_attention with a
  * block-mass workspace (same outputs, bit for bit), but instead of writing 8 bytes per (query, key
  * tile) to a workspace of the reference's layout, sorting the block masses with a library sort and

@@ -47,6 +47,12 @@ _SIGNATURES = {
         c_i32,
         [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
                                                                    c_i32, c_vp, c_vp, c_vp]),
+    "risa_b200_attention_scratch_size": (c_sz, [c_i32] * 6),
+    "risa_b200_attention_scratch": (
+        c_i32,
+        [c_vp] * 9 + [c_i64] * 4 + [c_i32] * 8 + [c_i64] * 3 + [c_f32, c_i32, c_vp, c_vp, c_vp,
+                                                                   c_i32, c_vp, c_vp, c_vp, c_sz,
+                                                                   c_vp]),
     "risa_b200_select_scratch_size": (c_sz, [c_i32] * 2),
     "risa_b200_select_max_key_tiles": (c_i32, [c_i32]),
     "risa_b200_attention_select": (
@@ -223,12 +229,22 @@ class _Native:
         o_b = hq * lq * d if b <= 1 else o.stride(0)
         o_n = d if lq <= 1 else o.stride(2)
         o_h = lq * d if hq <= 1 else o.stride(1)
-        self._check(self.lib.risa_b200_attention(
+        # room for the parts of a split last wave, only for the calls and shapes that take it
+        scratch, scratch_bytes = None, 0
+        if attn_mask is None and not is_causal and sparse_row_offsets is None and block_mass is None:
+            scratch_bytes = int(self.lib.risa_b200_attention_scratch_size(b, hq, lq, lk, d, cta_k))
+            if scratch_bytes:
+                with torch.cuda.device(q_int8.device), torch.cuda.stream(
+                        torch.cuda.ExternalStream(stream_ptr, device=q_int8.device) if stream_ptr
+                        else torch.cuda.default_stream(q_int8.device)):
+                    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=q_int8.device)
+        self._check(self.lib.risa_b200_attention_scratch(
             _ptr(q_int8), _ptr(k_int8), _ptr(v_int8), _ptr(o), _ptr(q_scale), _ptr(k_scale),
             _ptr(v_scale), _ptr(v_center), _ptr(attn_mask), ms[0], ms[1], ms[2], ms[3], mask_code,
             cta_k, b, lq, lk, hq, hkv, d, o_b, o_n, o_h, sm_scale, output_dtype_code,
             _ptr(sparse_row_offsets), _ptr(sparse_block_indices), _ptr(block_mass),
-            int(is_causal), _ptr(lse), _ptr(key_mask_tiles), stream_ptr))
+            int(is_causal), _ptr(lse), _ptr(key_mask_tiles), _ptr(scratch), scratch_bytes,
+            stream_ptr))
 
     # -- pattern construction inside the dense pass (no counterpart in the reference module) ------
     def select_scratch_size(self, k_len, cta_k) -> int:

@@ -1,6 +1,7 @@
 // C-ABI entry of the fused INT8 attention call: validation, kernel-family selection and the
 // block-mass reduction that follows a capture pass.
 #include "attention_common.cuh"
+#include <cstdint>
 
 namespace risa_b200 {
 namespace {
@@ -215,6 +216,39 @@ extern "C" int risa_b200_attention(
                        o_stride_h, sm_scale, out_dtype_code, sparse_row_offsets,
                        sparse_block_indices, block_mass, is_causal, lse, key_mask_tiles, stream_ptr,
                        nullptr);
+}
+
+extern "C" size_t risa_b200_attention_scratch_size(int batch, int q_heads, int q_len, int k_len,
+                                                   int head_dim, int cta_k) {
+  if (batch <= 0 || q_heads <= 0 || q_len <= 0 || k_len <= 0 || (cta_k != 64 && cta_k != 128))
+    return 0;
+  const int halves = head_dim == 256 ? 2 : 1;
+  const int64_t ctas = int64_t((q_len + 127) / 128) * q_heads * halves * batch;
+  if (ctas > INT32_MAX) return 0;
+  const int parts = risa_b200_split_last_wave_parts(int(ctas), (k_len + cta_k - 1) / cta_k, cta_k,
+                                                    select_slot_count());
+  return parts > 0 ? risa_b200::kTailScratchBytes : 0;
+}
+
+extern "C" int risa_b200_attention_scratch(
+    const void* q, const void* k, const void* v, void* o, const float* q_scale,
+    const float* k_scale, const float* v_scale, const float* v_center, const void* mask,
+    int64_t mask_stride_b, int64_t mask_stride_h, int64_t mask_stride_q, int64_t mask_stride_k,
+    int mask_dtype_code, int cta_k, int batch, int q_len, int k_len, int q_heads, int kv_heads,
+    int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
+    int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
+    float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles, void* scratch,
+    size_t scratch_bytes, void* stream_ptr) {
+  RISA_REQUIRE(scratch == nullptr || (scratch_bytes >= risa_b200::kTailScratchBytes &&
+                                      reinterpret_cast<uintptr_t>(scratch) % 16 == 0),
+               "risa_attention: scratch must be 16-byte aligned device memory of at least "
+               "risa_b200_attention_scratch_size() bytes, or null");
+  return run_attention(q, k, v, o, q_scale, k_scale, v_scale, v_center, mask, mask_stride_b,
+                       mask_stride_h, mask_stride_q, mask_stride_k, mask_dtype_code, cta_k, batch,
+                       q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
+                       o_stride_h, sm_scale, out_dtype_code, sparse_row_offsets,
+                       sparse_block_indices, block_mass, is_causal, lse, key_mask_tiles, stream_ptr,
+                       nullptr, static_cast<float*>(scratch));
 }
 
 extern "C" size_t risa_b200_select_scratch_size(int k_len, int cta_k) {

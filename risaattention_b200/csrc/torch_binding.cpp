@@ -146,7 +146,14 @@ void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at
   auto i32 = [](const std::optional<at::Tensor>& t) {
     return t.has_value() ? static_cast<const int32_t*>(t->data_ptr()) : nullptr;
   };
-  check(risa_b200_attention(
+  // room for the parts of a split last wave, only for the calls and shapes that take it
+  std::optional<at::Tensor> scratch;
+  if (mask_ptr == nullptr && !is_causal && !row_offsets.has_value() && !block_mass.has_value()) {
+    const size_t bytes =
+        risa_b200_attention_scratch_size(int(b), int(hq), int(lq), int(lk), int(d), cta_k);
+    if (bytes > 0) scratch = at::empty({int64_t(bytes)}, q_int8.options().dtype(at::kByte));
+  }
+  check(risa_b200_attention_scratch(
       q_int8.data_ptr(), k_int8.data_ptr(), v_int8.data_ptr(), o.data_ptr(),
       q_scale.data_ptr<float>(), k_scale.data_ptr<float>(), v_scale.data_ptr<float>(),
       v_center.data_ptr<float>(), mask_ptr, ms[0], ms[1], ms[2], ms[3], mask_code, cta_k, int(b),
@@ -154,7 +161,8 @@ void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at
       i32(row_offsets), i32(block_indices),
       block_mass.has_value() ? block_mass->data_ptr<float>() : nullptr, is_causal ? 1 : 0,
       lse.has_value() ? lse->data_ptr<float>() : nullptr, i32(key_mask_tiles),
-      stream_of(stream_ptr)));
+      scratch.has_value() ? scratch->data_ptr() : nullptr,
+      scratch.has_value() ? size_t(scratch->numel()) : 0, stream_of(stream_ptr)));
 }
 
 // ---- the reference module's entry points -------------------------------------------------------

@@ -388,12 +388,15 @@ def test_per_query_mask_staging_forms(ref, dtype, offset):
     (64, 5, 5, 4096),     # 64-key tiles, 64 output channels
 ])
 def test_split_last_wave_matches_whole_ctas(ref, shape):
-    """The one-call dense path cuts the CTAs of a small last wave into key-range parts and merges
-    them; the prequantised route has no scratch for that and runs whole CTAs.  Same inputs: every
-    element within the output tolerance, almost all bit-identical (only rows of split CTAs can differ,
-    by the last place of their FP32 sums), and both within tolerance of the reference's kernel."""
+    """The Python routes cut the CTAs of a small last wave into key-range parts and merge them;
+    risa_b200_attention (no scratch) runs whole CTAs.  Same packed operands: every element within
+    the output tolerance, almost all bit-identical (only rows of split CTAs can differ, by the last
+    place of their FP32 sums), and everything within tolerance of the reference's kernel."""
+    import ctypes
+
     import risaattention_b200 as risa
     from oracle import ref_gpu
+    from risaattention_b200 import _backend
 
     dim, hq, hkv, length = shape
     g = torch.Generator(device="cuda").manual_seed(length + dim + hq)
@@ -402,13 +405,25 @@ def test_split_last_wave_matches_whole_ctas(ref, shape):
     v = torch.randn(1, hkv, length, dim, device="cuda", generator=g).bfloat16()
     one_call = risa.int8_attention(q, k, v)
     packed = risa.prequantize_int8_attention(q, k, v)
-    whole = risa.int8_attention_from_prequantized(packed)
+    two_calls = risa.int8_attention_from_prequantized(packed)
+    C = _backend._ABI
+    assert C.lib.risa_b200_attention_scratch_size(1, hq, length, length, dim, packed.cta_k) > 0, \
+        "shape was meant to leave a small last wave"
+    whole = torch.empty_like(one_call)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    C._check(C.lib.risa_b200_attention(
+        p(packed.q), p(packed.k), p(packed.v), p(whole), p(packed.q_scale), p(packed.k_scale),
+        p(packed.v_scale), p(packed.v_center), None, 0, 0, 0, 0, -1, packed.cta_k, 1, length,
+        length, hq, hkv, dim, whole.stride(0), whole.stride(2), whole.stride(1),
+        packed.attention_scale, 2, None, None, None, 0, None, None,
+        torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
+    assert torch.equal(one_call, two_calls)  # same kernels, same split
     assert_outputs_match(one_call, whole, TOL)
-    assert (one_call != whole).float().mean() < 0.02
+    differing = (one_call != whole).float().mean()
+    assert 0 < differing < 0.02, "the split rows should differ somewhere, and only there"
     want = torch.empty_like(whole)
-    cta_k = packed.cta_k
-    pk = ref_gpu.prequantize(q, k, v, cta_k=cta_k)
+    pk = ref_gpu.prequantize(q, k, v, cta_k=packed.cta_k)
     ref_gpu.attention(pk, sm_scale=dim ** -0.5, out=want)
     torch.cuda.synchronize()
     assert_outputs_match(one_call, want, TOL)
