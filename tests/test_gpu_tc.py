@@ -386,6 +386,7 @@ def test_per_query_mask_staging_forms(ref, dtype, offset):
     (128, 5, 5, 4096),    # 160 CTAs: 12 in the last wave, four parts each
     (256, 5, 1, 4096),    # two CTAs per (query block, head): 320 CTAs, 24 in the last wave
     (64, 5, 5, 4096),     # 64-key tiles, 64 output channels
+    (128, 16, 4, 4000),   # ragged: the last query block and the last key tile are partial
 ])
 def test_split_last_wave_matches_whole_ctas(ref, shape):
     """The Python routes cut the CTAs of a small last wave into key-range parts and merge them;
