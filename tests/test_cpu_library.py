@@ -118,7 +118,7 @@ def test_fake_tensor_and_operator_schema():
 
 def test_split_last_wave_rule_known_answers():
     """The rule that decides whether the one-call dense path adds a merge launch is a pure function
-    of the launch shape; pin it on the shapes the design document quotes (148 SMs)."""
+    of the launch shape; known answers for a 148-SM GPU."""
     lib = ctypes.CDLL(str(ROOT / "risaattention_b200" / "librisa_b200.so"))
     parts = lib.risa_b200_split_last_wave_parts
     parts.restype = ctypes.c_int
