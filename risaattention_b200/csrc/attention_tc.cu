@@ -450,8 +450,9 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
     tmem_regs_ready<32>(raw);
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(raw[i]);
-    if (int_scores) tile_exp_chunk<kScoresInt, CAPTURE>(x, sc, -tile_m, P, numer, s4);
-    else tile_exp_chunk<kScoresScaled, CAPTURE>(x, sc, -tile_m, P, numer, s4);
+    const PackMultipliers mul{a.pack_by256, a.pack_by65536};
+    if (int_scores) tile_exp_chunk<kScoresInt, CAPTURE, 32, true>(x, sc, -tile_m, P, numer, s4, mul);
+    else tile_exp_chunk<kScoresScaled, CAPTURE, 32, true>(x, sc, -tile_m, P, numer, s4, mul);
     if constexpr (CAPTURE) {
 #pragma unroll
       for (int i = 0; i < 8; i += 2)
