@@ -76,11 +76,13 @@ int risa_b200_quantize_qkv(const void* q, void* q_codes, float* q_scale, const v
                            const int32_t* q_perm, const int32_t* kv_perm, void* workspace,
                            size_t workspace_bytes, void* stream);
 
-/* The rule by which risa_b200_dense_attention cuts the CTAs of a small last wave into key-range
+/* The rule by which dense unmasked calls cut the CTAs of their last, partial wave into key-range
  * parts: number of parts per CTA (2..4), or 0 when a launch of `ctas` CTAs (query blocks x heads x
  * batch, x 2 for head_dim 256) over `key_tiles` tiles of `cta_k` keys on a GPU with `sms` SMs runs
- * whole CTAs only.  A non-zero answer means one more launch (the merge) for a dense unmasked,
- * non-causal call.  Pure function; no counterpart in the reference. */
+ * whole CTAs only.  R = ctas mod sms CTAs in p parts each take ceil(R * p / sms) rounds of 1 / p of
+ * a CTA's time; the best p is taken if it saves at least a fifth of a CTA's time and 2048 keys.  A
+ * non-zero answer means one more launch (the merge).  Pure function; no counterpart in the
+ * reference. */
 int risa_b200_split_last_wave_parts(int ctas, int key_tiles, int cta_k, int sms);
 
 /* V quantisation for callers that must not allocate.  Some users of this library cannot obtain

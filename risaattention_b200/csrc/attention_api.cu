@@ -88,7 +88,8 @@ int run_attention(
     int head_dim, int64_t o_stride_b, int64_t o_stride_n, int64_t o_stride_h, float sm_scale,
     int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
     float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles,
-    void* stream_ptr, const SelectRequest* select, float* tail_scratch = nullptr) {
+    void* stream_ptr, const SelectRequest* select, float* tail_scratch = nullptr,
+    size_t tail_scratch_bytes = 0) {
   RISA_REQUIRE(cta_k == 64 || cta_k == 128, "risa_attention: cta_k must be 64 or 128");
   RISA_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256,
                "risa_attention: unsupported head_dim");
@@ -145,7 +146,8 @@ int run_attention(
   a.block_mass = block_mass;
   a.is_causal = is_causal != 0;
   a.lse = lse;
-  a.tail_scratch = tail_scratch;  // kTailScratchBytes of the caller's, or null: no split tail
+  a.tail_scratch = tail_scratch;  // room for the parts of a split last wave, or null
+  a.tail_scratch_bytes = tail_scratch_bytes;
   a.key_mask_tiles = (mask != nullptr && mask_stride_q == 0 && !sparse_row_offsets &&
                       !block_mass && !is_causal)
                          ? key_mask_tiles
@@ -218,16 +220,20 @@ extern "C" int risa_b200_attention(
                        nullptr);
 }
 
+extern "C" int risa_b200_split_last_wave_parts(int ctas, int key_tiles, int cta_k, int sms) {
+  return risa_b200::attention_tc_split_parts(ctas, key_tiles, cta_k, sms);
+}
+
 extern "C" size_t risa_b200_attention_scratch_size(int batch, int q_heads, int q_len, int k_len,
                                                    int head_dim, int cta_k) {
   if (batch <= 0 || q_heads <= 0 || q_len <= 0 || k_len <= 0 || (cta_k != 64 && cta_k != 128))
     return 0;
-  const int halves = head_dim == 256 ? 2 : 1;
+  const int halves = head_dim == 256 ? 2 : 1, sms = select_slot_count();
   const int64_t ctas = int64_t((q_len + 127) / 128) * q_heads * halves * batch;
-  if (ctas > INT32_MAX) return 0;
-  const int parts = risa_b200_split_last_wave_parts(int(ctas), (k_len + cta_k - 1) / cta_k, cta_k,
-                                                    select_slot_count());
-  return parts > 0 ? risa_b200::kTailScratchBytes : 0;
+  if (ctas > INT32_MAX || sms <= 0) return 0;
+  const int parts =
+      risa_b200::attention_tc_split_parts(int(ctas), (k_len + cta_k - 1) / cta_k, cta_k, sms);
+  return size_t(ctas % sms) * parts * risa_b200::kTailPartBytes;
 }
 
 extern "C" int risa_b200_attention_scratch(
@@ -239,16 +245,14 @@ extern "C" int risa_b200_attention_scratch(
     int out_dtype_code, const int32_t* sparse_row_offsets, const int32_t* sparse_block_indices,
     float* block_mass, int is_causal, float* lse, const int32_t* key_mask_tiles, void* scratch,
     size_t scratch_bytes, void* stream_ptr) {
-  RISA_REQUIRE(scratch == nullptr || (scratch_bytes >= risa_b200::kTailScratchBytes &&
-                                      reinterpret_cast<uintptr_t>(scratch) % 16 == 0),
-               "risa_attention: scratch must be 16-byte aligned device memory of at least "
-               "risa_b200_attention_scratch_size() bytes, or null");
+  RISA_REQUIRE(scratch == nullptr || reinterpret_cast<uintptr_t>(scratch) % 16 == 0,
+               "risa_attention: scratch must be 16-byte aligned device memory, or null");
   return run_attention(q, k, v, o, q_scale, k_scale, v_scale, v_center, mask, mask_stride_b,
                        mask_stride_h, mask_stride_q, mask_stride_k, mask_dtype_code, cta_k, batch,
                        q_len, k_len, q_heads, kv_heads, head_dim, o_stride_b, o_stride_n,
                        o_stride_h, sm_scale, out_dtype_code, sparse_row_offsets,
                        sparse_block_indices, block_mass, is_causal, lse, key_mask_tiles, stream_ptr,
-                       nullptr, static_cast<float*>(scratch));
+                       nullptr, static_cast<float*>(scratch), scratch_bytes);
 }
 
 extern "C" size_t risa_b200_select_scratch_size(int k_len, int cta_k) {
@@ -318,7 +322,8 @@ DenseScratch dense_scratch_layout(int batch, int q_heads, int q_len, int kv_head
   s.v_center = take(channels * sizeof(float));
   s.anchors = take(size_t(batch) * kv_heads * sizeof(int32_t));
   s.v_work = take(risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim));
-  s.tail = take(kTailScratchBytes);  // parts of a split last wave (attention_tc.cu)
+  // parts of a split last wave (attention_tc.cu); nothing for shapes the rule leaves whole
+  s.tail = take(risa_b200_attention_scratch_size(batch, q_heads, q_len, k_len, head_dim, cta_k));
   s.total = at;
   return s;
 }
@@ -367,5 +372,5 @@ extern "C" int risa_b200_dense_attention(
                        v_scale, v_center, nullptr, 0, 0, 0, 0, -1, cta_k, batch, q_len, k_len,
                        q_heads, kv_heads, head_dim, o_stride_b, o_stride_n, o_stride_h, sm_scale,
                        out_dtype_code, nullptr, nullptr, nullptr, is_causal, nullptr, nullptr,
-                       stream, nullptr, reinterpret_cast<float*>(base + s.tail));
+                       stream, nullptr, reinterpret_cast<float*>(base + s.tail), s.total - s.tail);
 }

@@ -43,14 +43,14 @@ struct AttentionArgs {
   // tail_splits <= 1: off.
   int tail_begin, tail_splits;
   float* tail_scratch;
+  size_t tail_scratch_bytes;  // what the caller provided (host side only)
   // 2^8 and 2^16 as run-time values for the multiply-add packing of probability codes
   // (softmax_row.cuh, MAD_PACK)
   uint32_t pack_by256, pack_by65536;
 };
 
-// Capacity of AttentionArgs::tail_scratch in parts (one part = 130 x 128 floats).
-constexpr int kTailScratchParts = 160;
-constexpr size_t kTailScratchBytes = size_t(kTailScratchParts) * 130 * 128 * sizeof(float);
+// One part of AttentionArgs::tail_scratch: 128 rows x (128 channels, maximum, denominator).
+constexpr size_t kTailPartBytes = size_t(130) * 128 * sizeof(float);
 
 // Capture workspace (FP32 words), identical to the reference's (attention_int8.cuh:58-60,
 // 770-797, 871-895): block masses [B*Hq*n_q, n_k]; then for every query row and every visited tile
@@ -116,5 +116,7 @@ int attention_rows(const AttentionArgs& a, cudaStream_t stream);
 bool attention_tc_supported(const AttentionArgs& a);
 int attention_tc(const AttentionArgs& a, cudaStream_t stream);
 int attention_tc_select_max_tiles(int cta_k);
+// Parts per CTA of the last wave (0: whole CTAs) for a dense unmasked launch; attention_tc.cu.
+int attention_tc_split_parts(int ctas, int n_k, int cta_k, int sms);
 
 }  // namespace risa_b200

@@ -1185,29 +1185,37 @@ __global__ __launch_bounds__(128) void tail_merge_kernel(const AttentionArgs a, 
     a.lse[(int64_t(batch) * a.q_heads + head) * a.q_len + row] = row_lse(denom, m);
 }
 
-// How the last, partial wave of a dense unmasked launch is split (0 = not at all): with C whole
-// CTAs on S SMs the last wave holds R = C mod S of them; when they fill at most half the GPU each
-// is cut into min(4, S / R) key-range parts, so the wave takes a part's time instead of a CTA's.
-// Needs the caller's scratch (kTailScratchParts parts), at least eight key tiles per part, and a
-// saving of at least 2048 keys' worth of tiles per CTA (about 16 us), several times what the parts'
-// stores and the merge launch cost.
+// How the last, partial wave of a dense unmasked launch is split (0 = not at all).  With C whole
+// CTAs on S SMs the last wave holds R = C mod S of them and takes a whole CTA's time however few
+// they are.  Cut into p key-range parts each (p = 2..4, at least eight key tiles per part) they are
+// R * p parts that take ceil(R * p / S) rounds of 1 / p of a CTA's time; the p with the shortest
+// last wave is taken if it saves at least a fifth of a CTA's time and at least 2048 keys' worth of
+// tiles (about 16 us), several times what the parts' stores and the merge launch cost.
 int split_parts(int ctas, int n_k, int cta_k, int sms) {
   if (sms <= 0 || ctas <= sms) return 0;
   const int rest = ctas % sms;
-  if (rest == 0 || rest > sms / 2) return 0;
-  int parts = std::min(4, sms / rest);
-  parts = std::min(parts, n_k / 8);
-  parts = std::min(parts, kTailScratchParts / rest);
-  if (parts < 2) return 0;
-  const int saved_keys = (n_k - (n_k + parts - 1) / parts) * cta_k;
-  return saved_keys >= 2048 ? parts : 0;
+  if (rest == 0) return 0;
+  int best = 0;
+  double best_time = 0.8;  // of a whole CTA
+  for (int parts = 2; parts <= 4 && n_k / parts >= 8; ++parts) {
+    const double time = double((rest * parts + sms - 1) / sms) / parts;
+    if (time < best_time - 1e-9) {
+      best_time = time;
+      best = parts;
+    }
+  }
+  if (best == 0) return 0;
+  return (1.0 - best_time) * n_k * cta_k >= 2048.0 ? best : 0;
 }
 
 int tail_split_factor(const AttentionArgs& a, int ctas, int n_k, int sms) {
   if (a.tail_scratch == nullptr || a.is_causal || a.mask || a.row_offsets || a.key_mask_tiles ||
       a.block_mass)
     return 0;
-  return split_parts(ctas, n_k, a.cta_k, sms);
+  const int parts = split_parts(ctas, n_k, a.cta_k, sms);
+  // the scratch was sized by the same rule; a caller who sized it for another device gets whole CTAs
+  if (parts > 0 && size_t(ctas % sms) * parts * kTailPartBytes > a.tail_scratch_bytes) return 0;
+  return parts;
 }
 
 template <int MODE, int CTA_K, int D>
@@ -1315,11 +1323,11 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
 // area the in-pass selection reuses (24 bytes per key tile).
 int attention_tc_select_max_tiles(int cta_k) { return 256 * cta_k / 24; }
 
-}  // namespace risa_b200
-
-extern "C" int risa_b200_split_last_wave_parts(int ctas, int key_tiles, int cta_k, int sms) {
-  return risa_b200::split_parts(ctas, key_tiles, cta_k, sms);
+int attention_tc_split_parts(int ctas, int n_k, int cta_k, int sms) {
+  return split_parts(ctas, n_k, cta_k, sms);
 }
+
+}  // namespace risa_b200
 
 extern "C" int risa_b200_device_status(void) {
   unsigned int status = 0, zero = 0;

@@ -122,7 +122,9 @@ def test_split_last_wave_rule_known_answers():
     lib = ctypes.CDLL(str(ROOT / "risaattention_b200" / "librisa_b200.so"))
     parts = lib.risa_b200_split_last_wave_parts
     parts.restype = ctypes.c_int
-    assert parts(4096, 256, 128, 148) == 0   # 16 heads at 32K: 100 CTAs in the last wave
+    assert parts(4096, 256, 128, 148) == 4   # 16 heads at 32K: 100 CTAs -> 400 quarters = 3 rounds of 1/4
+    assert parts(1280, 256, 128, 148) == 3   # 5 heads at 32K: 96 CTAs -> 288 thirds = 2 rounds of 1/3
+    assert parts(2048, 256, 128, 148) == 0   # 8 heads at 32K: 124 CTAs, no cut fills the rounds better
     assert parts(512, 256, 128, 148) == 2    # 2 heads at 32K (one of 8 GPUs): 68 CTAs, 2 parts each
     assert parts(1024, 256, 128, 148) == 0   # 4 heads at 32K: 136 CTAs
     assert parts(512, 32, 128, 148) == 2     # 16 heads at 4K
