@@ -418,7 +418,17 @@ def test_split_last_wave_matches_whole_ctas(ref, shape):
         length, hq, hkv, dim, whole.stride(0), whole.stride(2), whole.stride(1),
         packed.attention_scale, 2, None, None, None, 0, None, None,
         torch.cuda.current_stream().cuda_stream))
+    # a scratch too small for the parts (sized for another GPU, say) must give whole CTAs
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    guarded = torch.empty_like(one_call)
+    C._check(C.lib.risa_b200_attention_scratch(
+        p(packed.q), p(packed.k), p(packed.v), p(guarded), p(packed.q_scale), p(packed.k_scale),
+        p(packed.v_scale), p(packed.v_center), None, 0, 0, 0, 0, -1, packed.cta_k, 1, length,
+        length, hq, hkv, dim, guarded.stride(0), guarded.stride(2), guarded.stride(1),
+        packed.attention_scale, 2, None, None, None, 0, None, None, p(small), small.numel(),
+        torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
+    assert torch.equal(guarded, whole)
     assert torch.equal(one_call, two_calls)  # same kernels, same split
     assert_outputs_match(one_call, whole, TOL)
     differing = (one_call != whole).float().mean()
