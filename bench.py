@@ -2,7 +2,7 @@
 """Benchmark of the quantised-attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--seq-len 32768] [--scaling strong|weak] [--no-extras]
+                    [--seq-len 32768] [--scaling strong|weak] [--no-extras] [--report FILE]
 
 Workload: the reference's dense sweep at 32K -- ``int8_attention`` on B=1, Hq=16, Hkv=4, D=128,
 bf16, Lq=Lk=32768, HND contiguous, q/k/v i.i.d. N(0,1) from ``torch.Generator(seed 0)`` in the
@@ -345,9 +345,10 @@ def sparse_leg(seq_len, device, steps, workload="video_blocks"):
                        "per-128-token-block centroids + 0.5 N(0,1); reuse on 0.95 x + 0.05 N(0,1)")}
 
 
-def reference_protocol_ms(fn, warmup=200, samples=10, calls=20):
+def reference_protocol_ms(fn, warmup=200, samples=10, calls=20, keep=None):
     """The reference's timing protocol (benchmarks/common.py:184-220): warm-up calls, then
-    `samples` timings of `calls` back-to-back calls between CUDA events; returns the median."""
+    `samples` timings of `calls` back-to-back calls between CUDA events; returns the median.
+    `keep`: optional list that receives the per-sample times."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -360,10 +361,13 @@ def reference_protocol_ms(fn, warmup=200, samples=10, calls=20):
         stop.record()
         stop.synchronize()
         times.append(start.elapsed_time(stop) / calls)
+    if keep is not None:
+        keep.extend(times)
     return statistics.median(times)
 
 
-def dense_sweep_leg(device, lengths=(512, 1024, 2048, 4096, 8192, 16384, 32768), seeds=(0, 1, 2)):
+def dense_sweep_leg(device, lengths=(512, 1024, 2048, 4096, 8192, 16384, 32768), seeds=(0, 1, 2),
+                    records=None):
     """Full-call latency of every (length, V mode) of the dense sweep, median over seeds of the
     per-seed median, next to the reference's own CUDA kernels on the same inputs (shorter
     protocol for those: 20 warm-ups, 5 samples of 10 calls)."""
@@ -382,8 +386,19 @@ def dense_sweep_leg(device, lengths=(512, 1024, 2048, 4096, 8192, 16384, 32768),
                 q, k, v = make_inputs(length, device, seed=seed)
                 # long sequences need fewer warm-ups to reach steady clocks than 200 x 7 ms
                 warm = 200 if length <= 8192 else 50
+                samples = []
                 ours.append(reference_protocol_ms(
-                    lambda: risa.int8_attention(q, k, v, v_quantization=mode), warmup=warm))
+                    lambda: risa.int8_attention(q, k, v, v_quantization=mode), warmup=warm,
+                    keep=samples))
+                if records is not None:  # one report record per (length, seed, V mode)
+                    from risaattention_b200 import report
+
+                    records.append(report.result_record(
+                        case=f"L{length}", seed=seed, implementation="risa_b200",
+                        v_quantization=mode, stage="full",
+                        shape={"batch": B, "q_heads": HQ, "kv_heads": HKV, "q_length": length,
+                               "kv_length": length, "head_dim": D},
+                        timing=report.timing_summary(samples, calls_per_sample=20, warmup=warm)))
                 if have_ref and seed == seeds[0]:
                     cta_k = 128 if length > 1024 else 64
                     out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
@@ -700,10 +715,11 @@ def run_ours(args):
         del packed
         if not args.no_extras:
             half = max(3, args.steps // 2)
+            records = [] if args.report else None
             for key, leg in (("sparse_reuse", lambda: sparse_leg(L, device, half)),
                              ("sparse_reuse_block_centroids",
                               lambda: sparse_leg(L, device, half, "block_centroids")),
-                             ("dense_sweep", lambda: dense_sweep_leg(device)),
+                             ("dense_sweep", lambda: dense_sweep_leg(device, records=records)),
                              ("video_dit", lambda: video_dit_leg(device, half)),
                              ("edge_sweep", lambda: edge_sweep_leg(device, half))):
                 try:
@@ -711,6 +727,13 @@ def run_ours(args):
                 except Exception as error:  # an extra must never cost the headline line
                     line[key] = {"error": str(error)[:200]}
                 torch.cuda.empty_cache()
+            if args.report and records:
+                from risaattention_b200 import report
+
+                config = {"layout": "hnd", "samples": 10, "calls_per_sample": 20,
+                          "timing_order": "one implementation per pass", "seeds": [0, 1, 2],
+                          "dtype": "bfloat16"}
+                report.write_report(args.report, "dense_sweep", config, records)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(L)
     print(json.dumps(line))
@@ -730,6 +753,9 @@ def main():
                     help="N > 1: split one call's heads over the ranks (strong, default) or run "
                          "one full call per rank (weak)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--report", default=None,
+                    help="also write the dense sweep as a schema_version 2 report (the reference's "
+                         "benchmark file layout) to this path")
     ap.add_argument("--no-extras", "--no-sparse", dest="no_extras", action="store_true",
                     help="skip the sparse-reuse, dense-sweep, video-DiT and edge-sweep legs")
     args = ap.parse_args()
