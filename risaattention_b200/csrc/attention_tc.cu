@@ -24,6 +24,9 @@
 // Numerics: reference csrc/kernels/attention_int8.cuh:427-1026 via softmax_row.cuh.  The integer
 // products are exact, so probabilities, capture statistics and block masses are bit-identical to
 // the row-per-thread kernel; without capture the denominator is kept in one partial instead of four.
+// Dense unmasked launches may cut the CTAs of their last, partial wave into key-range parts (see
+// split_parts below): a part runs the same loop over its share of the key tiles and leaves its
+// unnormalised rows, maximum and denominator in scratch for tail_merge_kernel.
 // Every mbarrier wait is bounded (tc_ptx.cuh): when one expires the CTA's waiters leave, the producer
 // waits for its loads in flight, the rows of the CTA are written as NaN and a device status word
 // records the site; the CTA then exits instead of spinning.
