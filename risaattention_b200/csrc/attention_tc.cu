@@ -182,12 +182,15 @@ struct Bars {
 template <bool CAPTURE, int CTA_K, int KIND>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
-                                                 uint16_t* sums, PackMultipliers mul) {
+                                                 uint16_t* sums, PackMultipliers mul,
+                                                 int max_floor = INT_MIN) {
   // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
   // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
   // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
   uint32_t raw_a[32], raw[32];
-  int imax[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  // max_floor: where the lane maxima start; the last visited tile starts them at -50000 (the
+  // reference's generic arithmetic), every other tile below any score
+  int imax[4] = {max_floor, max_floor, max_floor, max_floor};
 #pragma unroll
   for (int h = 0; h < CTA_K / 64; ++h) {
     tmem_load32(tmem_row + 64 * h, raw_a);
@@ -726,9 +729,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       tc_fence_after();
       // causal: tiles that end at or before the CTA's first query are fully visible
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
-      if (int_scores && !last)
+      // A last tile without tail keys differs from the others only in where its maxima start;
+      // with tail keys (their scores are zero-filled, not masked) it takes the general path.
+      if (int_scores && (!last || a.k_len % CTA_K == 0))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
-                                                     my_sums, pack_mul);
+                                                     my_sums, pack_mul, last ? -50000 : INT_MIN);
       else if (below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
@@ -957,12 +962,18 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
                     2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
 #pragma unroll
       for (int ch = 0; ch < kOut; ch += 8) {
+        // eight channels' scales and centres as four 16-byte loads (the same addresses in every
+        // thread: one broadcast each)
+        float scale8[8], centre8[8];
+        *reinterpret_cast<float4*>(scale8) = __ldg(reinterpret_cast<const float4*>(vs + ch));
+        *reinterpret_cast<float4*>(scale8 + 4) = __ldg(reinterpret_cast<const float4*>(vs + ch + 4));
+        *reinterpret_cast<float4*>(centre8) = __ldg(reinterpret_cast<const float4*>(vc + ch));
+        *reinterpret_cast<float4*>(centre8 + 4) = __ldg(reinterpret_cast<const float4*>(vc + ch + 4));
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          float r0 = fmaf(O[ch + 2 * i] * inv, __ldg(vs + ch + 2 * i), __ldg(vc + ch + 2 * i));
-          float r1 = fmaf(O[ch + 2 * i + 1] * inv, __ldg(vs + ch + 2 * i + 1),
-                          __ldg(vc + ch + 2 * i + 1));
+          float r0 = fmaf(O[ch + 2 * i] * inv, scale8[2 * i], centre8[2 * i]);
+          float r1 = fmaf(O[ch + 2 * i + 1] * inv, scale8[2 * i + 1], centre8[2 * i + 1]);
           if (zero) r0 = r1 = 0.0f;
           if (a.out_dtype_code == 1) {
             const __half2 h = __floats2half2_rn(r0, r1);
@@ -1290,7 +1301,8 @@ bool attention_tc_supported(const AttentionArgs& a) {
                      (a.head_dim == 64 && a.cta_k == 64);
   auto aligned16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   return shape && padded >= 128 && encode_fn() != nullptr && aligned16(a.q) && aligned16(a.k) &&
-         aligned16(a.v) && aligned16(a.o) && a.o_stride_b % 8 == 0 &&
+         aligned16(a.v) && aligned16(a.o) && aligned16(a.v_scale) && aligned16(a.v_center) &&
+         a.o_stride_b % 8 == 0 &&
          a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
 }
 
