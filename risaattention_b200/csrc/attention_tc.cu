@@ -99,7 +99,8 @@ struct SmemLayout {
   static constexpr int sums = stats + 4 * 128 * 8;         // uint16 [slots][128][CTA_K / 4] (capture)
   static constexpr int mask_stage = sums + 4 * 128 * (CTA_K / 2);
   static constexpr int rowstate = mask_stage + kMaskStageBytes;  // float [5][128]: m, d[4] (capture)
-  static constexpr int bars = rowstate + 5 * 128 * 4;      // 8-byte mbarriers
+  static constexpr int v_affine = rowstate + 5 * 128 * 4;  // float [2][128]: V scales, V centres
+  static constexpr int bars = v_affine + 2 * 128 * 4;      // 8-byte mbarriers
   static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 7 * 4 + 3;  // a few spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int gave_up = tmem_slot + 8;            // site of the first expired wait, or 0
@@ -848,6 +849,15 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
 #pragma unroll
     for (int i = 0; i < kOut / 2; ++i) O2[i] = 0ull;
     bool ok = true;
+    // The epilogue multiplies every output channel by its V scale and adds its V centre; the two
+    // vectors are the same for all rows, so they are brought into shared memory now (their global
+    // load latency passes during the first tiles instead of in front of every store).
+    float* v_affine = reinterpret_cast<float*>(smem + L::v_affine);
+    if (row_in < kOut) {
+      v_affine[row_in] = __ldg(a.v_scale + kvh * D + kOut * half + row_in);
+      v_affine[128 + row_in] = __ldg(a.v_center + kvh * D + kOut * half + row_in);
+    }
+    asm volatile("bar.sync 3, 128;" ::: "memory");
     // One iteration per tile and one barrier round trip per iteration: a finished accumulator
     // (OFULL) implies that the tile's probabilities and statistics were published before (P.V is
     // only issued after them), so the statistics need no wait of their own.  This group is the one
@@ -956,19 +966,19 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       // dense path: denominator and rows share the stale maximum's units, the quotient is exact
       const float inv = rcp_approx(denom);
       const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
-      const float* vs = a.v_scale + kvh * D + kOut * half;
-      const float* vc = a.v_center + kvh * D + kOut * half;
+      const float* vs = v_affine;
+      const float* vc = v_affine + 128;
       char* o_row = static_cast<char*>(a.o) + 2 * kOut * half +
                     2 * (batch * a.o_stride_b + head * a.o_stride_h + int64_t(row) * a.o_stride_n);
 #pragma unroll
       for (int ch = 0; ch < kOut; ch += 8) {
-        // eight channels' scales and centres as four 16-byte loads (the same addresses in every
-        // thread: one broadcast each)
+        // eight channels' scales and centres as four 16-byte shared-memory loads (the same
+        // addresses in every thread: one broadcast each)
         float scale8[8], centre8[8];
-        *reinterpret_cast<float4*>(scale8) = __ldg(reinterpret_cast<const float4*>(vs + ch));
-        *reinterpret_cast<float4*>(scale8 + 4) = __ldg(reinterpret_cast<const float4*>(vs + ch + 4));
-        *reinterpret_cast<float4*>(centre8) = __ldg(reinterpret_cast<const float4*>(vc + ch));
-        *reinterpret_cast<float4*>(centre8 + 4) = __ldg(reinterpret_cast<const float4*>(vc + ch + 4));
+        *reinterpret_cast<float4*>(scale8) = *reinterpret_cast<const float4*>(vs + ch);
+        *reinterpret_cast<float4*>(scale8 + 4) = *reinterpret_cast<const float4*>(vs + ch + 4);
+        *reinterpret_cast<float4*>(centre8) = *reinterpret_cast<const float4*>(vc + ch);
+        *reinterpret_cast<float4*>(centre8 + 4) = *reinterpret_cast<const float4*>(vc + ch + 4);
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -1301,8 +1311,7 @@ bool attention_tc_supported(const AttentionArgs& a) {
                      (a.head_dim == 64 && a.cta_k == 64);
   auto aligned16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   return shape && padded >= 128 && encode_fn() != nullptr && aligned16(a.q) && aligned16(a.k) &&
-         aligned16(a.v) && aligned16(a.o) && aligned16(a.v_scale) && aligned16(a.v_center) &&
-         a.o_stride_b % 8 == 0 &&
+         aligned16(a.v) && aligned16(a.o) && a.o_stride_b % 8 == 0 &&
          a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
 }
 
