@@ -384,14 +384,18 @@ __device__ __forceinline__ void mask_prefetch_runs(const AttentionArgs& a, int b
 // applied, keys past the end removed -- takes their maxima and writes them back over the raw
 // scores in tensor memory; pass 2 reads those floats, so masks are fetched once per tile.
 // mask_stage: the warp's staging area (64-key-tile kernels), or nullptr.
-template <bool CAPTURE, int CTA_K>
+// MASKED = false is the instantiation for causal diagonals and ragged last tiles of calls without
+// a mask: none of the mask code is in it, which matters because every CTA of such a call runs it
+// once or twice, cold.
+template <bool CAPTURE, int CTA_K, bool MASKED>
 __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int batch, int head,
                                                      bool row_ok, uint32_t tmem_row,
                                                      const float (&sc)[4], unsigned char* p_row,
                                                      int swz, float2* stat, uint16_t* sums,
                                                      bool int_scores, bool last, int row, int c0,
                                                      uint32_t* mask_stage) {
-  const bool causal = a.is_causal != 0, masked = a.mask != nullptr;
+  const bool causal = a.is_causal != 0;
+  constexpr bool masked = MASKED;
   const int k_len = a.k_len;
   // per-query masks go through the staging area; masks broadcast over queries are read directly
   // (all lanes of a warp then ask for the same address)
@@ -738,10 +742,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       else if (below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
+      else if (a.mask != nullptr)
+        softmax_tile_general<CAPTURE, CTA_K, true>(a, batch, head, row_ok, tmem_row, sc, p_row,
+                                                   row_in & 7, stat, my_sums, int_scores, last, row,
+                                                   tile * CTA_K, mask_stage);
       else
-        softmax_tile_general<CAPTURE, CTA_K>(a, batch, head, row_ok, tmem_row, sc, p_row,
-                                             row_in & 7, stat, my_sums, int_scores, last, row,
-                                             tile * CTA_K, mask_stage);
+        softmax_tile_general<CAPTURE, CTA_K, false>(a, batch, head, row_ok, tmem_row, sc, p_row,
+                                                    row_in & 7, stat, my_sums, int_scores, last,
+                                                    row, tile * CTA_K, mask_stage);
       // every score of the tile has been read (the loads were waited for) and the probabilities
       // are in shared memory: P.V may now overwrite the buffer
       tc_fence_before();
