@@ -506,6 +506,9 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     by = (unit / n_q) % rows_y;
     batch = unit / (n_q * rows_y);
   }
+  // Causal CTAs visit bx + 1 query blocks' worth of key tiles: the longest ones are launched first,
+  // so that the short ones fill the end of the launch instead of the long ones stretching it.
+  if (a.is_causal) bx = n_q - 1 - bx;
   const int head = by / L::kHalves, half = by % L::kHalves;
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const int64_t bh = int64_t(batch) * a.q_heads + head;
