@@ -537,7 +537,9 @@ def cta_waves(q_heads_local, seq_len, sms=None):
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     ctas = q_heads_local * ((seq_len + 127) // 128)
     parts = tail_split_parts(ctas, (seq_len + 127) // 128, sms)
-    waves = ctas // sms + (ctas % sms > 0) / max(parts, 1)
+    rest = ctas % sms
+    # the last wave: whole CTAs, or ceil(rest * parts / sms) rounds of 1 / parts of a CTA's time
+    waves = ctas // sms + (-(-rest * parts // sms) / parts if parts else float(rest > 0))
     return {"ctas": ctas, "sms": sms, "waves": ctas / sms,
             "last_wave_key_range_parts": parts,
             "wave_efficiency": (ctas / sms) / waves}
