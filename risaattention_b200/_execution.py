@@ -31,7 +31,7 @@ def execute_dense_attention(q, k, v, *, scale=None, attn_mask=None, use_midpoint
         dim, k.shape[2], has_mask=attn_mask is not None and attn_mask.stride(-2) != 0)
     out_dtype = _output_dtype(input_dtype)
     output = torch.empty(batch, q_heads, q_len, dim, dtype=out_dtype, device=q.device)
-    stream = torch.cuda.current_stream(q.device).cuda_stream
+    stream = _backend.current_stream_ptr(q.device)
     if attn_mask is None:
         # one native call, one scratch allocation: what bounds short sequences is the host side
         scratch = torch.empty(
@@ -156,7 +156,7 @@ def int8_attention_from_prequantized(quantized, *, sparse_pattern=None, output_l
     _backend._C.risa_sdpa_prequantized(
         quantized.q, quantized.k, quantized.v, output, quantized.q_scale, quantized.k_scale,
         quantized.v_scale, quantized.v_center, quantized.cta_k, quantized.attention_scale,
-        DTYPE_CODES[out_dtype], torch.cuda.current_stream(device).cuda_stream,
+        DTYPE_CODES[out_dtype], _backend.current_stream_ptr(device),
         attn_mask=quantized.attn_mask,
         sparse_row_offsets=None if sparse_pattern is None else sparse_pattern.row_offsets,
         sparse_block_indices=None if sparse_pattern is None else sparse_pattern.block_indices,

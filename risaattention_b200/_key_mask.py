@@ -13,5 +13,5 @@ def prepare_key_mask_tiles(mask, key_block_size, query_length, scale, is_causal)
     tiles = torch.empty((batch, heads, -(-length // key_block_size) + 1), device=mask.device,
                         dtype=torch.int32)
     _backend._C.prepare_key_mask_tiles(mask, tiles, key_block_size,
-                                       torch.cuda.current_stream(mask.device).cuda_stream)
+                                       _backend.current_stream_ptr(mask.device))
     return tiles

@@ -59,7 +59,7 @@ def quantize_into(buffers, q, k, v, key_block_size, use_midpoint_affine, kv_tabl
         q, k, v, buffers.q_codes, buffers.q_scales, buffers.k_codes, buffers.k_scales,
         buffers.v_codes, buffers.v_scales, buffers.v_centers, key_block_size,
         DTYPE_CODES[q.dtype], use_midpoint_affine,
-        torch.cuda.current_stream(q.device).cuda_stream, buffers.anchors, kv_table,
+        _backend.current_stream_ptr(q.device), buffers.anchors, kv_table,
         workspace=buffers.workspace)
 
 
@@ -92,7 +92,7 @@ def prequantize_int8_attention(q, k, v, *, scale=None, attn_mask=None, v_quantiz
         # offset so LSE values of different key windows can be merged.
         lse_shift = torch.empty(q.shape[:3], device=q.device, dtype=torch.float32)
         _backend._C.risa_lse_shift(q, k, buffers.anchors, lse_shift, attention_scale,
-                                   torch.cuda.current_stream(q.device).cuda_stream)
+                                   _backend.current_stream_ptr(q.device))
     return PrequantizedInt8Attention(
         q=buffers.q_codes, k=buffers.k_codes, v=buffers.v_codes, q_scale=buffers.q_scales,
         k_scale=buffers.k_scales, v_scale=buffers.v_scales, v_center=buffers.v_centers,

@@ -31,7 +31,7 @@ def select_retained_mass_csr(masses: torch.Tensor, theta: float):
                           dtype=torch.uint8, device=dev)
     _backend._C.select_retained_mass_csr(sorted_mass, order, counts, support, row_totals,
                                          row_offsets, storage, summary, scratch, theta,
-                                         torch.cuda.current_stream(dev).cuda_stream)
+                                         _backend.current_stream_ptr(dev))
     selected_mass, total_mass, selected_blocks = summary.tolist()
     return row_offsets, storage[: int(selected_blocks)], selected_mass / max(total_mass, 1e-20)
 
@@ -53,7 +53,7 @@ def _construct_in_pass(quantized, theta, output_layout, rows, k_blocks):
     if not is_available(device):
         raise RuntimeError(UNAVAILABLE)
     native = _backend._C
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _backend.current_stream_ptr(device)
     output = allocate_output(quantized, output_layout)
     counts = torch.empty(rows, dtype=torch.int32, device=device)
     bitmaps = torch.empty(rows, (k_blocks + 31) // 32, dtype=torch.int32, device=device)
