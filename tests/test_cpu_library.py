@@ -28,6 +28,19 @@ def test_contract_violations_are_reported_not_computed():
     lib.risa_b200_quantize_v_workspace_size.restype = ctypes.c_size_t
     assert lib.risa_b200_quantize_v_workspace_size(1, 4, 32768, 128) > 0
     assert lib.risa_b200_quantize_v_workspace_size(0, 4, 32768, 128) == 0
+    # the combined quantiser checks V's contract first and Q/K's before any launch: null tensors are
+    # a contract violation (status 1) with a message, not a crash
+    c_vp, c_i32, c_i64, c_sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+    lib.risa_b200_quantize_qkv.restype = c_i32
+    lib.risa_b200_quantize_qkv.argtypes = ([c_vp] * 10 + [c_i32] * 8 + [c_i64] * 9 + [c_i32] * 2
+                                          + [c_vp] * 4 + [c_sz, c_vp])
+    status = lib.risa_b200_quantize_qkv(*([None] * 10), 1, 16, 128, 4, 128, 128, 64, 128,
+                                        *([128] * 9), 2, 0, None, None, None, None, 0, None)
+    assert status == 1 and b"null tensor" in lib.risa_b200_last_error()
+    # scratch sizes are zero for shapes that are never split and for nonsense
+    lib.risa_b200_attention_scratch_size.restype = c_sz
+    assert lib.risa_b200_attention_scratch_size(0, 16, 128, 128, 128, 64) == 0
+    assert lib.risa_b200_attention_scratch_size(1, 16, 128, 128, 128, 96) == 0
 
 
 def test_public_names_match_reference():
