@@ -207,6 +207,33 @@ def test_graph_capture_and_streams():
     assert torch.equal(actual, expected)
 
 
+def test_graph_replays_follow_their_inputs():
+    """A captured dense call (chained launches, split last wave and merge launch included) replayed
+    after its inputs were overwritten in place gives what an eager call gives on the new inputs."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(1, 16, 4096, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(1, 4, 4096, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(1, 4, 4096, 128, device="cuda", generator=g).bfloat16()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            risa.int8_attention(q, k, v)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = risa.int8_attention(q, k, v)
+        for _ in range(3):
+            q.copy_(torch.randn(q.shape, device="cuda", generator=g).bfloat16())
+            k.copy_(torch.randn(k.shape, device="cuda", generator=g).bfloat16())
+            v.copy_(torch.randn(v.shape, device="cuda", generator=g).bfloat16())
+            graph.replay()
+            replayed = captured.clone()
+            eager = risa.int8_attention(q, k, v)
+            assert torch.equal(replayed, eager)
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+
+
 def test_host_pipeline_matches_device_call():
     """Host-resident operands, pipelined per KV head over three streams: identical bits to one
     device-resident call (every stage is independent per head)."""
