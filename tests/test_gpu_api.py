@@ -176,6 +176,40 @@ def test_key_mask_metadata_and_skipping():
     torch.testing.assert_close(actual, generic, atol=0.002, rtol=0.01)
 
 
+@pytest.mark.parametrize("mode", ["absmax", "midpoint_affine"])
+def test_key_mask_is_read_at_call_time(mode):
+    """The visible-tile list of a broadcast key mask is rebuilt by every call, inside a captured
+    graph as well: a mask changed in place after prequantisation (or between replays) is the mask
+    the next call sees (reference behaviour: tests/cuda/test_key_mask_tiles.py:79-128)."""
+    g = torch.Generator(device="cuda").manual_seed(21)
+    q = torch.randn(1, 4, 300, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(1, 2, 1300, 128, device="cuda", generator=g).bfloat16()
+    v = torch.full_like(k, 1.5)
+    mask = torch.ones(1, 1, 1, 1300, device="cuda", dtype=torch.bool)
+    mask[..., :640] = False
+    packed = risa.prequantize_int8_attention(q, k, v, attn_mask=mask, v_quantization=mode)
+    hidden_prefix = risa.int8_attention_from_prequantized(packed)
+    mask.fill_(True)  # in place: `packed` holds the same storage
+    all_visible = risa.int8_attention_from_prequantized(packed)
+    fresh = risa.int8_attention_from_prequantized(
+        risa.prequantize_int8_attention(q, k, v, attn_mask=mask.clone(), v_quantization=mode))
+    assert torch.equal(all_visible, fresh)
+    assert torch.allclose(hidden_prefix.float(), all_visible.float(), atol=0.02)  # V is constant
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            risa.int8_attention_from_prequantized(packed)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = risa.int8_attention_from_prequantized(packed)
+        mask.fill_(False)  # every key hidden: rows must come out as zeros
+        graph.replay()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(captured) == 0
+
+
 @pytest.mark.parametrize("length", [512, 2048])
 @pytest.mark.parametrize("mode", ["absmax", "midpoint_affine"])
 def test_accuracy_against_fp32_sdpa(length, mode):
