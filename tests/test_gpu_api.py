@@ -286,3 +286,57 @@ def test_host_pipeline_matches_device_call():
         assert got.is_pinned() and torch.equal(got, want.cpu())
     with pytest.raises(ValueError, match="does not support"):
         risa.int8_attention_from_host(q, k, v, return_lse=True)
+
+
+@pytest.mark.parametrize("mode", ["absmax", "midpoint_affine"])
+def test_causal_rows_never_see_later_values(mode):
+    """Values that only exist at later positions cannot reach earlier causal rows, dense or through
+    a retained pattern (reference behaviour: tests/cuda/test_risa_attention.py:151-165)."""
+    q = torch.zeros(1, 1, 200, 64, device="cuda", dtype=torch.float16)
+    v = torch.zeros_like(q)
+    v[:, :, 128:] = 64.0
+    dense, pattern = risa.construct_sparse_int8_attention(q, q, v, is_causal=True, theta=1.0,
+                                                          v_quantization=mode)
+    sparse = risa.sparse_int8_attention(q, q, v, pattern, is_causal=True, v_quantization=mode)
+    assert dense[:, :, :128].abs().max() <= 0.01
+    assert dense[:, :, 199].float().mean() > 10  # the last row sees 72 of 200 non-zero values
+    torch.testing.assert_close(sparse, dense, atol=0.05, rtol=0.01)
+
+
+@pytest.mark.parametrize("mode", ["absmax", "midpoint_affine"])
+def test_key_bias_with_large_tiles_and_lse(mode):
+    """A float mask broadcast over queries keeps 128-key tiles; with zero scores the output is the
+    constant value and the LSE is the log-sum-exp of the bias (reference behaviour:
+    tests/cuda/test_risa_attention.py:167-179)."""
+    q = torch.zeros(1, 2, 17, 128, device="cuda", dtype=torch.float16)
+    k = torch.zeros(1, 1, 1200, 128, device="cuda", dtype=torch.float16)
+    v = torch.full_like(k, 2.5)
+    bias = torch.linspace(-4, 0, 1200, device="cuda")[None, None, None, :]
+    packed = risa.prequantize_int8_attention(q, k, v, attn_mask=bias, return_lse=True,
+                                             v_quantization=mode)
+    assert packed.cta_k == 128
+    out, lse = risa.int8_attention_from_prequantized(packed, return_lse=True)
+    assert (out.float() - 2.5).abs().max() <= 0.03
+    want = bias.logsumexp(-1).expand(1, 2, 17)
+    assert (lse - want).abs().max() <= 0.01
+
+
+def test_packed_value_rows_beyond_two_gibibytes():
+    """56 heads x 128 channels of 299 521 keys: the packed V tensor is 2.15 GB, so element offsets
+    into it do not fit 32 bits (the reference keeps this as an opt-in large test:
+    tests/cuda/test_risa_attention.py:195-208).  Constant values must come back exactly."""
+    if torch.cuda.mem_get_info()[0] < 24 * 1024 ** 3:
+        pytest.skip("needs 24 GiB of free device memory")
+    heads, keys = 56, 299521
+    q = torch.zeros(1, heads, 1, 128, device="cuda", dtype=torch.float16)
+    k = torch.zeros(1, heads, keys, 128, device="cuda", dtype=torch.float16)
+    v = torch.ones_like(k)
+    v[:, -1] = 3.0  # the last head's rows lie wholly beyond the 2 GiB mark
+    for mode in ("absmax", "midpoint_affine"):
+        out = risa.int8_attention(q, k, v, v_quantization=mode)
+        torch.cuda.synchronize()
+        assert (out[:, :-1].float() - 1.0).abs().max() <= 0.01
+        assert (out[:, -1].float() - 3.0).abs().max() <= 0.03
+        del out
+    del q, k, v
+    torch.cuda.empty_cache()
