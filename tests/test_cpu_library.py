@@ -146,3 +146,45 @@ def test_split_last_wave_rule_known_answers():
     assert parts(128, 256, 128, 148) == 0    # less than one wave
     assert parts(296, 256, 128, 148) == 0    # whole waves only
     assert parts(512, 256, 128, 0) == 0
+
+
+def test_public_call_passes_causal_flag_and_value_mode_to_the_launch():
+    """Every combination of V mode, causal flag and mask presence reaches the function that
+    launches the kernels unchanged (after reference tests/contracts/test_risa_attention.py:29-43)."""
+    from unittest.mock import patch
+
+    import risaattention_b200 as risa
+    from risaattention_b200 import dense
+
+    q = torch.randn(1, 2, 3, 64)
+    for mode in ("midpoint_affine", "absmax"):
+        for causal in (False, True):
+            for mask in (None, torch.ones(3, 3, dtype=torch.bool)):
+                with patch.object(dense, "execute_dense_attention",
+                                  return_value=q.clone()) as launch:
+                    risa.int8_attention(q, q, q, attn_mask=mask, is_causal=causal,
+                                        v_quantization=mode)
+                assert launch.call_count == 1
+                assert launch.call_args.kwargs["is_causal"] == causal
+                assert launch.call_args.kwargs["use_midpoint_affine"] == (mode == "midpoint_affine")
+                assert (launch.call_args.kwargs["attn_mask"] is None) == (mask is None)
+
+
+def test_mask_identity_follows_in_place_writes():
+    """A retained pattern is bound to the mask it was built with: an in-place write changes the
+    mask's identity; masked and causal scores follow the FP32 specification (after reference
+    tests/contracts/test_risa_attention.py:59-67)."""
+    from risaattention_b200._validation import apply_score_mask, mask_signature
+
+    mask = torch.ones(1, 1, 3, 5, dtype=torch.bool)
+    before = mask_signature(mask)
+    assert before == mask_signature(mask)
+    mask[..., 0] = False
+    assert before != mask_signature(mask)
+    assert mask_signature(None) is None
+    scores = apply_score_mask(torch.zeros(1, 1, 3, 5), mask, True, 0)
+    assert torch.isneginf(scores[..., 0, :]).all()
+    assert torch.isneginf(scores[..., 1, 2:]).all()
+    assert scores[0, 0, 1, 1] == 0
+    bias = torch.full((1, 1, 3, 5), 0.5)
+    assert torch.equal(apply_score_mask(torch.zeros(1, 1, 3, 5), bias, False, 0), bias)
