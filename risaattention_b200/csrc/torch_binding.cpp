@@ -10,7 +10,9 @@
 
 #include <ATen/DLConvertor.h>
 
+#include <climits>
 #include <cstdint>
+#include <initializer_list>
 #include <optional>
 #include <stdexcept>
 #include <string>
@@ -59,6 +61,24 @@ void* address_of(const py::object& object, const char* what) {
 
 void* stream_of(uintptr_t stream_ptr) { return reinterpret_cast<void*>(stream_ptr); }
 
+// True when `t` has this element type and exactly these sizes, densely packed in row-major order.
+bool packed_as(const at::Tensor& t, at::ScalarType type, std::initializer_list<int64_t> sizes) {
+  if (t.scalar_type() != type || t.dim() != int64_t(sizes.size())) return false;
+  int64_t axis = 0;
+  for (const int64_t size : sizes)
+    if (t.size(axis++) != size) return false;
+  return t.is_contiguous();
+}
+
+// Visible-tile lists hold, per (batch, query head), the ids of the key tiles with a visible key
+// and, in the last slot, their count (csrc/bindings.cpp:52-68).
+void require_key_mask_tiles(const at::Tensor& tiles, int64_t batch, int64_t q_heads,
+                            int64_t key_length, int tile_size) {
+  if (!tiles.is_cuda() ||
+      !packed_as(tiles, at::kInt, {batch, q_heads, (key_length + tile_size - 1) / tile_size + 1}))
+    throw std::runtime_error("key mask tiles must be contiguous CUDA int32 [B,Hq,tiles+1]");
+}
+
 int dtype_code(const at::Tensor& t) {
   switch (t.scalar_type()) {
     case at::kFloat: return 0;
@@ -76,10 +96,38 @@ void quantize_tensors(const at::Tensor& q, const at::Tensor& k, const at::Tensor
                       const at::Tensor& v_center, int cta_k, int input_dtype_code,
                       bool use_midpoint_affine, uintptr_t stream_ptr, void* anchors,
                       void* kv_table, void* q_table, std::optional<at::Tensor> workspace) {
-  if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4 || v_int8.dim() != 2)
-    throw std::runtime_error("risa_sdpa_quantize: q, k, v must be 4D and packed V 2D");
+  // shapes the kernels index by, checked in the order of the reference module
+  // (csrc/bindings.cpp:196-246); what the kernels themselves can take is checked behind the C-ABI
+  if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4)
+    throw std::runtime_error(
+        "risa_sdpa_quantize: q, k, and v must be 4D [batch_size,num_heads,L,head_dim]");
+  if (cta_k != 64 && cta_k != 128)
+    throw std::runtime_error("risa_sdpa_quantize: cta_k must be 64 or 128");
+  if (input_dtype_code < 0 || input_dtype_code > 2)
+    throw std::runtime_error(
+        "risa_sdpa_quantize: input_dtype_code must be 0 (fp32), 1 (fp16), or 2 (bf16)");
+  if (anchors == nullptr)
+    throw std::runtime_error("risa_sdpa_quantize: anchor_indices scratch is required");
   const int b = int(q.size(0)), hq = int(q.size(1)), lq = int(q.size(2)), d = int(q.size(3));
   const int hkv = int(k.size(1)), lk = int(k.size(2));
+  const int64_t padded = int64_t(lk + cta_k - 1) / cta_k * cta_k;
+  if (k.size(0) != b || v.size(0) != b || v.size(1) != hkv || v.size(2) != lk || k.size(3) != d ||
+      v.size(3) != d)
+    throw std::runtime_error("risa_sdpa_quantize: incompatible q, k, and v shapes");
+  if (dtype_code(q) != input_dtype_code || dtype_code(k) != input_dtype_code ||
+      dtype_code(v) != input_dtype_code)
+    throw std::runtime_error("risa_sdpa_quantize: q, k, and v must have the element type "
+                             "input_dtype_code names");
+  if (!packed_as(q_int8, at::kChar, {b, hq, lq, d}) || !packed_as(k_int8, at::kChar, {b, hkv, lk, d}) ||
+      !packed_as(v_int8, at::kChar, {int64_t(b) * hkv * d, padded}))
+    throw std::runtime_error("risa_sdpa_quantize: incompatible INT8 output shapes");
+  const int64_t q_blocks = (lq + 127) / 128, k_tiles = padded / cta_k;
+  if (q_scale.numel() < int64_t(b) * hq * q_blocks * (d == 256 ? 64 : 32) ||
+      k_scale.numel() < int64_t(b) * hkv * k_tiles * 4 || v_scale.numel() < int64_t(b) * hkv * d ||
+      v_center.numel() < int64_t(b) * hkv * d || !q_scale.is_contiguous() ||
+      !k_scale.is_contiguous() || !v_scale.is_contiguous() || !v_center.is_contiguous())
+    throw std::runtime_error("risa_sdpa_quantize: scale and centre tensors must be contiguous "
+                             "float32 with one entry per quantization group");
   if (!workspace.has_value()) {
     // scratch of the V quantiser, taken from the caching allocator on the current stream
     const size_t bytes = risa_b200_quantize_v_workspace_size(b, hkv, lk, d);
@@ -105,15 +153,40 @@ void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at
                     const std::optional<at::Tensor>& block_mass, bool is_causal,
                     const std::optional<at::Tensor>& lse,
                     const std::optional<at::Tensor>& key_mask_tiles) {
-  if (q_int8.dim() != 4 || k_int8.dim() != 4 || o.dim() != 4)
-    throw std::runtime_error("risa_sdpa_prequantized: packed q, k and the output must be 4D");
+  // checked in the order of the reference module (csrc/bindings.cpp:290-432)
+  if (q_int8.dim() != 4 || k_int8.dim() != 4 || v_int8.dim() != 2 || o.dim() != 4)
+    throw std::runtime_error("risa_sdpa_prequantized: q/k/o must be 4D and packed v must be 2D");
+  if (cta_k != 64 && cta_k != 128)
+    throw std::runtime_error("risa_sdpa_prequantized: cta_k must be 64 or 128");
+  if (output_dtype_code != 1 && output_dtype_code != 2)
+    throw std::runtime_error(
+        "risa_sdpa_prequantized: output_dtype_code must be 1 (fp16) or 2 (bf16)");
   const int64_t b = q_int8.size(0), hq = q_int8.size(1), lq = q_int8.size(2), d = q_int8.size(3);
   const int64_t hkv = k_int8.size(1), lk = k_int8.size(2);
   const int64_t padded = (lk + cta_k - 1) / cta_k * cta_k;
-  if (v_int8.dim() != 2 || v_int8.size(0) != b * hkv * d || v_int8.size(1) != padded ||
+  if (cta_k == 128 && d == 64)
+    throw std::runtime_error("risa_sdpa_prequantized: cta_k 128 requires head_dim 128 or 256");
+  if (row_offsets.has_value() != block_indices.has_value())
+    throw std::runtime_error(
+        "risa_sdpa_prequantized: sparse row offsets and block indices must be provided together");
+  if (block_mass.has_value() && row_offsets.has_value())
+    throw std::runtime_error("risa_sdpa_prequantized: block mass requires dense attention");
+  if (v_int8.size(0) != b * hkv * d || v_int8.size(1) != padded ||
       o.size(0) != b || o.size(1) != hq || o.size(2) != lq || o.size(3) != d ||
       k_int8.size(0) != b || k_int8.size(3) != d)
     throw std::runtime_error("risa_sdpa_prequantized: incompatible quantized tensor shapes");
+  if (q_int8.scalar_type() != at::kChar || k_int8.scalar_type() != at::kChar ||
+      v_int8.scalar_type() != at::kChar ||
+      o.scalar_type() != (output_dtype_code == 1 ? at::kHalf : at::kBFloat16))
+    throw std::runtime_error("risa_sdpa_prequantized: packed operands must be int8 and the "
+                             "output of the type output_dtype_code names");
+  const int64_t q_blocks = (lq + 127) / 128, k_tiles = padded / cta_k;
+  if (q_scale.numel() < b * hq * q_blocks * (d == 256 ? 64 : 32) ||
+      k_scale.numel() < b * hkv * k_tiles * 4 || v_scale.numel() < b * hkv * d ||
+      v_center.numel() < b * hkv * d || !q_scale.is_contiguous() || !k_scale.is_contiguous() ||
+      !v_scale.is_contiguous() || !v_center.is_contiguous())
+    throw std::runtime_error("risa_sdpa_prequantized: scale and centre tensors must be "
+                             "contiguous float32 with one entry per quantization group");
   const bool hnd = (lq <= 1 || o.stride(2) == d) && (hq <= 1 || o.stride(1) == lq * d);
   const bool nhd = (hq <= 1 || o.stride(1) == d) && (lq <= 1 || o.stride(2) == hq * d);
   if (!q_int8.is_contiguous() || !k_int8.is_contiguous() || !v_int8.is_contiguous() ||
@@ -140,6 +213,21 @@ void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at
     mask_ptr = m.data_ptr();
     for (int i = 0; i < 4; ++i) ms[i] = m.stride(i);
   }
+  if (row_offsets.has_value()) {
+    if (!packed_as(*row_offsets, at::kInt, {b * hq * q_blocks + 1}) ||
+        block_indices->dim() != 1 || block_indices->scalar_type() != at::kInt)
+      throw std::runtime_error("risa_sdpa_prequantized: sparse support must be contiguous int32 "
+                               "CSR with batch_size*Hq*ceil(query_length/128)+1 row offsets");
+    if (!block_indices->is_contiguous() || block_indices->numel() == 0)
+      throw std::runtime_error(
+          "risa_sdpa_prequantized: sparse CSR tensors must be non-empty and contiguous");
+  }
+  if (block_mass.has_value() &&
+      !packed_as(*block_mass, at::kFloat,
+                 {b * hq * q_blocks * k_tiles + b * hq * lq * (2 * k_tiles + 2)}))
+    throw std::runtime_error("risa_sdpa_prequantized: block_mass workspace must contain "
+                             "mass rows followed by captured tile statistics and softmax state");
+  if (key_mask_tiles.has_value()) require_key_mask_tiles(*key_mask_tiles, b, hq, lk, cta_k);
   const int64_t o_b = b <= 1 ? hq * lq * d : o.stride(0);
   const int64_t o_n = lq <= 1 ? d : o.stride(2);
   const int64_t o_h = hq <= 1 ? lq * d : o.stride(1);
@@ -240,19 +328,33 @@ void select_retained_mass_csr(py::object sorted_mass, py::object descending_indi
   const at::Tensor mass = tensor_of(sorted_mass, "sorted_mass");
   const at::Tensor order = tensor_of(descending_indices, "descending_indices");
   const at::Tensor scan = tensor_of(scan_workspace, "scan_workspace");
-  if (mass.dim() != 2 || mass.scalar_type() != at::kFloat || order.scalar_type() != at::kLong)
-    throw std::runtime_error("select_retained_mass_csr: sorted masses must be 2D float32 with "
-                             "int64 indices");
+  const at::Tensor count = tensor_of(counts, "counts"), kept = tensor_of(support, "support"),
+                   totals = tensor_of(row_totals, "row_totals"),
+                   offsets = tensor_of(row_offsets, "row_offsets"),
+                   indices = tensor_of(block_indices, "block_indices"),
+                   sums = tensor_of(summary, "summary");
+  // every buffer the selector writes, checked as the reference module does
+  // (csrc/bindings.cpp:95-140)
+  if (mass.dim() != 2 || order.dim() != 2)
+    throw std::runtime_error("select_retained_mass_csr: masses and indices must be 2D");
+  const int64_t rows = mass.size(0), columns = mass.size(1);
+  if (rows <= 0 || columns <= 0 || !packed_as(mass, at::kFloat, {rows, columns}) ||
+      !packed_as(order, at::kLong, {rows, columns}) || !packed_as(count, at::kInt, {rows}) ||
+      !packed_as(kept, at::kByte, {rows, columns}) || !packed_as(totals, at::kDouble, {rows, 2}) ||
+      !packed_as(offsets, at::kInt, {rows + 1}) ||
+      !packed_as(indices, at::kInt, {rows * columns}) || !packed_as(sums, at::kDouble, {3}) ||
+      scan.dim() != 1 || scan.scalar_type() != at::kByte || !scan.is_contiguous())
+    throw std::runtime_error("select_retained_mass_csr: invalid shape, dtype, or stride");
+  if (rows > INT_MAX || columns > INT_MAX || rows > INT_MAX / columns)
+    throw std::runtime_error("select_retained_mass_csr: matrix is too large");
+  if (size_t(scan.numel()) < risa_b200_selector_workspace_size(int(rows)))
+    throw std::runtime_error("select_retained_mass_csr: scan workspace is too small");
   check(risa_b200_select_retained_mass(
-      mass.data_ptr<float>(), order.data_ptr<int64_t>(),
-      static_cast<int32_t*>(tensor_of(counts, "counts").data_ptr()),
-      static_cast<uint8_t*>(tensor_of(support, "support").data_ptr()),
-      tensor_of(row_totals, "row_totals").data_ptr<double>(),
-      static_cast<int32_t*>(tensor_of(row_offsets, "row_offsets").data_ptr()),
-      static_cast<int32_t*>(tensor_of(block_indices, "block_indices").data_ptr()),
-      tensor_of(summary, "summary").data_ptr<double>(), scan.numel() ? scan.data_ptr() : nullptr,
-      size_t(scan.numel()) * scan.element_size(), int(mass.size(0)), int(mass.size(1)), theta,
-      stream_of(stream_ptr)));
+      mass.data_ptr<float>(), order.data_ptr<int64_t>(), count.data_ptr<int32_t>(),
+      kept.data_ptr<uint8_t>(), totals.data_ptr<double>(), offsets.data_ptr<int32_t>(),
+      indices.data_ptr<int32_t>(), sums.data_ptr<double>(),
+      scan.numel() ? scan.data_ptr() : nullptr, size_t(scan.numel()), int(rows), int(columns),
+      theta, stream_of(stream_ptr)));
 }
 
 void prepare_key_mask_tiles(py::object mask, py::object tiles, int tile_size,
@@ -260,6 +362,10 @@ void prepare_key_mask_tiles(py::object mask, py::object tiles, int tile_size,
   const at::Tensor m = tensor_of(mask, "mask"), t = tensor_of(tiles, "tiles");
   if (m.dim() != 4 || m.stride(2) != 0 || (tile_size != 64 && tile_size != 128))
     throw std::runtime_error("prepare_key_mask_tiles requires an expanded broadcast key mask");
+  require_key_mask_tiles(t, m.size(0), m.size(1), m.size(3), tile_size);
+  if (dtype_code(m) < 0 || !m.is_cuda() || m.device() != t.device())
+    throw std::runtime_error(
+        "prepare_key_mask_tiles requires matching CUDA devices and a supported mask dtype");
   check(risa_b200_prepare_key_mask_tiles(m.data_ptr(), static_cast<int32_t*>(t.data_ptr()),
                                          int(m.size(0)), int(m.size(1)), int(m.size(3)), tile_size,
                                          m.stride(0), m.stride(1), m.stride(3), dtype_code(m),

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 import risaattention_b200 as risa  # noqa: E402
 from risaattention_b200._validation import apply_score_mask  # noqa: E402
-from tests.util import nrmse  # noqa: E402
+from tests.util import assert_outputs_match, nrmse  # noqa: E402
 
 
 def test_available():
@@ -340,3 +340,38 @@ def test_packed_value_rows_beyond_two_gibibytes():
         del out
     del q, k, v
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+@pytest.mark.parametrize("key_length", [1, 5, 17, 63, 64, 65, 127, 128])
+@pytest.mark.parametrize("is_causal", [False, True])
+def test_key_sequences_of_one_or_two_tiles(head_dim, key_length, is_causal):
+    """Fewer keys than one tile, exactly one tile, and one key more: the packed V row is shorter
+    than the 128-key slab the tensor-core kernel loads up to 64 keys (those calls take the
+    row-per-thread kernel), and a single tile is first and last at once.  Against the FP32
+    specification; with one key the output is that key's value whatever the scores are."""
+    from risaattention_b200 import _backend
+
+    g = torch.Generator(device="cuda").manual_seed(100 * head_dim + key_length)
+    q = torch.randn(1, 4, 200, head_dim, device="cuda", generator=g).bfloat16()
+    k = torch.randn(1, 2, key_length, head_dim, device="cuda", generator=g).bfloat16()
+    v = torch.randn(1, 2, key_length, head_dim, device="cuda", generator=g).bfloat16()
+    scores = q.float() @ k.float().repeat_interleave(2, 1).transpose(-1, -2) / head_dim ** 0.5
+    scores = apply_score_mask(scores, None, is_causal, 0)
+    want = scores.softmax(-1) @ v.float().repeat_interleave(2, 1)
+    outputs = []
+    for path in (0, 1):
+        previous = _backend._C.set_attention_path(path)
+        try:
+            out, lse = risa.int8_attention(q, k, v, is_causal=is_causal, return_lse=True,
+                                           v_quantization="midpoint_affine")
+        finally:
+            _backend._C.set_attention_path(previous)
+        _backend._C.device_status()
+        outputs.append(out)
+        assert nrmse(out, want) <= 0.04
+        torch.testing.assert_close(lse, scores.logsumexp(-1), atol=0.15, rtol=0.02)
+        if key_length == 1:
+            step = v.float().abs().amax() / 127
+            assert (out.float() - v.float().repeat_interleave(2, 1)).abs().max() <= step
+    assert_outputs_match(outputs[0], outputs[1], 2e-3)

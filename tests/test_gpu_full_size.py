@@ -175,3 +175,59 @@ def test_edge_sweep_full_size(ref, dim, feature):
     if feature == "batch2_lse":
         direct, lse_direct = risa.int8_attention(q, k, v, return_lse=True)
         assert torch.equal(out, direct) and torch.equal(lse, lse_direct)
+
+
+@pytest.fixture(scope="module")
+def wide_operands():
+    """Packed operands whose query-head stride is 2^30 + 8192 bytes, so the last of the five heads
+    starts beyond 4 GiB in Q and beyond 8 GiB in the FP16 output (the reference keeps the same
+    case as an opt-in test: tests/cuda/test_large_offsets.py:22-37)."""
+    if torch.cuda.mem_get_info()[0] < 24 * 1024 ** 3:
+        pytest.skip("needs 24 GiB of free device memory")
+    length, heads, dim = (1 << 30) // 64 + 128, 5, 64
+    q = torch.zeros((1, heads, length, dim), dtype=torch.int8, device="cuda")
+    q_scale = torch.ones((1, heads, -(-length // 128) * 32), device="cuda")
+    assert (heads - 1) * q.stride(1) > (1 << 32) - 1
+    yield q, q_scale
+    del q, q_scale
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("keys", [1, 128])
+@pytest.mark.parametrize("route", ["dense", "sparse", "capture"])
+def test_head_offsets_beyond_four_gibibytes(wide_operands, route, keys):
+    """Every output element of a 5 x 16.8M-query call is checked: with zero scores and the value
+    100 x 0.2 under every key, each row is exactly 20.  One key runs the row-per-thread kernel (the
+    packed V row is shorter than a 128-key slab), 128 keys the tensor-core kernel with two tiles;
+    the sparse route keeps the first tile of every row, the capture route also checks the block
+    masses (128 queries per block, spread evenly over the key tiles)."""
+    from risaattention_b200 import _backend
+
+    q, q_scale = wide_operands
+    heads, length, dim = q.shape[1], q.shape[2], q.shape[3]
+    tiles = -(-keys // 64)
+    k = torch.zeros((1, 1, keys, dim), dtype=torch.int8, device="cuda")
+    v = torch.zeros((dim, tiles * 64), dtype=torch.int8, device="cuda")
+    v[:, :keys] = 100
+    k_scale = torch.ones((1, 1, tiles * 4), device="cuda")
+    v_scale = torch.full((dim,), 0.2, device="cuda")
+    v_center = torch.zeros_like(v_scale)
+    output = torch.empty(q.shape, dtype=torch.float16, device="cuda")
+    rows = heads * -(-length // 128)
+    extra = {}
+    if route == "sparse":
+        extra["sparse_row_offsets"] = torch.arange(rows + 1, device="cuda", dtype=torch.int32)
+        extra["sparse_block_indices"] = torch.zeros(rows, device="cuda", dtype=torch.int32)
+    elif route == "capture":
+        workspace = torch.empty(rows * tiles + heads * length * (2 * tiles + 2), device="cuda")
+        extra["block_mass"] = workspace
+    _backend._C.risa_sdpa_prequantized(q, k, v, output, q_scale, k_scale, v_scale, v_center, 64,
+                                       0.125, 1, torch.cuda.current_stream().cuda_stream, **extra)
+    torch.cuda.synchronize()
+    _status()
+    assert output.amin().item() == 20.0
+    assert output.amax().item() == 20.0
+    if route == "capture":
+        masses = workspace[: rows * tiles]
+        torch.testing.assert_close(masses, torch.full_like(masses, 128.0 / tiles), rtol=0.0,
+                                   atol=2e-5)
