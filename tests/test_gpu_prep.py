@@ -97,10 +97,12 @@ def test_prep_against_cpu_oracle():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", ["hnd", "nhd", "interleaved"])
 @pytest.mark.parametrize("length", [1025, 2048, 2049, 4097])
-def test_absmax_values_known_answer(dtype, length):
+def test_absmax_values_known_answer(dtype, length, layout):
     """Power-of-two data make codes and scales independent of rounding (the reference's own
-    known-answer test, tests/cuda/test_value_quantization.py:18-52)."""
+    known-answer test, tests/cuda/test_value_quantization.py:18-52), for head-major, token-major
+    and fused-QKV storage of V."""
     import risaattention_b200 as risa
 
     batch, heads, channels = 2, 3, 128
@@ -109,6 +111,11 @@ def test_absmax_values_known_answer(dtype, length):
     codes = ((tokens + offs) % 255 - 127).expand(batch, heads, length, channels)
     scales = 2.0 ** ((torch.arange(channels, device="cuda") % 4).float() - 2)
     v = (codes * scales).to(dtype)
+    if layout == "nhd":
+        v = v.transpose(1, 2).contiguous().transpose(1, 2)
+    elif layout == "interleaved":
+        fused = torch.empty(batch, length, 3, heads, channels, device="cuda", dtype=dtype)
+        v = fused[:, :, 1].transpose(1, 2).copy_(v)
     q = torch.zeros(batch, heads * 2, 3, channels, device="cuda", dtype=dtype)
     packed = risa.prequantize_int8_attention(q, torch.zeros_like(v), v, v_quantization="absmax")
     padded = packed.v.shape[-1]
@@ -216,3 +223,32 @@ def test_separate_entry_points_equal_the_combined_call(case, affine):
     for name in ("anchors", "q_codes", "q_scales", "k_codes", "k_scales", "v_codes", "v_scales",
                  "v_centers"):
         assert torch.equal(getattr(combined, name), getattr(apart, name)), name
+
+
+@pytest.mark.parametrize("mode", ["absmax", "midpoint_affine"])
+def test_quantisation_on_a_side_stream_and_in_a_graph(mode):
+    """Quantising on a stream other than the default one, and replaying the same call from a
+    captured graph, gives the bytes of the plain call (reference behaviour:
+    tests/cuda/test_value_quantization.py:75-91); the chained launches of the call are captured
+    with their programmatic dependencies."""
+    import risaattention_b200 as risa
+
+    g = torch.Generator(device="cuda").manual_seed(75)
+    q = torch.randn(1, 4, 17, 128, device="cuda", generator=g).bfloat16()
+    k, v = [torch.randn(1, 2, 4097, 128, device="cuda", generator=g).bfloat16() for _ in range(2)]
+    plain = risa.prequantize_int8_attention(q, k, v, v_quantization=mode)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        expected = risa.prequantize_int8_attention(q, k, v, v_quantization=mode)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            actual = risa.prequantize_int8_attention(q, k, v, v_quantization=mode)
+        for name in ("q", "k", "v", "q_scale", "k_scale", "v_scale", "v_center"):
+            getattr(actual, name).zero_()
+        graph.replay()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    for name in ("q", "k", "v", "q_scale", "k_scale", "v_scale", "v_center"):
+        assert torch.equal(getattr(actual, name), getattr(expected, name)), name
+        assert torch.equal(getattr(plain, name), getattr(expected, name)), name
