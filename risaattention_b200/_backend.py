@@ -18,6 +18,7 @@ There is no CPU fallback: when the extension or a capable GPU is missing every e
 from __future__ import annotations
 
 import ctypes
+import functools
 from pathlib import Path
 
 import torch
@@ -96,6 +97,22 @@ def _ptr(x):
     return ctypes.c_void_p(x.data_ptr())
 
 
+def _on_device_of_first_tensor(method):
+    """The library launches on the thread's current device: make the device of the call's first
+    tensor current for the duration of the call, so that tensors on another GPU are served there
+    (the C++ module does the same with a device guard)."""
+
+    @functools.wraps(method)
+    def call(self, first, *args, **kwargs):
+        first = _t(first)
+        if not first.is_cuda:
+            return method(self, first, *args, **kwargs)
+        with torch.cuda.device(first.device):
+            return method(self, first, *args, **kwargs)
+
+    return call
+
+
 def _default_cta_k(head_dim, key_length, has_mask):
     # csrc/bindings.cpp:549-551
     return 128 if (not has_mask and head_dim >= 128 and key_length > 1024) else 64
@@ -117,6 +134,7 @@ class _Native:
             raise RuntimeError(self.lib.risa_b200_last_error().decode())
 
     # -- risa_sdpa_quantize (csrc/bindings.cpp:195-272) ---------------------------------------
+    @_on_device_of_first_tensor
     def risa_sdpa_quantize(self, q, k, v, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale,
                            v_center, cta_k, input_dtype_code, use_midpoint_affine, stream_ptr,
                            anchor_indices_ptr, permutation_ptr=0, *, q_permutation_ptr=0,
@@ -144,6 +162,7 @@ class _Native:
             stream_ptr))
 
     # -- risa_sdpa (csrc/bindings.cpp:497-616) ----------------------------------------------------
+    @_on_device_of_first_tensor
     def risa_sdpa(self, q, k, v, o, q_int8, q_scale, k_int8, k_scale, v_int8, v_scale, v_center,
                   sm_scale, input_dtype_code, output_dtype_code, use_midpoint_affine, stream_ptr,
                   anchor_indices_ptr, attn_mask=None, cta_k=0, is_causal=False,
@@ -175,6 +194,7 @@ class _Native:
         return int(self.lib.risa_b200_dense_scratch_size(batch, q_heads, q_len, kv_heads, k_len,
                                                          head_dim, cta_k))
 
+    @_on_device_of_first_tensor
     def risa_dense_attention(self, q, k, v, o, scratch, cta_k, input_dtype_code,
                              use_midpoint_affine, sm_scale, output_dtype_code, is_causal,
                              stream_ptr):
@@ -191,6 +211,7 @@ class _Native:
         return int(self.lib.risa_b200_quantize_v_workspace_size(batch, kv_heads, k_len, head_dim))
 
     # -- risa_sdpa_prequantized (csrc/bindings.cpp:277-461) -------------------------------------
+    @_on_device_of_first_tensor
     def risa_sdpa_prequantized(self, q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale,
                                v_center, cta_k, sm_scale, output_dtype_code, stream_ptr,
                                attn_mask=None, sparse_row_offsets=None, sparse_block_indices=None,
@@ -253,6 +274,7 @@ class _Native:
     def select_max_key_tiles(self, cta_k) -> int:
         return int(self.lib.risa_b200_select_max_key_tiles(cta_k))
 
+    @_on_device_of_first_tensor
     def risa_sdpa_select(self, q_int8, k_int8, v_int8, o, q_scale, k_scale, v_scale, v_center,
                          cta_k, sm_scale, output_dtype_code, stream_ptr, theta, scratch, counts,
                          bitmaps, row_totals, attn_mask=None, is_causal=False, block_masses=None):
@@ -271,6 +293,7 @@ class _Native:
             int(is_causal), float(theta), _ptr(scratch), scratch.numel() * scratch.element_size(),
             _ptr(block_masses), _ptr(counts), _ptr(bitmaps), _ptr(row_totals), stream_ptr))
 
+    @_on_device_of_first_tensor
     def pack_selected(self, counts, bitmaps, row_totals, row_offsets, block_indices, summary,
                       key_blocks, stream_ptr):
         self._check(self.lib.risa_b200_pack_selected(
@@ -281,6 +304,7 @@ class _Native:
     def retained_mass_selector_workspace_size(self, row_count: int) -> int:
         return int(self.lib.risa_b200_selector_workspace_size(row_count))
 
+    @_on_device_of_first_tensor
     def select_retained_mass_csr(self, sorted_mass, descending_indices, counts, support,
                                  row_totals, row_offsets, block_indices, summary, scan_workspace,
                                  theta, stream_ptr):
@@ -294,6 +318,7 @@ class _Native:
             _ptr(row_totals), _ptr(row_offsets), _ptr(block_indices), _ptr(summary),
             _ptr(scan_workspace), scan_workspace.numel(), rows, blocks, float(theta), stream_ptr))
 
+    @_on_device_of_first_tensor
     def prepare_key_mask_tiles(self, mask, tiles, tile_size, stream_ptr):
         mask, tiles = _t(mask), _t(tiles)
         if mask.ndim != 4 or mask.stride(2) != 0 or tile_size not in (64, 128):
@@ -303,6 +328,7 @@ class _Native:
             _ptr(mask), _ptr(tiles), b, h, lk, tile_size, mask.stride(0), mask.stride(1),
             mask.stride(3), DTYPE_CODES[mask.dtype], stream_ptr))
 
+    @_on_device_of_first_tensor
     def risa_lse_shift(self, q, k, anchors, out, scale, stream_ptr):
         q, k, anchors, out = map(_t, (q, k, anchors, out))
         b, hq, lq, d = q.shape

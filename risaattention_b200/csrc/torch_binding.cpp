@@ -5,10 +5,13 @@
 // the reference's runtime passes); scratch pointers may be tensors or raw integer addresses.  The
 // module only unpacks shapes, strides and pointers and forwards them: every kernel, and every
 // check on what the kernels can take, lives behind include/risa_b200.h.  A non-zero status becomes
-// RuntimeError carrying risa_b200_last_error().
+// RuntimeError carrying risa_b200_last_error().  Every entry point makes the device of its first
+// tensor current for the duration of the call, so tensors on a GPU other than the thread's current
+// one are served on their own GPU (the library launches on the current device).
 #include <torch/extension.h>
 
 #include <ATen/DLConvertor.h>
+#include <c10/core/DeviceGuard.h>
 
 #include <climits>
 #include <cstdint>
@@ -96,6 +99,7 @@ void quantize_tensors(const at::Tensor& q, const at::Tensor& k, const at::Tensor
                       const at::Tensor& v_center, int cta_k, int input_dtype_code,
                       bool use_midpoint_affine, uintptr_t stream_ptr, void* anchors,
                       void* kv_table, void* q_table, std::optional<at::Tensor> workspace) {
+  const c10::DeviceGuard on_device(q.device());
   // shapes the kernels index by, checked in the order of the reference module
   // (csrc/bindings.cpp:196-246); what the kernels themselves can take is checked behind the C-ABI
   if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4)
@@ -153,6 +157,7 @@ void attend_tensors(const at::Tensor& q_int8, const at::Tensor& k_int8, const at
                     const std::optional<at::Tensor>& block_mass, bool is_causal,
                     const std::optional<at::Tensor>& lse,
                     const std::optional<at::Tensor>& key_mask_tiles) {
+  const c10::DeviceGuard on_device(q_int8.device());
   // checked in the order of the reference module (csrc/bindings.cpp:290-432)
   if (q_int8.dim() != 4 || k_int8.dim() != 4 || v_int8.dim() != 2 || o.dim() != 4)
     throw std::runtime_error("risa_sdpa_prequantized: q/k/o must be 4D and packed v must be 2D");
@@ -328,6 +333,7 @@ void select_retained_mass_csr(py::object sorted_mass, py::object descending_indi
   const at::Tensor mass = tensor_of(sorted_mass, "sorted_mass");
   const at::Tensor order = tensor_of(descending_indices, "descending_indices");
   const at::Tensor scan = tensor_of(scan_workspace, "scan_workspace");
+  const c10::DeviceGuard on_device(mass.device());
   const at::Tensor count = tensor_of(counts, "counts"), kept = tensor_of(support, "support"),
                    totals = tensor_of(row_totals, "row_totals"),
                    offsets = tensor_of(row_offsets, "row_offsets"),
@@ -360,6 +366,7 @@ void select_retained_mass_csr(py::object sorted_mass, py::object descending_indi
 void prepare_key_mask_tiles(py::object mask, py::object tiles, int tile_size,
                             uintptr_t stream_ptr) {
   const at::Tensor m = tensor_of(mask, "mask"), t = tensor_of(tiles, "tiles");
+  const c10::DeviceGuard on_device(m.device());
   if (m.dim() != 4 || m.stride(2) != 0 || (tile_size != 64 && tile_size != 128))
     throw std::runtime_error("prepare_key_mask_tiles requires an expanded broadcast key mask");
   require_key_mask_tiles(t, m.size(0), m.size(1), m.size(3), tile_size);
@@ -375,6 +382,7 @@ void prepare_key_mask_tiles(py::object mask, py::object tiles, int tile_size,
 void risa_lse_shift(py::object q, py::object k, py::object anchors, py::object out, float scale,
                     uintptr_t stream_ptr) {
   const at::Tensor tq = tensor_of(q, "q"), tk = tensor_of(k, "k");
+  const c10::DeviceGuard on_device(tq.device());
   check(risa_b200_correct_lse(tq.data_ptr(), tk.data_ptr(),
                               static_cast<const int32_t*>(address_of(anchors, "anchors")),
                               tensor_of(out, "out").data_ptr<float>(), int(tq.size(0)),
@@ -393,6 +401,7 @@ void risa_dense_attention(const at::Tensor& q, const at::Tensor& k, const at::Te
                           const at::Tensor& o, const at::Tensor& scratch, int cta_k,
                           int input_dtype_code, bool use_midpoint_affine, float sm_scale,
                           int output_dtype_code, bool is_causal, uintptr_t stream_ptr) {
+  const c10::DeviceGuard on_device(q.device());
   check(risa_b200_dense_attention(
       q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), scratch.data_ptr(),
       size_t(scratch.numel()), int(q.size(0)), int(q.size(1)), int(q.size(2)), int(k.size(1)),
@@ -410,6 +419,7 @@ void risa_sdpa_select(const at::Tensor& q_int8, const at::Tensor& k_int8, const 
                       const at::Tensor& bitmaps, const at::Tensor& row_totals,
                       std::optional<at::Tensor> attn_mask, bool is_causal,
                       std::optional<at::Tensor> block_masses) {
+  const c10::DeviceGuard on_device(q_int8.device());
   const int64_t b = q_int8.size(0), hq = q_int8.size(1), lq = q_int8.size(2), d = q_int8.size(3);
   const int64_t hkv = k_int8.size(1), lk = k_int8.size(2);
   int64_t ms[4] = {0, 0, 0, 0};
@@ -438,6 +448,7 @@ void pack_selected(const at::Tensor& counts, const at::Tensor& bitmaps,
                    const at::Tensor& row_totals, const at::Tensor& row_offsets,
                    const at::Tensor& block_indices, const at::Tensor& summary, int key_blocks,
                    uintptr_t stream_ptr) {
+  const c10::DeviceGuard on_device(counts.device());
   check(risa_b200_pack_selected(
       static_cast<const int32_t*>(counts.data_ptr()),
       static_cast<const uint32_t*>(bitmaps.data_ptr()), row_totals.data_ptr<double>(),
