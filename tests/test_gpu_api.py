@@ -375,3 +375,56 @@ def test_key_sequences_of_one_or_two_tiles(head_dim, key_length, is_causal):
             step = v.float().abs().amax() / 127
             assert (out.float() - v.float().repeat_interleave(2, 1)).abs().max() <= step
     assert_outputs_match(outputs[0], outputs[1], 2e-3)
+
+
+def test_concurrent_host_threads_on_their_own_streams():
+    """Four host threads, each on a stream of its own, interleave dense, masked, LSE and pattern
+    calls; every result equals the one the same call gives alone (per-call scratch, thread-local
+    error text and launch configuration, no state shared between calls)."""
+    import threading
+
+    def inputs(seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        q = torch.randn(1, 4, 260 + 16 * seed, 128, device="cuda", generator=g).bfloat16()
+        k = torch.randn(1, 2, 1100 + 64 * seed, 128, device="cuda", generator=g).bfloat16()
+        v = torch.randn(1, 2, 1100 + 64 * seed, 128, device="cuda", generator=g).bfloat16()
+        return q, k, v
+
+    def routes(q, k, v):
+        mask = torch.ones(1, 1, 1, k.shape[2], dtype=torch.bool, device="cuda")
+        mask[..., ::3] = False
+        dense = risa.int8_attention(q, k, v, v_quantization="midpoint_affine")
+        out, lse = risa.int8_attention(q, k, v, is_causal=True, return_lse=True)
+        masked = risa.int8_attention(q, k, v, attn_mask=mask)
+        built, pattern = risa.construct_sparse_int8_attention(q, k, v, theta=0.9)
+        sparse = risa.sparse_int8_attention(q, k, v, pattern)
+        return [dense, out, lse, masked, built, sparse, pattern.block_indices]
+
+    cases = [inputs(seed) for seed in range(4)]
+    alone = [routes(*case) for case in cases]
+    torch.cuda.synchronize()
+    results, failures = [None] * 4, []
+
+    def worker(index):
+        try:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.default_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(5):
+                    results[index] = routes(*cases[index])
+            stream.synchronize()
+        except Exception as error:  # noqa: BLE001 - reported by the main thread
+            failures.append((index, error))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures
+    from risaattention_b200 import _backend
+
+    _backend._C.device_status()
+    for got, want in zip(results, alone):
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
