@@ -1027,40 +1027,73 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         // summed in the reference's tree (attention_int8.cuh:1067-1086: shift-down inside each
         // warp, then the four warp sums as (w0 + w2) + (w1 + w3)), because the masses feed an
         // exact selection.  The rings are idle by now: the capture sums' area is reused.
-        float* s_mass = reinterpret_cast<float*>(smem + L::sums);  // [n_k]
-        float* s_sorted = s_mass + n_k;                            // [n_k] descending
+        const int n4 = (n_k + 3) & ~3;
+        float* s_mass = reinterpret_cast<float*>(smem + L::sums);  // [n4], padded with -inf
+        float* s_sorted = s_mass + n4;                             // [n_k] descending
         float* s_warp = s_sorted + n_k;                            // [4][n_k], then the ranks
         const int w = warp & 3;
         const bool live = ok && row_ok;
-#pragma unroll 4
-        for (int t = 0; t < n_k; ++t) {
-          const uint2 pr = pairs[size_t(t) * 128];
-          float mass = 0.0f;
-          if (live)
-            mass = denom > 0.0f ? __uint2float_rn(pr.x) * ex2_approx(__uint_as_float(pr.y) - st.m) /
-                                      denom
-                                : 0.0f;
+        // Sum over the warp's 32 rows, 32 tiles at a time: every lane leaves its row's 32 masses in
+        // a [tile][row] block of the idle P ring (rows padded to 33 words), then lane l adds up
+        // tile l's column in the order of the shift-down tree (x[i] += x[i + off] for off = 16, 8,
+        // 4, 2, 1: the value lane 0 ends with after five shuffle steps) -- 31 independent additions
+        // per lane in place of five dependent shuffles per tile.  The pairs come back from L2:
+        // sixteen tiles' loads are issued together, nothing else hides the round trip here.
+        float* stage = reinterpret_cast<float*>(smem + L::p) + w * (32 * 33);
+        constexpr int kPairBatch = 16;
+        for (int t0 = 0; t0 < n_k; t0 += 32) {
 #pragma unroll
-          for (int off = 16; off > 0; off >>= 1) mass += __shfl_down_sync(0xffffffffu, mass, off);
-          if (lane == 0) s_warp[w * n_k + t] = mass;
+          for (int jb = 0; jb < 32; jb += kPairBatch) {
+            uint2 pr[kPairBatch];
+#pragma unroll
+            for (int j = 0; j < kPairBatch; ++j)
+              pr[j] = t0 + jb + j < n_k ? pairs[size_t(t0 + jb + j) * 128] : make_uint2(0u, 0u);
+#pragma unroll
+            for (int j = 0; j < kPairBatch; ++j) {
+              float mass = 0.0f;
+              if (live && denom > 0.0f)
+                mass = __uint2float_rn(pr[j].x) * ex2_approx(__uint_as_float(pr[j].y) - st.m) /
+                       denom;
+              stage[(jb + j) * 33 + lane] = mass;
+            }
+          }
+          __syncwarp();
+          float x[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x[i] = stage[lane * 33 + i];
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int i = 0; i < off; ++i) x[i] = __fadd_rn(x[i], x[i + off]);
+          }
+          if (t0 + lane < n_k) s_warp[w * n_k + t0 + lane] = x[0];
+          __syncwarp();
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int64_t block_row = bh * n_q + bx;
-        for (int t = row_in; t < n_k; t += 128) {
-          const float mass = __fadd_rn(__fadd_rn(s_warp[t], s_warp[2 * n_k + t]),
-                                       __fadd_rn(s_warp[n_k + t], s_warp[3 * n_k + t]));
+        for (int t = row_in; t < n4; t += 128) {
+          float mass = -INFINITY;  // padding: never above and never equal to a mass
+          if (t < n_k) {
+            mass = __fadd_rn(__fadd_rn(s_warp[t], s_warp[2 * n_k + t]),
+                             __fadd_rn(s_warp[n_k + t], s_warp[3 * n_k + t]));
+            if (a.select_masses) a.select_masses[block_row * n_k + t] = mass;
+          }
           s_mass[t] = mass;
-          if (a.select_masses) a.select_masses[block_row * n_k + t] = mass;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        // descending order by counting: rank = tiles with a larger mass, ties by ascending tile id
+        // descending order by counting: rank = tiles with a larger mass, ties by ascending tile id;
+        // the masses are read four at a time (the same address in every lane: one broadcast)
         int* s_rank = reinterpret_cast<int*>(s_warp);
         for (int t = row_in; t < n_k; t += 128) {
           const float mine = s_mass[t];
           int rank = 0;
-          for (int u = 0; u < n_k; ++u) {
-            const float other = s_mass[u];
-            rank += (other > mine || (other == mine && u < t)) ? 1 : 0;
+#pragma unroll 4
+          for (int u = 0; u < n4; u += 4) {
+            const float4 other = *reinterpret_cast<const float4*>(s_mass + u);
+            rank += (other.x > mine || (other.x == mine && u < t)) ? 1 : 0;
+            rank += (other.y > mine || (other.y == mine && u + 1 < t)) ? 1 : 0;
+            rank += (other.z > mine || (other.z == mine && u + 2 < t)) ? 1 : 0;
+            rank += (other.w > mine || (other.w == mine && u + 3 < t)) ? 1 : 0;
           }
           s_sorted[rank] = mine;
           s_rank[t] = rank;
@@ -1356,7 +1389,7 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
 
 // Largest key-tile count whose masses, sorted copy and per-warp partials fit the shared-memory
 // area the in-pass selection reuses (24 bytes per key tile).
-int attention_tc_select_max_tiles(int cta_k) { return 256 * cta_k / 24; }
+int attention_tc_select_max_tiles(int cta_k) { return (256 * cta_k - 12) / 24; }
 
 int attention_tc_split_parts(int ctas, int n_k, int cta_k, int sms) {
   return split_parts(ctas, n_k, cta_k, sms);
