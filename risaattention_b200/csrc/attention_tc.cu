@@ -101,7 +101,7 @@ struct SmemLayout {
   static constexpr int rowstate = mask_stage + kMaskStageBytes;  // float [5][128]: m, d[4] (capture)
   static constexpr int v_affine = rowstate + 5 * 128 * 4;  // float [2][128]: V scales, V centres
   static constexpr int bars = v_affine + 2 * 128 * 4;      // 8-byte mbarriers
-  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 7 * 4 + 3;  // a few spare
+  static constexpr int n_bars = 1 + 2 * kKStages + 2 * kVStages + 7 * 4 + 3;  // one spare
   static constexpr int tmem_slot = bars + n_bars * 8;
   static constexpr int gave_up = tmem_slot + 8;            // site of the first expired wait, or 0
   static constexpr int total = tmem_slot + 16;
@@ -162,7 +162,8 @@ struct Bars {
   static constexpr int QFULL = 0, KFULL = 1, KEMPTY = KFULL + kKStages, VFULL = KEMPTY + kKStages,
                        VEMPTY = VFULL + kVStages, SFULL = VEMPTY + kVStages,
                        BUFFREE = SFULL + kBuffers, PFULL = BUFFREE + kBuffers, PFREE = PFULL + 4,
-                       OFULL = PFREE + 4, STATFREE = OFULL + kBuffers, WFULL = STATFREE + 4;
+                       OFULL = PFREE + 4, STATFREE = OFULL + kBuffers, WFULL = STATFREE + 4,
+                       PAIRS = WFULL + 4;  // two: the selection epilogue's bulk copies
   // Tensor memory is four accumulator buffers of 128 columns; tile it owns buffer it % 4 for its
   // whole life: Q.K^T writes the scores there (SFULL), the softmax group reads them, P.V then
   // overwrites the same columns with the tile's integer output (OFULL) and the correction group
@@ -538,6 +539,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       mbar_init(bar(Bars::PFREE + i), 1);
       mbar_init(bar(Bars::WFULL + i), 128);
     }
+    if constexpr (MODE == kSelect)
+      for (int i = 0; i < 2; ++i) mbar_init(bar(Bars::PAIRS + i), 1);
     mbar_init_fence();
   }
   if (warp == 17) tmem_alloc(sbase + L::tmem_slot, 512);
@@ -1033,32 +1036,58 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
         float* s_warp = s_sorted + n_k;                            // [4][n_k], then the ranks
         const int w = warp & 3;
         const bool live = ok && row_ok;
-        // Sum over the warp's 32 rows, 32 tiles at a time: every lane leaves its row's 32 masses in
-        // a [tile][row] block of the idle P ring (rows padded to 33 words), then lane l adds up
-        // tile l's column in the order of the shift-down tree (x[i] += x[i + off] for off = 16, 8,
-        // 4, 2, 1: the value lane 0 ends with after five shuffle steps) -- 31 independent additions
-        // per lane in place of five dependent shuffles per tile.  The pairs come back from L2:
-        // sixteen tiles' loads are issued together, nothing else hides the round trip here.
+        // The pairs of 32 tiles are 32 KB in one piece of the scratch slot: they come back as bulk
+        // copies into the idle K / V rings, two in flight, while the previous 32 tiles are reduced.
+        // Sum over a warp's 32 rows: every lane leaves its row's 32 masses in a [tile][row] block
+        // of the idle P ring (rows padded to 33 words), then lane l adds up tile l's column in the
+        // order of the shift-down tree (x[i] += x[i + off] for off = 16, 8, 4, 2, 1: the value lane
+        // 0 ends with after five shuffle steps) -- 31 independent additions per lane in place of
+        // five dependent shuffles per tile.
+        constexpr int kChunkTiles = 32;
+        constexpr uint32_t kChunkBytes = kChunkTiles * 128 * 8;
+        static_assert(L::p - L::k >= 2 * int(kChunkBytes) && L::k % 16 == 0,
+                      "the K and V rings hold two chunks of pairs");
+        static_assert(L::kSlots * kTile >= 4 * 32 * 33 * 4, "the P ring holds the four sum blocks");
         float* stage = reinterpret_cast<float*>(smem + L::p) + w * (32 * 33);
-        constexpr int kPairBatch = 16;
-        for (int t0 = 0; t0 < n_k; t0 += 32) {
+        const uint2* slot_pairs = pairs - row_in;
+        const int n_chunks = (n_k + kChunkTiles - 1) / kChunkTiles;
+        auto fetch = [&](int c) {
+          const uint32_t bytes = uint32_t(min(kChunkTiles, n_k - c * kChunkTiles)) * (128u * 8u);
+          const uint32_t full = bar(Bars::PAIRS + (c & 1));
+          mbar_expect_tx(full, bytes);
+          bulk_load(sbase + L::k + (c & 1) * kChunkBytes,
+                    slot_pairs + size_t(c) * kChunkTiles * 128, bytes, full);
+        };
+        if (row_in == 0) {
+          // the pairs were written through the generic proxy by the softmax threads, whose WFULL
+          // arrivals this thread has waited for; the bulk copies read them through the async proxy
+          fence_async_all();
+          fetch(0);
+          if (n_chunks > 1) fetch(1);
+        }
+        bool fetched = true;
+        for (int c = 0; c < n_chunks; ++c) {
+          const int t0 = c * kChunkTiles;
+          // an expired wait raises the CTA's give-up word; the loop still runs to its end so that
+          // the 128 threads meet at every barrier, and the copies in flight are drained below
+          fetched &= mbar_wait(bar(Bars::PAIRS + (c & 1)), (c >> 1) & 1, gave_up, 501);
+          const uint2* chunk =
+              reinterpret_cast<const uint2*>(smem + L::k + (c & 1) * kChunkBytes) + row_in;
+          // loads, arithmetic and stores as three separate sweeps: the 32 tiles are independent,
+          // and a store between two loads of the same memory would keep them in program order
+          uint2 pr[kChunkTiles];
 #pragma unroll
-          for (int jb = 0; jb < 32; jb += kPairBatch) {
-            uint2 pr[kPairBatch];
-#pragma unroll
-            for (int j = 0; j < kPairBatch; ++j)
-              pr[j] = t0 + jb + j < n_k ? pairs[size_t(t0 + jb + j) * 128] : make_uint2(0u, 0u);
-#pragma unroll
-            for (int j = 0; j < kPairBatch; ++j) {
-              float mass = 0.0f;
-              if (live && denom > 0.0f)
-                mass = __uint2float_rn(pr[j].x) * ex2_approx(__uint_as_float(pr[j].y) - st.m) /
-                       denom;
-              stage[(jb + j) * 33 + lane] = mass;
-            }
-          }
-          __syncwarp();
+          for (int j = 0; j < kChunkTiles; ++j) pr[j] = chunk[j * 128];
           float x[32];
+#pragma unroll
+          for (int j = 0; j < kChunkTiles; ++j) {
+            x[j] = 0.0f;
+            if (live && denom > 0.0f && t0 + j < n_k)
+              x[j] = __uint2float_rn(pr[j].x) * ex2_approx(__uint_as_float(pr[j].y) - st.m) / denom;
+          }
+#pragma unroll
+          for (int j = 0; j < kChunkTiles; ++j) stage[j * 33 + lane] = x[j];
+          __syncwarp();
 #pragma unroll
           for (int i = 0; i < 32; ++i) x[i] = stage[lane * 33 + i];
 #pragma unroll
@@ -1067,7 +1096,13 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
             for (int i = 0; i < off; ++i) x[i] = __fadd_rn(x[i], x[i + off]);
           }
           if (t0 + lane < n_k) s_warp[w * n_k + t0 + lane] = x[0];
-          __syncwarp();
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // every row has read the chunk
+          if (row_in == 0 && c + 2 < n_chunks) fetch(c + 2);
+        }
+        if (!fetched && row_in == 0) {
+          // copies that were issued land in this CTA's shared memory: wait for them before leaving
+          for (int c = max(n_chunks - 2, 0); c < n_chunks; ++c)
+            mbar_drain(bar(Bars::PAIRS + (c & 1)), (c >> 1) & 1);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int64_t block_row = bh * n_q + bx;
@@ -1081,22 +1116,40 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           s_mass[t] = mass;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        // descending order by counting: rank = tiles with a larger mass, ties by ascending tile id;
-        // the masses are read four at a time (the same address in every lane: one broadcast)
+        // Descending order by counting: rank = tiles with a larger mass + earlier tiles with the
+        // same mass.  Masses are non-negative, so their bit patterns order like signed integers
+        // (the -inf padding is negative); "larger, or equal and earlier" is one comparison against
+        // bits - 1 for the tiles before this one and against bits from this tile on.  The masses
+        // are read four at a time (the same address in every lane: one broadcast), and a thread
+        // ranks its tiles t and t + 128 from the same loads.
         int* s_rank = reinterpret_cast<int*>(s_warp);
-        for (int t = row_in; t < n_k; t += 128) {
-          const float mine = s_mass[t];
-          int rank = 0;
+        const int4* bits4 = reinterpret_cast<const int4*>(s_mass);
+        for (int t = row_in; t < n_k; t += 256) {
+          const int t2 = t + 128;
+          const bool second = t2 < n_k;
+          const int mine = __float_as_int(s_mass[t]);
+          const int mine2 = second ? __float_as_int(s_mass[t2]) : 0x7f800000;
+          int r0 = 0, r1 = 0, r2 = 0, r3 = 0, q0 = 0, q1 = 0, q2 = 0, q3 = 0;
 #pragma unroll 4
           for (int u = 0; u < n4; u += 4) {
-            const float4 other = *reinterpret_cast<const float4*>(s_mass + u);
-            rank += (other.x > mine || (other.x == mine && u < t)) ? 1 : 0;
-            rank += (other.y > mine || (other.y == mine && u + 1 < t)) ? 1 : 0;
-            rank += (other.z > mine || (other.z == mine && u + 2 < t)) ? 1 : 0;
-            rank += (other.w > mine || (other.w == mine && u + 3 < t)) ? 1 : 0;
+            const int4 other = bits4[u >> 2];
+            r0 += other.x > mine - (u < t ? 1 : 0) ? 1 : 0;
+            r1 += other.y > mine - (u + 1 < t ? 1 : 0) ? 1 : 0;
+            r2 += other.z > mine - (u + 2 < t ? 1 : 0) ? 1 : 0;
+            r3 += other.w > mine - (u + 3 < t ? 1 : 0) ? 1 : 0;
+            q0 += other.x > mine2 - (u < t2 ? 1 : 0) ? 1 : 0;
+            q1 += other.y > mine2 - (u + 1 < t2 ? 1 : 0) ? 1 : 0;
+            q2 += other.z > mine2 - (u + 2 < t2 ? 1 : 0) ? 1 : 0;
+            q3 += other.w > mine2 - (u + 3 < t2 ? 1 : 0) ? 1 : 0;
           }
-          s_sorted[rank] = mine;
+          const int rank = (r0 + r1) + (r2 + r3);
+          s_sorted[rank] = __int_as_float(mine);
           s_rank[t] = rank;
+          if (second) {
+            const int rank2 = (q0 + q1) + (q2 + q3);
+            s_sorted[rank2] = __int_as_float(mine2);
+            s_rank[t2] = rank2;
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (w == 0) {

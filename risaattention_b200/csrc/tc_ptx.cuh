@@ -153,6 +153,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, `bytes` a
+// multiple of 16), completing `bytes` on the mbarrier; no multicast.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Orders this thread's earlier accesses through the generic proxy (and those it has observed)
+// with later accesses through the async proxy, in every state space.
+__device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Asks L2 to fetch `bytes` (a multiple of 16) starting at a 16-byte aligned global address; one
 // thread, no destination, no completion to wait for.
 __device__ __forceinline__ void l2_prefetch_run(const void* address, uint32_t bytes) {
