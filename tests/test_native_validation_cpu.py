@@ -169,3 +169,35 @@ def test_key_mask_tile_entry_refuses_inconsistent_buffers():
         _backend._C.prepare_key_mask_tiles(broadcast, tiles, 64, 0)
     with pytest.raises(RuntimeError, match="key mask tiles must be contiguous CUDA int32"):
         _backend._C.prepare_key_mask_tiles(broadcast, torch.zeros(1, 2, 4, dtype=torch.int32), 64, 0)
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 2, 300, 1300, 128, 128), (2, 2, 2, 130, 70, 64, 64),
+                                   (1, 2, 1, 128, 1025, 256, 64)])
+def test_one_call_allocation_matches_the_python_allocations(shape):
+    """The module's single allocation call hands out the same nine buffers (shape, element type)
+    as the allocations the Python layer falls back to on a surface without it."""
+    from risaattention_b200._quantization import PackedBuffers
+
+    batch, q_heads, kv_heads, q_len, k_len, dim, tile = shape
+    q = torch.zeros(batch, q_heads, q_len, dim)
+    k = torch.zeros(batch, kv_heads, k_len, dim)
+    names = ("q_codes", "k_codes", "q_scales", "k_scales", "v_codes", "v_scales", "v_centers",
+             "anchors", "workspace")
+    through_module = PackedBuffers(q, k, tile)
+    original = _backend._C
+
+    class WithoutAllocation:
+        def __getattr__(self, name):
+            if name == "allocate_packed":
+                raise AttributeError(name)
+            return getattr(original, name)
+
+    _backend._C = WithoutAllocation()
+    try:
+        from_python = PackedBuffers(q, k, tile)
+    finally:
+        _backend._C = original
+    assert through_module.padded_key_length == from_python.padded_key_length
+    for name in names:
+        a, b = getattr(through_module, name), getattr(from_python, name)
+        assert a.shape == b.shape and a.dtype == b.dtype and a.is_contiguous(), name
