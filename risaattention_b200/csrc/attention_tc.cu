@@ -181,11 +181,18 @@ struct Bars {
 // score (unmasked, non-causal calls); kScoresScaled multiplies first and subtracts the maximum
 // afterwards (causal calls, for their tiles below the diagonal) -- the positive scale keeps the
 // maximum of the products equal to the product of the integer maximum.
-template <bool CAPTURE, int CTA_K, int KIND>
+// KEEPBITS (with kScoresScaled): a boolean per-query mask of the row arrives as one bit per key
+// (bit i of keep[c] = key 32 c + i is visible).  Hidden scores enter the maxima as INT_MIN, which the
+// -50000 floor of the pre-scaled arithmetic turns into the maximum a tile without a visible key
+// has, and go into the exponent pass as -inf, so their codes are zero: the arithmetic of the
+// general path on the same tile, without the trip through floats in tensor memory.
+template <bool CAPTURE, int CTA_K, int KIND, bool KEEPBITS = false>
 __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float (&sc)[4],
                                                  unsigned char* p_row, int swz, float2* stat,
                                                  uint16_t* sums, PackMultipliers mul,
-                                                 int max_floor = INT_MIN) {
+                                                 int max_floor = INT_MIN,
+                                                 const uint32_t* keep = nullptr) {
+  static_assert(!KEEPBITS || KIND == kScoresScaled, "masked tiles use the pre-scaled arithmetic");
   // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
   // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
   // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
@@ -200,6 +207,13 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     tmem_load_wait();
     tmem_regs_ready<32>(raw_a);
     tmem_regs_ready<32>(raw);
+    if constexpr (KEEPBITS) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (((keep[2 * h] >> i) & 1u) == 0u) raw_a[i] = 0x80000000u;
+        if (((keep[2 * h + 1] >> i) & 1u) == 0u) raw[i] = 0x80000000u;
+      }
+    }
     // columns of K scale group g inside a chunk: 8k + 2g, 8k + 2g + 1 for k = 0..3
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -234,6 +248,11 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
       // pre-scaled arithmetic); scalar multiplies with an explicit rounding mode on purpose: a packed
       // multiply followed by the packed add was observed to be merged into one fused operation
       for (int i = 0; i < 32; ++i) x[i] = __fmul_rn(x[i], sc[(i & 7) >> 1]);
+    }
+    if constexpr (KEEPBITS) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (((keep[c] >> i) & 1u) == 0u) x[i] = -INFINITY;
     }
     if (c > 0) tmem_load32(tmem_row + 32 * (c - 1), raw);
     uint32_t P[8], s4[8];
@@ -360,6 +379,31 @@ __device__ __forceinline__ void mask_block_rows(const AttentionArgs& a, int batc
   __syncwarp();
 }
 
+// 64 consecutive entries of one row of a boolean mask (16-byte aligned) as 64 bits: bit i of
+// keep[c] = entry 32 c + i is non-zero.  Four 16-byte loads by the thread that owns the row (issued
+// before the thread waits for the tile's scores, so that their latency passes during that wait);
+// a word of four bytes, each made 0 / 1, times 0x01020408 leaves its four bits in the top nibble.
+__device__ __forceinline__ void mask_row_load64(const unsigned char* entries, uint4 (&v)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = __ldg(reinterpret_cast<const uint4*>(entries) + j);
+}
+__device__ __forceinline__ void mask_row_bits64(const uint4 (&v)[4], uint32_t (&keep)[2]) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t w[4] = {v[2 * c + j].x, v[2 * c + j].y, v[2 * c + j].z, v[2 * c + j].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t ones = __vcmpne4(w[i], 0u) & 0x01010101u;
+        bits |= ((ones * 0x01020408u) >> 24) << (16 * j + 4 * i);
+      }
+    }
+    keep[c] = bits;
+  }
+}
+
 // A per-query mask is one long row per query: a CTA's tile touches 128 rows that lie far apart in
 // memory and takes only CTA_K elements of each, which on its own makes every access open a new
 // DRAM page.  Every kMaskRunKeys keys the warp that owns the rows therefore asks L2 for the next
@@ -477,7 +521,11 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
   *stat = make_float2(tile_m, __uint_as_float(numer));
 }
 
-template <int MODE, int CTA_K, int D>
+// BOOLROWS: the instantiation for dense calls with a boolean per-query mask whose rows can be read
+// as 16-byte pieces (chosen on the host, launch_tc): their tiles take the bit form of the fast path.
+// It is a kernel of its own so that the code of every other call stays exactly as it is -- the
+// register allocation of the tile loop reacts to any path that is compiled into it.
+template <int MODE, int CTA_K, int D, bool BOOLROWS = false>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
@@ -665,6 +713,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
     const bool int_scores = !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
     const bool causal_fast = a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const unsigned char* bool_row = nullptr;  // this row of a boolean per-query mask
+    if constexpr (BOOLROWS)
+      bool_row = static_cast<const unsigned char*>(a.mask) + int64_t(batch) * a.mask_stride_b +
+                 int64_t(head) * a.mask_stride_h + int64_t(row) * a.mask_stride_q;
     const PackMultipliers pack_mul{a.pack_by256, a.pack_by65536};
     const bool row_ok = row < a.q_len;
     const float scale2 = a.sm_scale * kLog2e;
@@ -734,6 +786,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       float2* stat = stats + slot * 128 + row_in;
       uint16_t* my_sums = sums + (slot * 128 + row_in) * (CTA_K / 4);
       unsigned char* p_row = smem + L::p + slot * kTile + row_in * 128;
+      uint4 mask_bytes[4] = {};
+      if constexpr (BOOLROWS) {
+        if (!last && row_ok) mask_row_load64(bool_row + tile * CTA_K, mask_bytes);
+      }
       ok = mbar_wait3(bar(Bars::PFREE + slot), ((it / L::kSlots) & 1) ^ 1, bar(Bars::STATFREE + slot),
                       ((it / L::kSlots) & 1) ^ 1, bar(Bars::SFULL + sb), u & 1, gave_up, 301);
       if (!ok) break;
@@ -742,13 +798,23 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       // A last tile without tail keys differs from the others only in where its maxima start;
       // with tail keys (their scores are zero-filled, not masked) it takes the general path.
-      if (int_scores && (!last || a.k_len % CTA_K == 0))
+      if (!BOOLROWS && int_scores && (!last || a.k_len % CTA_K == 0))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
                                                      my_sums, pack_mul, last ? -50000 : INT_MIN);
-      else if (below_diagonal && !last)
+      else if (!BOOLROWS && below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
-      else if (a.mask != nullptr)
+      else if (BOOLROWS && !last) {
+        // boolean per-query mask, tile wholly inside the key range: the row's 64 entries as bits
+        if constexpr (BOOLROWS) {
+          if (tile * CTA_K % kMaskRunKeys == 0)
+            mask_prefetch_runs(a, batch, head, row, tile * CTA_K + kMaskRunKeys);
+          uint32_t keep[2];
+          mask_row_bits64(mask_bytes, keep);  // rows past the end hold zeros: nothing visible
+          softmax_tile_int<CAPTURE, CTA_K, kScoresScaled, true>(
+              tmem_row, sc, p_row, row_in & 7, stat, my_sums, pack_mul, INT_MIN, keep);
+        }
+      } else if (a.mask != nullptr)
         softmax_tile_general<CAPTURE, CTA_K, true>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                                    row_in & 7, stat, my_sums, int_scores, last, row,
                                                    tile * CTA_K, mask_stage);
@@ -1339,10 +1405,22 @@ int tail_split_factor(const AttentionArgs& a, int ctas, int n_k, int sms) {
   return parts;
 }
 
-template <int MODE, int CTA_K, int D>
+// Dense calls whose mask is boolean, per query, with contiguous keys and rows that start on 16-byte
+// boundaries (base and every stride a multiple of 16 entries), a positive scale and neither causal
+// rule nor tile lists: the kernel instantiation that reads such rows as bits (64-key tiles only,
+// which per-query masks always have).
+bool reads_mask_rows_as_bits(const AttentionArgs& a) {
+  return a.cta_k == 64 && a.mask != nullptr && a.mask_dtype_code == 3 && a.mask_stride_k == 1 &&
+         a.mask_stride_q != 0 && a.sm_scale > 0.0f && !a.is_causal && a.row_offsets == nullptr &&
+         a.key_mask_tiles == nullptr && a.block_mass == nullptr && a.select_scratch == nullptr &&
+         (reinterpret_cast<uintptr_t>(a.mask) | uintptr_t(a.mask_stride_b) |
+          uintptr_t(a.mask_stride_h) | uintptr_t(a.mask_stride_q)) % 16 == 0;
+}
+
+template <int MODE, int CTA_K, int D, bool BOOLROWS = false>
 int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
               const CUtensorMap& map_v, cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<MODE, CTA_K, D>;
+  auto kernel = attention_tc_kernel<MODE, CTA_K, D, BOOLROWS>;
   static thread_local int configured = -1;  // per instantiation, thread and device
   int device = -1;
   cudaGetDevice(&device);
@@ -1429,6 +1507,10 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
     constexpr int K = decltype(cta_k)::value, HD = decltype(head_dim)::value;
     if (mode == kSelect) return launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
     if (mode == kCapture) return launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
+    if constexpr (K == 64) {
+      if (reads_mask_rows_as_bits(a))
+        return launch_tc<kDense, K, HD, true>(a, map_q, map_k, map_v, stream);
+    }
     return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
   };
   using std::integral_constant;
