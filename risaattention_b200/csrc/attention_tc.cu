@@ -525,11 +525,12 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
 // as 16-byte pieces (chosen on the host, launch_tc): their tiles take the bit form of the fast path.
 // It is a kernel of its own so that the code of every other call stays exactly as it is -- the
 // register allocation of the tile loop reacts to any path that is compiled into it.
-template <int MODE, int CTA_K, int D, bool BOOLROWS = false>
+template <int MODE, int CTA_K, int D, int VARIANT = 0>
 __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
   constexpr bool CAPTURE = MODE != kDense;  // exact per-tile statistics and denominators
+  constexpr bool BOOLROWS = VARIANT == 1, PLAIN = VARIANT == 2;
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -557,7 +558,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   }
   // Causal CTAs visit bx + 1 query blocks' worth of key tiles: the longest ones are launched first,
   // so that the short ones fill the end of the launch instead of the long ones stretching it.
-  if (a.is_causal) bx = n_q - 1 - bx;
+  if (!PLAIN && a.is_causal) bx = n_q - 1 - bx;
   const int head = by / L::kHalves, half = by % L::kHalves;
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const int64_t bh = int64_t(batch) * a.q_heads + head;
@@ -711,8 +712,8 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
-    const bool int_scores = !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
-    const bool causal_fast = a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const bool int_scores = PLAIN || (!a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr);
+    const bool causal_fast = !PLAIN && a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
     const unsigned char* bool_row = nullptr;  // this row of a boolean per-query mask
     if constexpr (BOOLROWS)
       bool_row = static_cast<const unsigned char*>(a.mask) + int64_t(batch) * a.mask_stride_b +
@@ -759,7 +760,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
     }
     float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
-    if (b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
+    if (!PLAIN && b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
         seq.ids == nullptr)
       mask_prefetch_runs(a, batch, head, row, 0);
     if (b < seq.n_iter) {
@@ -801,7 +802,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (!BOOLROWS && int_scores && (!last || a.k_len % CTA_K == 0))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
                                                      my_sums, pack_mul, last ? -50000 : INT_MIN);
-      else if (!BOOLROWS && below_diagonal && !last)
+      else if (!BOOLROWS && !PLAIN && below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
       else if (BOOLROWS && !last) {
@@ -814,7 +815,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           softmax_tile_int<CAPTURE, CTA_K, kScoresScaled, true>(
               tmem_row, sc, p_row, row_in & 7, stat, my_sums, pack_mul, INT_MIN, keep);
         }
-      } else if (a.mask != nullptr)
+      } else if (!PLAIN && a.mask != nullptr)
         softmax_tile_general<CAPTURE, CTA_K, true>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                                    row_in & 7, stat, my_sums, int_scores, last, row,
                                                    tile * CTA_K, mask_stage);
@@ -1045,7 +1046,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
       // dense path: denominator and rows share the stale maximum's units, the quotient is exact
       const float inv = rcp_approx(denom);
-      const bool zero = (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
+      const bool zero = !PLAIN && (a.is_causal || a.mask != nullptr) && !(denom > 0.0f);
       const float* vs = v_affine;
       const float* vc = v_affine + 128;
       char* o_row = static_cast<char*>(a.o) + 2 * kOut * half +
@@ -1417,10 +1418,10 @@ bool reads_mask_rows_as_bits(const AttentionArgs& a) {
           uintptr_t(a.mask_stride_h) | uintptr_t(a.mask_stride_q)) % 16 == 0;
 }
 
-template <int MODE, int CTA_K, int D, bool BOOLROWS = false>
+template <int MODE, int CTA_K, int D, int VARIANT = 0>
 int launch_tc(const AttentionArgs& a, const CUtensorMap& map_q, const CUtensorMap& map_k,
               const CUtensorMap& map_v, cudaStream_t stream) {
-  auto kernel = attention_tc_kernel<MODE, CTA_K, D, BOOLROWS>;
+  auto kernel = attention_tc_kernel<MODE, CTA_K, D, VARIANT>;
   static thread_local int configured = -1;  // per instantiation, thread and device
   int device = -1;
   cudaGetDevice(&device);
@@ -1505,12 +1506,20 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
   const int mode = a.select_scratch ? kSelect : a.block_mass ? kCapture : kDense;
   auto launch = [&](auto cta_k, auto head_dim) {
     constexpr int K = decltype(cta_k)::value, HD = decltype(head_dim)::value;
-    if (mode == kSelect) return launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
-    if (mode == kCapture) return launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
+    // calls without mask or causal rule and with a positive scale: the instantiations that hold
+    // nothing but the integer fast path and the ragged last tile
+    const bool plain = a.mask == nullptr && !a.is_causal && a.sm_scale > 0.0f;
+    if (mode == kSelect)
+      return plain ? launch_tc<kSelect, K, HD, 2>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
+    if (mode == kCapture)
+      return plain ? launch_tc<kCapture, K, HD, 2>(a, map_q, map_k, map_v, stream)
+                   : launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
     if constexpr (K == 64) {
       if (reads_mask_rows_as_bits(a))
-        return launch_tc<kDense, K, HD, true>(a, map_q, map_k, map_v, stream);
+        return launch_tc<kDense, K, HD, 1>(a, map_q, map_k, map_v, stream);
     }
+    if (plain) return launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
     return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
   };
   using std::integral_constant;
