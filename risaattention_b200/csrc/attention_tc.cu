@@ -530,7 +530,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const AttentionArgs a) {
   constexpr bool CAPTURE = MODE != kDense;  // exact per-tile statistics and denominators
-  constexpr bool BOOLROWS = VARIANT == 1, PLAIN = VARIANT == 2;
+  // Which softmax paths an instantiation holds (the host picks the instantiation, launch_tc):
+  // 0 every path; 1 boolean per-query masks read as bits; 2 no mask, not causal, positive scale;
+  // 3 causal without mask, positive scale; 4 any other mask.
+  constexpr bool BOOLROWS = VARIANT == 1, PLAIN = VARIANT == 2, CAUSAL = VARIANT == 3,
+                 MASKED = VARIANT == 4;
+  constexpr bool kHasInt = VARIANT == 0 || PLAIN, kHasScaled = VARIANT == 0 || CAUSAL,
+                 kHasMasked = VARIANT == 0 || BOOLROWS || MASKED,
+                 kHasUnmasked = VARIANT == 0 || PLAIN || CAUSAL;
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -558,7 +565,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   }
   // Causal CTAs visit bx + 1 query blocks' worth of key tiles: the longest ones are launched first,
   // so that the short ones fill the end of the launch instead of the long ones stretching it.
-  if (!PLAIN && a.is_causal) bx = n_q - 1 - bx;
+  if (CAUSAL || (!PLAIN && a.is_causal)) bx = n_q - 1 - bx;
   const int head = by / L::kHalves, half = by % L::kHalves;
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const int64_t bh = int64_t(batch) * a.q_heads + head;
@@ -712,8 +719,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
     const int row_in = threadIdx.x & 127;  // tensor-memory lane
     const int row = bx * 128 + row_in;
     const uint32_t tmem_lane = tmem + (uint32_t((warp & 3) * 32) << 16);
-    const bool int_scores = PLAIN || (!a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr);
-    const bool causal_fast = !PLAIN && a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr;
+    const bool int_scores =
+        PLAIN || (kHasInt && !a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr);
+    const bool causal_fast =
+        CAUSAL || (kHasScaled && a.is_causal && a.sm_scale > 0.0f && a.mask == nullptr);
     const unsigned char* bool_row = nullptr;  // this row of a boolean per-query mask
     if constexpr (BOOLROWS)
       bool_row = static_cast<const unsigned char*>(a.mask) + int64_t(batch) * a.mask_stride_b +
@@ -760,7 +769,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       }
     }
     float ks_next[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!PLAIN && b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
+    if (kHasMasked && b == 0 && mask_stage != nullptr && a.mask != nullptr && a.mask_stride_q != 0 &&
         seq.ids == nullptr)
       mask_prefetch_runs(a, batch, head, row, 0);
     if (b < seq.n_iter) {
@@ -799,10 +808,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       // A last tile without tail keys differs from the others only in where its maxima start;
       // with tail keys (their scores are zero-filled, not masked) it takes the general path.
-      if (!BOOLROWS && int_scores && (!last || a.k_len % CTA_K == 0))
+      if (kHasInt && int_scores && (!last || a.k_len % CTA_K == 0))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
                                                      my_sums, pack_mul, last ? -50000 : INT_MIN);
-      else if (!BOOLROWS && !PLAIN && below_diagonal && !last)
+      else if (kHasScaled && below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
       else if (BOOLROWS && !last) {
@@ -815,11 +824,11 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
           softmax_tile_int<CAPTURE, CTA_K, kScoresScaled, true>(
               tmem_row, sc, p_row, row_in & 7, stat, my_sums, pack_mul, INT_MIN, keep);
         }
-      } else if (!PLAIN && a.mask != nullptr)
+      } else if (kHasMasked && (!kHasUnmasked || a.mask != nullptr))
         softmax_tile_general<CAPTURE, CTA_K, true>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                                    row_in & 7, stat, my_sums, int_scores, last, row,
                                                    tile * CTA_K, mask_stage);
-      else
+      else if constexpr (kHasUnmasked)
         softmax_tile_general<CAPTURE, CTA_K, false>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                                     row_in & 7, stat, my_sums, int_scores, last,
                                                     row, tile * CTA_K, mask_stage);
@@ -1520,6 +1529,9 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
         return launch_tc<kDense, K, HD, 1>(a, map_q, map_k, map_v, stream);
     }
     if (plain) return launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
+    if (a.mask != nullptr) return launch_tc<kDense, K, HD, 4>(a, map_q, map_k, map_v, stream);
+    if (a.is_causal && a.sm_scale > 0.0f)
+      return launch_tc<kDense, K, HD, 3>(a, map_q, map_k, map_v, stream);
     return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
   };
   using std::integral_constant;
