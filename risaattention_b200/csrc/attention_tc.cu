@@ -275,13 +275,34 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
 // staging area as 16-byte chunks.  Chunk j of row r is stored at position j ^ f(r) of its row, f
 // chosen per row width so that both the stores (lanes = chunks of a few rows) and the loads (lanes
 // = rows, same chunk) touch every bank once per quarter warp.
+// 32 mask entries held as packed words -> FP32 bit patterns: the additive bias, 0 for a kept
+// boolean entry, NaN for a boolean false.
+template <int ESIZE>
+__device__ __forceinline__ void mask_words_to_bits(const AttentionArgs& a,
+                                                   const uint32_t (&words)[8 * ESIZE],
+                                                   uint32_t (&vals)[32]) {
+  constexpr uint32_t kMasked = 0x7fc00000u;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    if constexpr (ESIZE == 4) {
+      vals[i] = words[i];
+    } else if constexpr (ESIZE == 2) {
+      const uint32_t half_bits = (words[i >> 1] >> (16 * (i & 1))) & 0xffffu;
+      vals[i] = a.mask_dtype_code == 2
+                    ? half_bits << 16
+                    : __float_as_uint(__half2float(__ushort_as_half(static_cast<unsigned short>(half_bits))));
+    } else {
+      vals[i] = ((words[i >> 2] >> (8 * (i & 3))) & 0xffu) != 0 ? 0u : kMasked;
+    }
+  }
+}
+
 template <int ESIZE>
 __device__ __forceinline__ void mask_block_rows_vec(const AttentionArgs& a, const char* block,
                                                     int64_t row_step_bytes, uint32_t* stage,
                                                     int lane, uint32_t (&vals)[32]) {
   constexpr int LPR = 2 * ESIZE;   // 16-byte chunks per row: 8 (FP32), 4 (FP16 / BF16), 2 (bool)
   constexpr int RPI = 32 / LPR;    // rows per warp-wide request
-  constexpr uint32_t kMasked = 0x7fc00000u;
   auto fold = [](int r) { return LPR == 8 ? (r & 7) : LPR == 4 ? ((r >> 1) & 3) : ((r >> 2) & 1); };
   uint4* stage16 = reinterpret_cast<uint4*>(stage);
   const int j = lane % LPR, sub = lane / LPR;
@@ -302,19 +323,26 @@ __device__ __forceinline__ void mask_block_rows_vec(const AttentionArgs& a, cons
     words[4 * c + 3] = v.w;
   }
   __syncwarp();
+  mask_words_to_bits<ESIZE>(a, words, vals);
+}
+
+// A mask that is broadcast over the queries has one row per (batch, head): the 32 entries of a
+// chunk are the same for every row of the CTA, so each thread reads them as 16-byte pieces (the
+// same addresses in all lanes: one request per piece for the warp) instead of one entry at a time.
+template <int ESIZE>
+__device__ __forceinline__ void mask_shared_row_vec(const AttentionArgs& a, const char* entries,
+                                                    uint32_t (&vals)[32]) {
+  constexpr int LPR = 2 * ESIZE;
+  uint32_t words[4 * LPR];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    if constexpr (ESIZE == 4) {
-      vals[i] = words[i];
-    } else if constexpr (ESIZE == 2) {
-      const uint32_t half_bits = (words[i >> 1] >> (16 * (i & 1))) & 0xffffu;
-      vals[i] = a.mask_dtype_code == 2
-                    ? half_bits << 16
-                    : __float_as_uint(__half2float(__ushort_as_half(static_cast<unsigned short>(half_bits))));
-    } else {
-      vals[i] = ((words[i >> 2] >> (8 * (i & 3))) & 0xffu) != 0 ? 0u : kMasked;
-    }
+  for (int c = 0; c < LPR; ++c) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(entries) + c);
+    words[4 * c] = v.x;
+    words[4 * c + 1] = v.y;
+    words[4 * c + 2] = v.z;
+    words[4 * c + 3] = v.w;
   }
+  mask_words_to_bits<ESIZE>(a, words, vals);
 }
 
 // Mask values of a block of 32 query rows x 32 keys, fetched by the warp that owns the rows: for
@@ -432,7 +460,7 @@ __device__ __forceinline__ void mask_prefetch_runs(const AttentionArgs& a, int b
 // MASKED = false is the instantiation for causal diagonals and ragged last tiles of calls without
 // a mask: none of the mask code is in it, which matters because every CTA of such a call runs it
 // once or twice, cold.
-template <bool CAPTURE, int CTA_K, bool MASKED>
+template <bool CAPTURE, int CTA_K, bool MASKED, bool SHARED_ROW = false>
 __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int batch, int head,
                                                      bool row_ok, uint32_t tmem_row,
                                                      const float (&sc)[4], unsigned char* p_row,
@@ -454,9 +482,28 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
     uint32_t raw[32];
     float x[32];
     tmem_load32(tmem_row + 32 * c, raw);
-    if (staged) {
+    // a mask broadcast over the queries, contiguous keys, chunk inside the key range and on a
+    // 16-byte boundary: the chunk's entries as 16-byte pieces
+    const char* shared_entries = nullptr;
+    if (SHARED_ROW && masked && !staged && a.mask_stride_q == 0 && a.mask_stride_k == 1 &&
+        c0 + 32 * c + 32 <= k_len) {
+      const int esize = a.mask_dtype_code == 3 ? 1 : a.mask_dtype_code == 0 ? 4 : 2;
+      const char* entries =
+          static_cast<const char*>(a.mask) + (int64_t(batch) * a.mask_stride_b +
+                                              int64_t(head) * a.mask_stride_h + c0 + 32 * c) * esize;
+      if (reinterpret_cast<uintptr_t>(entries) % 16 == 0) shared_entries = entries;
+    }
+    if (staged || shared_entries != nullptr) {
       uint32_t bias_bits[32];
-      mask_block_rows(a, batch, head, row - lane, c0 + 32 * c, mask_stage, lane, bias_bits);
+      if (staged) {
+        mask_block_rows(a, batch, head, row - lane, c0 + 32 * c, mask_stage, lane, bias_bits);
+      } else if (a.mask_dtype_code == 0) {
+        mask_shared_row_vec<4>(a, shared_entries, bias_bits);
+      } else if (a.mask_dtype_code == 3) {
+        mask_shared_row_vec<1>(a, shared_entries, bias_bits);
+      } else {
+        mask_shared_row_vec<2>(a, shared_entries, bias_bits);
+      }
       tmem_load_wait();
       tmem_regs_ready<32>(raw);
 #pragma unroll
@@ -467,6 +514,7 @@ __device__ __forceinline__ void softmax_tile_general(const AttentionArgs& a, int
                             bias * kLog2e);
         if (!isfinite(bias)) s = -INFINITY;
         if (causal && c0 + 32 * c + i > row) s = -INFINITY;
+        if (!staged && !row_ok) s = -INFINITY;  // the staged block marks rows past the end itself
         x[i] = s;
       }
     } else {
@@ -532,11 +580,12 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   constexpr bool CAPTURE = MODE != kDense;  // exact per-tile statistics and denominators
   // Which softmax paths an instantiation holds (the host picks the instantiation, launch_tc):
   // 0 every path; 1 boolean per-query masks read as bits; 2 no mask, not causal, positive scale;
-  // 3 causal without mask, positive scale; 4 any other mask.
+  // 3 causal without mask, positive scale; 4 any other per-query mask; 5 masks broadcast over the
+  // queries (their entries are read as 16-byte pieces shared by all rows).
   constexpr bool BOOLROWS = VARIANT == 1, PLAIN = VARIANT == 2, CAUSAL = VARIANT == 3,
-                 MASKED = VARIANT == 4;
+                 MASKED = VARIANT == 4, KEYMASK = VARIANT == 5;
   constexpr bool kHasInt = VARIANT == 0 || PLAIN, kHasScaled = VARIANT == 0 || CAUSAL,
-                 kHasMasked = VARIANT == 0 || BOOLROWS || MASKED,
+                 kHasMasked = VARIANT == 0 || BOOLROWS || MASKED || KEYMASK,
                  kHasUnmasked = VARIANT == 0 || PLAIN || CAUSAL;
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
@@ -825,9 +874,10 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
               tmem_row, sc, p_row, row_in & 7, stat, my_sums, pack_mul, INT_MIN, keep);
         }
       } else if (kHasMasked && (!kHasUnmasked || a.mask != nullptr))
-        softmax_tile_general<CAPTURE, CTA_K, true>(a, batch, head, row_ok, tmem_row, sc, p_row,
-                                                   row_in & 7, stat, my_sums, int_scores, last, row,
-                                                   tile * CTA_K, mask_stage);
+        softmax_tile_general<CAPTURE, CTA_K, true, KEYMASK>(a, batch, head, row_ok, tmem_row, sc,
+                                                            p_row, row_in & 7, stat, my_sums,
+                                                            int_scores, last, row, tile * CTA_K,
+                                                            mask_stage);
       else if constexpr (kHasUnmasked)
         softmax_tile_general<CAPTURE, CTA_K, false>(a, batch, head, row_ok, tmem_row, sc, p_row,
                                                     row_in & 7, stat, my_sums, int_scores, last,
@@ -1529,7 +1579,9 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
         return launch_tc<kDense, K, HD, 1>(a, map_q, map_k, map_v, stream);
     }
     if (plain) return launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
-    if (a.mask != nullptr) return launch_tc<kDense, K, HD, 4>(a, map_q, map_k, map_v, stream);
+    if (a.mask != nullptr)
+      return a.mask_stride_q == 0 ? launch_tc<kDense, K, HD, 5>(a, map_q, map_k, map_v, stream)
+                                  : launch_tc<kDense, K, HD, 4>(a, map_q, map_k, map_v, stream);
     if (a.is_causal && a.sm_scale > 0.0f)
       return launch_tc<kDense, K, HD, 3>(a, map_q, map_k, map_v, stream);
     return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
