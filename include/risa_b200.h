@@ -197,8 +197,11 @@ int risa_b200_dense_attention(const void* q, const void* k, const void* v, void*
                               int64_t o_stride_h, int is_causal, void* stream);
 
 /* Selects which attention kernel family calls made BY THE CALLING THREAD may use: 0 = automatic
- * (tensor-core kernel where it applies), 1 = force the row-per-thread integer kernel, whose FP32
- * operation order equals the reference's (the on-device cross-check of the tensor-core kernel).
+ * (tensor-core kernel where it applies, in the instantiation for the call's class: no mask / causal
+ * / boolean rows / other per-query masks / masks broadcast over queries), 1 = force the
+ * row-per-thread integer kernel, whose FP32 operation order equals the reference's (the on-device
+ * cross-check of the tensor-core kernel), 2 = the tensor-core kernel with every softmax path
+ * compiled in, whose bits the class-specific instantiations must reproduce (a diagnostic).
  * Thread-local: other threads of the process are not affected.  Returns the previous value. */
 int risa_b200_set_attention_path(int path);
 

@@ -342,7 +342,8 @@ class _Native:
         self._check(self.lib.risa_b200_device_status())
 
     def set_attention_path(self, path: int) -> int:
-        """Kernel family for calls made by the calling thread (0 automatic, 1 row-per-thread)."""
+        """Kernel family for calls made by the calling thread (0 automatic, 1 row-per-thread, 2 the
+        tensor-core kernel with every softmax path compiled in)."""
         return int(self.lib.risa_b200_set_attention_path(path))
 
     def bounded_wait_self_test(self, limit_ns: int, stream_ptr) -> None:

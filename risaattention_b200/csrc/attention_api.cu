@@ -6,8 +6,9 @@
 namespace risa_b200 {
 namespace {
 
-// Kernel family the calling thread asked for (0 = automatic); per thread, so that a parity check
-// forcing the row-per-thread kernel cannot change what other threads of the process run.
+// Kernel family the calling thread asked for (0 = automatic, 1 = row-per-thread kernel, 2 = the
+// tensor-core kernel with every path compiled in); per thread, so that a parity check forcing a
+// kernel cannot change what other threads of the process run.
 thread_local int g_attention_path = 0;
 
 // Block mass of (query block, key tile): sum over the block's queries of
@@ -63,7 +64,7 @@ using namespace risa_b200;
 
 extern "C" int risa_b200_set_attention_path(int path) {
   const int previous = g_attention_path;
-  g_attention_path = path == 1 ? 1 : 0;
+  g_attention_path = path == 1 || path == 2 ? path : 0;
   return previous;
 }
 
@@ -167,11 +168,11 @@ int run_attention(
     a.select_counts = select->counts;
     a.select_bitmaps = select->bitmaps;
     a.select_totals = select->totals;
-    return attention_tc(a, stream);
+    return attention_tc(a, stream, g_attention_path == 2);
   }
   int status;
-  if (g_attention_path == 0 && attention_tc_supported(a))
-    status = attention_tc(a, stream);
+  if (g_attention_path != 1 && attention_tc_supported(a))
+    status = attention_tc(a, stream, g_attention_path == 2);
   else
     status = attention_rows(a, stream);
   if (status != RISA_B200_OK) return status;

@@ -114,7 +114,9 @@ __device__ __forceinline__ void store_pair(void* p, float a, float b, int out_dt
 // Kernel families (defined in attention_rows.cu / attention_tc.cu).
 int attention_rows(const AttentionArgs& a, cudaStream_t stream);
 bool attention_tc_supported(const AttentionArgs& a);
-int attention_tc(const AttentionArgs& a, cudaStream_t stream);
+// every_path: run the instantiation with all softmax paths compiled in instead of the one for the
+// call's class (the results are the same bits; a diagnostic).
+int attention_tc(const AttentionArgs& a, cudaStream_t stream, bool every_path = false);
 int attention_tc_select_max_tiles(int cta_k);
 // Parts per CTA of the last wave (0: whole CTAs) for a dense unmasked launch; attention_tc.cu.
 int attention_tc_split_parts(int ctas, int n_k, int cta_k, int sms);

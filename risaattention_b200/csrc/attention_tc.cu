@@ -1550,7 +1550,7 @@ bool attention_tc_supported(const AttentionArgs& a) {
          a.o_stride_h % 8 == 0 && a.o_stride_n % 8 == 0;
 }
 
-int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
+int attention_tc(const AttentionArgs& a, cudaStream_t stream, bool every_path) {
   const int n_k = (a.k_len + a.cta_k - 1) / a.cta_k;
   const uint32_t d = uint32_t(a.head_dim);
   CUtensorMap map_q, map_k, map_v;
@@ -1567,6 +1567,13 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream) {
     constexpr int K = decltype(cta_k)::value, HD = decltype(head_dim)::value;
     // calls without mask or causal rule and with a positive scale: the instantiations that hold
     // nothing but the integer fast path and the ragged last tile
+    // every_path: the instantiation that holds all paths, which the class-specific ones must
+    // reproduce bit for bit (a diagnostic switch of the calling thread)
+    if (every_path) {
+      if (mode == kSelect) return launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
+      if (mode == kCapture) return launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
+      return launch_tc<kDense, K, HD>(a, map_q, map_k, map_v, stream);
+    }
     const bool plain = a.mask == nullptr && !a.is_causal && a.sm_scale > 0.0f;
     if (mode == kSelect)
       return plain ? launch_tc<kSelect, K, HD, 2>(a, map_q, map_k, map_v, stream)
