@@ -581,12 +581,13 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   // Which softmax paths an instantiation holds (the host picks the instantiation, launch_tc):
   // 0 every path; 1 boolean per-query masks read as bits; 2 no mask, not causal, positive scale;
   // 3 causal without mask, positive scale; 4 any other per-query mask; 5 masks broadcast over the
-  // queries (their entries are read as 16-byte pieces shared by all rows).
-  constexpr bool BOOLROWS = VARIANT == 1, PLAIN = VARIANT == 2, CAUSAL = VARIANT == 3,
-                 MASKED = VARIANT == 4, KEYMASK = VARIANT == 5;
+  // queries (their entries are read as 16-byte pieces shared by all rows); 6 as 2 with a key length
+  // that is a whole number of tiles (no ragged last tile: the integer fast path alone).
+  constexpr bool BOOLROWS = VARIANT == 1, WHOLE = VARIANT == 6, PLAIN = VARIANT == 2 || WHOLE,
+                 CAUSAL = VARIANT == 3, MASKED = VARIANT == 4, KEYMASK = VARIANT == 5;
   constexpr bool kHasInt = VARIANT == 0 || PLAIN, kHasScaled = VARIANT == 0 || CAUSAL,
                  kHasMasked = VARIANT == 0 || BOOLROWS || MASKED || KEYMASK,
-                 kHasUnmasked = VARIANT == 0 || PLAIN || CAUSAL;
+                 kHasUnmasked = VARIANT == 0 || (PLAIN && !WHOLE) || CAUSAL;
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -857,7 +858,7 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       const bool below_diagonal = causal_fast && (tile + 1) * CTA_K - 1 <= bx * 128;
       // A last tile without tail keys differs from the others only in where its maxima start;
       // with tail keys (their scores are zero-filled, not masked) it takes the general path.
-      if (kHasInt && int_scores && (!last || a.k_len % CTA_K == 0))
+      if (WHOLE || (kHasInt && int_scores && (!last || a.k_len % CTA_K == 0)))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
                                                      my_sums, pack_mul, last ? -50000 : INT_MIN);
       else if (kHasScaled && below_diagonal && !last)
@@ -1576,8 +1577,9 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream, bool every_path) {
     }
     const bool plain = a.mask == nullptr && !a.is_causal && a.sm_scale > 0.0f;
     if (mode == kSelect)
-      return plain ? launch_tc<kSelect, K, HD, 2>(a, map_q, map_k, map_v, stream)
-                   : launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream);
+      return !plain ? launch_tc<kSelect, K, HD>(a, map_q, map_k, map_v, stream)
+             : a.k_len % K == 0 ? launch_tc<kSelect, K, HD, 6>(a, map_q, map_k, map_v, stream)
+                                : launch_tc<kSelect, K, HD, 2>(a, map_q, map_k, map_v, stream);
     if (mode == kCapture)
       return plain ? launch_tc<kCapture, K, HD, 2>(a, map_q, map_k, map_v, stream)
                    : launch_tc<kCapture, K, HD>(a, map_q, map_k, map_v, stream);
@@ -1585,7 +1587,9 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream, bool every_path) {
       if (reads_mask_rows_as_bits(a))
         return launch_tc<kDense, K, HD, 1>(a, map_q, map_k, map_v, stream);
     }
-    if (plain) return launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
+    if (plain)
+      return a.k_len % K == 0 ? launch_tc<kDense, K, HD, 6>(a, map_q, map_k, map_v, stream)
+                              : launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
     if (a.mask != nullptr)
       return a.mask_stride_q == 0 ? launch_tc<kDense, K, HD, 5>(a, map_q, map_k, map_v, stream)
                                   : launch_tc<kDense, K, HD, 4>(a, map_q, map_k, map_v, stream);
