@@ -192,7 +192,8 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
                                                  uint16_t* sums, PackMultipliers mul,
                                                  int max_floor = INT_MIN,
                                                  const uint32_t* keep = nullptr) {
-  static_assert(!KEEPBITS || KIND == kScoresScaled, "masked tiles use the pre-scaled arithmetic");
+  // (With kScoresInt the bits mark the keys that exist in a ragged last tile; the others go into
+  // the exponent pass as -1e30, the value the general path gives them.)
   // Pass 1 lands two 32-column chunks per wait (nothing else is live yet, so 64 landing registers
   // are free); pass 2 walks the chunks backwards so that it starts on chunk 3, which is still in
   // registers, and every later chunk is fetched underneath the previous chunk's exponentials.
@@ -252,7 +253,7 @@ __device__ __forceinline__ void softmax_tile_int(uint32_t tmem_row, const float 
     if constexpr (KEEPBITS) {
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (((keep[c] >> i) & 1u) == 0u) x[i] = -INFINITY;
+        if (((keep[c] >> i) & 1u) == 0u) x[i] = KIND == kScoresScaled ? -INFINITY : -1.0e30f;
     }
     if (c > 0) tmem_load32(tmem_row + 32 * (c - 1), raw);
     uint32_t P[8], s4[8];
@@ -582,12 +583,14 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
   // 0 every path; 1 boolean per-query masks read as bits; 2 no mask, not causal, positive scale;
   // 3 causal without mask, positive scale; 4 any other per-query mask; 5 masks broadcast over the
   // queries (their entries are read as 16-byte pieces shared by all rows); 6 as 2 with a key length
-  // that is a whole number of tiles (no ragged last tile: the integer fast path alone).
-  constexpr bool BOOLROWS = VARIANT == 1, WHOLE = VARIANT == 6, PLAIN = VARIANT == 2 || WHOLE,
-                 CAUSAL = VARIANT == 3, MASKED = VARIANT == 4, KEYMASK = VARIANT == 5;
+  // that is a whole number of tiles (no ragged last tile: the integer fast path alone); 7 as 2 with
+  // a ragged last tile, which takes the integer fast path with the existing keys marked by bits.
+  constexpr bool BOOLROWS = VARIANT == 1, WHOLE = VARIANT == 6, RAGGED = VARIANT == 7,
+                 PLAIN = VARIANT == 2 || WHOLE || RAGGED, CAUSAL = VARIANT == 3,
+                 MASKED = VARIANT == 4, KEYMASK = VARIANT == 5;
   constexpr bool kHasInt = VARIANT == 0 || PLAIN, kHasScaled = VARIANT == 0 || CAUSAL,
                  kHasMasked = VARIANT == 0 || BOOLROWS || MASKED || KEYMASK,
-                 kHasUnmasked = VARIANT == 0 || (PLAIN && !WHOLE) || CAUSAL;
+                 kHasUnmasked = VARIANT == 0 || VARIANT == 2 || CAUSAL;
   using L = SmemLayout<D, CTA_K>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -861,7 +864,19 @@ __global__ __launch_bounds__(kThreads, 1) void attention_tc_kernel(
       if (WHOLE || (kHasInt && int_scores && (!last || a.k_len % CTA_K == 0)))
         softmax_tile_int<CAPTURE, CTA_K, kScoresInt>(tmem_row, sc, p_row, row_in & 7, stat,
                                                      my_sums, pack_mul, last ? -50000 : INT_MIN);
-      else if (kHasScaled && below_diagonal && !last)
+      else if (RAGGED) {
+        // last visited tile of a call without mask or causal rule: the keys that exist, as bits
+        if constexpr (RAGGED) {
+          uint32_t keep[CTA_K / 32];
+#pragma unroll
+          for (int c = 0; c < CTA_K / 32; ++c) {
+            const int exist = a.k_len - (tile * CTA_K + 32 * c);
+            keep[c] = exist >= 32 ? 0xffffffffu : exist <= 0 ? 0u : (1u << exist) - 1u;
+          }
+          softmax_tile_int<CAPTURE, CTA_K, kScoresInt, true>(tmem_row, sc, p_row, row_in & 7, stat,
+                                                             my_sums, pack_mul, -50000, keep);
+        }
+      } else if (kHasScaled && below_diagonal && !last)
         softmax_tile_int<CAPTURE, CTA_K, kScoresScaled>(tmem_row, sc, p_row, row_in & 7, stat,
                                                         my_sums, pack_mul);
       else if (BOOLROWS && !last) {
@@ -1587,9 +1602,13 @@ int attention_tc(const AttentionArgs& a, cudaStream_t stream, bool every_path) {
       if (reads_mask_rows_as_bits(a))
         return launch_tc<kDense, K, HD, 1>(a, map_q, map_k, map_v, stream);
     }
-    if (plain)
-      return a.k_len % K == 0 ? launch_tc<kDense, K, HD, 6>(a, map_q, map_k, map_v, stream)
-                              : launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
+    if (plain) {
+      if (a.k_len % K == 0) return launch_tc<kDense, K, HD, 6>(a, map_q, map_k, map_v, stream);
+      // measured: the bit form of the ragged last tile gains at head_dim 128 (a 1000-key call
+      // 45 -> 34 us, long calls 0.5-1.5 %) and loses 1-4 % at head_dim 64 and 256
+      if constexpr (HD == 128) return launch_tc<kDense, K, HD, 7>(a, map_q, map_k, map_v, stream);
+      return launch_tc<kDense, K, HD, 2>(a, map_q, map_k, map_v, stream);
+    }
     if (a.mask != nullptr)
       return a.mask_stride_q == 0 ? launch_tc<kDense, K, HD, 5>(a, map_q, map_k, map_v, stream)
                                   : launch_tc<kDense, K, HD, 4>(a, map_q, map_k, map_v, stream);
